@@ -1,0 +1,80 @@
+/*
+ * Pool sub-allocator with the call interface of NVIDIA cnmem, written from scratch for this
+ * library (the reference includes "./cnmem/include/cnmem.h" at layer.h:21 and links -lcnmem at
+ * build.sh:2, but vendors neither).  Only the behaviour the reference relies on is implemented:
+ * one device, one root pool reserved up front, 512-byte granularity, best-fit allocation with
+ * coalescing on free, and "used = total - free" accounting (network.cu:1069,1098,1129,1176).
+ * The stream arguments are accepted and ignored, as the reference always passes NULL.
+ *
+ * The vdnnPool* functions below the cnmem block are extensions used by the event-ordered
+ * memory manager; the reference has no counterpart for them.
+ */
+#ifndef VDNN_B200_CNMEM_COMPAT_H_
+#define VDNN_B200_CNMEM_COMPAT_H_
+
+#include <stddef.h>
+#include <stdio.h>
+#include <cuda_runtime_api.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    CNMEM_STATUS_SUCCESS = 0,
+    CNMEM_STATUS_CUDA_ERROR,
+    CNMEM_STATUS_INVALID_ARGUMENT,
+    CNMEM_STATUS_NOT_INITIALIZED,
+    CNMEM_STATUS_OUT_OF_MEMORY,
+    CNMEM_STATUS_UNKNOWN_ERROR
+} cnmemStatus_t;
+
+typedef enum {
+    CNMEM_FLAGS_DEFAULT = 0,
+    CNMEM_FLAGS_CANNOT_GROW = 1,
+    CNMEM_FLAGS_CANNOT_STEAL = 2,
+    CNMEM_FLAGS_MANAGED = 4
+} cnmemManagerFlags_t;
+
+typedef struct cnmemDevice_t_ {
+    int device;
+    size_t size;
+    int numStreams;
+    cudaStream_t* streams;
+    size_t* streamSizes;
+} cnmemDevice_t;
+
+/* network.cu:47-53, 113-118.  The requested size is clamped to the environment variable
+ * VDNN_POOL_BYTES when that is set (the reference asks for the whole device). */
+cnmemStatus_t cnmemInit(int numDevices, const cnmemDevice_t* devices, unsigned flags);
+cnmemStatus_t cnmemFinalize(void);                                             /* network.cu:103 */
+cnmemStatus_t cnmemMalloc(void** ptr, size_t size, cudaStream_t stream);       /* layer.cu:549,989-1011 */
+cnmemStatus_t cnmemFree(void* ptr, cudaStream_t stream);                       /* network.cu:1095,1172 */
+cnmemStatus_t cnmemMemGetInfo(size_t* freeMem, size_t* totalMem, cudaStream_t stream);
+cnmemStatus_t cnmemPrintMemoryState(FILE* file, cudaStream_t stream);
+cnmemStatus_t cnmemRegisterStream(cudaStream_t stream);
+const char* cnmemGetErrorString(cnmemStatus_t status);                         /* layer.h:114 */
+
+/* ---- extensions --------------------------------------------------------------------------- */
+/* Same as cnmemFree, but remembers that the bytes are still in use on the device until every
+ * event in `events` has completed.  A later allocation that lands on those bytes makes its
+ * streams wait for the events first, so the host can free in the reference's order without
+ * synchronising. */
+cnmemStatus_t vdnnPoolFreeAfter(void* ptr, const cudaEvent_t* events, int numEvents);
+/* cnmemMalloc followed by cudaStreamWaitEvent(streams[i], e) for every pending event e that
+ * covers part of the returned block. */
+cnmemStatus_t vdnnPoolMallocFor(void** ptr, size_t size, const cudaStream_t* streams, int numStreams);
+cnmemStatus_t vdnnPoolHighWater(size_t* peakBytes, int reset);
+/* Makes the k-th allocation from now fail with CNMEM_STATUS_OUT_OF_MEMORY (k >= 1; 0 disarms).
+ * Host-side fault injection for the soft-OOM return path (layer.h:119-125). */
+cnmemStatus_t vdnnPoolFailAfter(int k);
+int vdnnPoolIsInitialized(void);
+/* Bookkeeping-only pool: hands out addresses from a range that is never backed by memory and
+ * never dereferenced.  Lets the allocation schedule of a network be replayed on a machine
+ * without a GPU (dry-run networks, allocator unit tests). */
+cnmemStatus_t vdnnPoolInitVirtual(size_t size);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

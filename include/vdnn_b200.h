@@ -1,0 +1,267 @@
+/*
+ * vdnn_b200 -- C ABI of the B200 (sm_100a) implementation of the vDNN training hot path.
+ *
+ * Every entry point replaces one library call site of james98kr/vDNN_Implementation
+ * (cuDNN / cuBLAS / CUDA runtime); the citation beside each declaration is the reference
+ * file:line it stands in for.  Conventions shared by all of them:
+ *   - plain pointers and sizes only; tensors are fp32, NCHW / KCRS, densely packed
+ *     (vdnn.h:11,19), living in device memory unless a name ends in _h;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *     work is enqueued, never synchronised;
+ *   - no entry point of sections 1-3 allocates memory: scratch is the caller-provided
+ *     `workspace` whose size vdnn_conv_workspace_bytes / vdnn_sgemm_workspace_bytes report;
+ *   - alpha / beta follow cuDNN / cuBLAS: out = alpha * op(...) + beta * out;
+ *   - the return value is VDNN_OK (0) or a negative vdnn_status; nothing falls back to a
+ *     CPU path or to another library.
+ */
+#ifndef VDNN_B200_H_
+#define VDNN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    VDNN_OK = 0,
+    VDNN_ERR_BAD_ARG = -1,        /* NULL pointer, non-positive extent, unknown enum value   */
+    VDNN_ERR_CUDA = -2,           /* a CUDA runtime call failed; see vdnn_last_cuda_error()  */
+    VDNN_ERR_WORKSPACE = -3,      /* workspace smaller than vdnn_*_workspace_bytes reports   */
+    VDNN_ERR_UNSUPPORTED = -4,    /* shape outside what the selected engine implements       */
+    VDNN_ERR_OUT_OF_MEMORY = -5,  /* pool exhausted (network-level calls only)               */
+    VDNN_ERR_TIMEOUT = -6,        /* a bounded device-side wait expired                      */
+    VDNN_ERR_STATE = -7           /* call order violated (e.g. backward before forward)      */
+} vdnn_status;
+
+const char* vdnn_status_string(int status);
+/* cudaError_t of the most recent failing runtime call on this thread (0 if none). */
+int vdnn_last_cuda_error(void);
+/* Library version and the compute capability the kernels were built for ("sm_100a"). */
+const char* vdnn_build_info(void);
+
+/* -------------------------------------------------------------------------------------------
+ * 1. Convolution and GEMM  (reference: cudnnConvolution* and cublasSgemm call sites)
+ * ----------------------------------------------------------------------------------------- */
+
+/* vdnnAlgoMode_t of the reference (vdnn.h:31-36).  MEMORY_OPT = zero-workspace kernels,
+ * PERF_OPT = kernels that may use workspace (deterministic split-K partial sums). */
+typedef enum { VDNN_ALGO_MEMORY_OPT = 0, VDNN_ALGO_PERF_OPT = 1, VDNN_ALGO_DYNAMIC = 2 } vdnn_algo_mode;
+typedef enum { VDNN_CONV_FWD = 0, VDNN_CONV_BWD_DATA = 1, VDNN_CONV_BWD_FILTER = 2 } vdnn_conv_op;
+/* Which contraction engine runs CONV/FC.  AUTO picks TCGEN05 (3xTF32 on the 5th-generation
+ * tensor cores, fp32-accurate) when the shape is supported by it and FFMA otherwise. */
+typedef enum { VDNN_ENGINE_AUTO = 0, VDNN_ENGINE_FFMA = 1, VDNN_ENGINE_TCGEN05 = 2 } vdnn_engine;
+int vdnn_set_engine(int engine);   /* process-wide; returns the previous value */
+int vdnn_get_engine(void);
+
+/* Shape of one convolution: what the reference spreads over srcTensorDesc, filterDesc and
+ * convDesc (layer.cu:152-204).  Dilation is 1, mode is cross-correlation (vdnn.h:20). */
+typedef struct {
+    int n, c, h, w;               /* input  N x C x H x W   */
+    int k, r, s;                  /* filter K x C x R x S   */
+    int pad_h, pad_w;
+    int stride_h, stride_w;
+} vdnn_conv_desc;
+
+/* cudnnGetConvolution2dForwardOutputDim (layer.cu:207-215). */
+int vdnn_conv_out_dims(const vdnn_conv_desc* d, int* p, int* q);
+/* cudnnGetPooling2dForwardOutputDim (layer.cu:431-438); padding is 0 as in the reference. */
+int vdnn_pool_out_dims(int h, int w, int win_h, int win_w, int stride_h, int stride_w, int* p, int* q);
+
+/* cudnnGetConvolution{Forward,BackwardData,BackwardFilter}WorkspaceSize (layer.cu:268-294)
+ * together with the algorithm choice of find{MemOpt,PerfOpt}*Algo (layer.cu:1013-1089):
+ * 0 for VDNN_ALGO_MEMORY_OPT, the split-K scratch of the PERF_OPT kernel otherwise. */
+size_t vdnn_conv_workspace_bytes(int op, int algo_mode, const vdnn_conv_desc* d);
+
+/* cudnnConvolutionForward (layer.cu:560-569): y = alpha * (x corr w) + beta * y.
+ * `bias` (K floats) may be NULL; when given, bias[k] is added to every y[n][k][p][q] in the
+ * same pass, which is what the reference does with a second call, cudnnAddTensor
+ * (layer.cu:576-582). */
+int vdnn_conv_fwd(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* x,
+                  const float* w, const float* bias, float beta, float* y,
+                  void* workspace, size_t workspace_bytes, void* stream);
+/* cudnnAddTensor with a 1xKx1x1 operand (layer.cu:576-582): y[n][k][*] += alpha * bias[k]. */
+int vdnn_add_bias(int n, int k, int pq, float alpha, const float* bias, float* y, void* stream);
+/* cudnnConvolutionBackwardData (layer.cu:616-625): dx = alpha * convT(dy, w) + beta * dx. */
+int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* w,
+                       const float* dy, float beta, float* dx,
+                       void* workspace, size_t workspace_bytes, void* stream);
+/* cudnnConvolutionBackwardBias (layer.cu:631-637): db[k] = alpha * sum_{n,p,q} dy + beta * db[k].
+ * The reference passes alpha = -LEARNING_RATE, beta = 1: the SGD step is part of the call. */
+int vdnn_conv_bwd_bias(int n, int k, int pq, float alpha, const float* dy, float beta, float* db,
+                       void* stream);
+/* cudnnConvolutionBackwardFilter (layer.cu:651-660): dw = alpha * (x corr dy) + beta * dw,
+ * in place on the weights when alpha = -lr, beta = 1. */
+int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* x,
+                         const float* dy, float beta, float* dw,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+/* cublasSgemm (layer.cu:677-685, 697-705, 725-733, 736-744, 752-760): column-major
+ * C(m x n) = alpha * op(A) * op(B) + beta * C, transa/transb: 0 = N, 1 = T. */
+size_t vdnn_sgemm_workspace_bytes(int algo_mode, int m, int n, int k);
+int vdnn_sgemm(int transa, int transb, int m, int n, int k, float alpha, const float* A, int lda,
+               const float* B, int ldb, float beta, float* C, int ldc,
+               int algo_mode, void* workspace, size_t workspace_bytes, void* stream);
+/* fillVectorWithOnes (layer.cu:33-38). */
+int vdnn_fill(size_t count, float value, float* dst, void* stream);
+
+/* -------------------------------------------------------------------------------------------
+ * 2. Bandwidth-bound layers  (reference: cudnnActivation*, cudnnPooling*, cudnnSoftmax*)
+ * ----------------------------------------------------------------------------------------- */
+
+/* cudnnActivationForward, RELU, PROPAGATE_NAN, out of place (layer.cu:774-781, 380-385). */
+int vdnn_relu_fwd(size_t count, const float* x, float* y, void* stream);
+/* cudnnActivationBackward (layer.cu:802-811): dx = dy where x > 0, else 0.  y is accepted
+ * for signature parity and not read. */
+int vdnn_relu_bwd(size_t count, const float* y, const float* dy, const float* x, float* dx,
+                  void* stream);
+/* cudnnPoolingForward, MAX, NOT_PROPAGATE_NAN, pad 0 (layer.cu:875-882, 417-428). */
+int vdnn_maxpool_fwd(int n, int c, int h, int w, int win_h, int win_w, int stride_h, int stride_w,
+                     const float* x, float* y, void* stream);
+/* cudnnPoolingBackward (layer.cu:903-912): dy of each window goes to the first element (row-major
+ * scan of the window) equal to the window maximum; overlapping windows accumulate. */
+int vdnn_maxpool_bwd(int n, int c, int h, int w, int win_h, int win_w, int stride_h, int stride_w,
+                     const float* y, const float* dy, const float* x, float* dx, void* stream);
+/* cudnnSoftmaxForward, ACCURATE, MODE_INSTANCE over rows x cols (layer.cu:824-832). */
+int vdnn_softmax_fwd(int rows, int cols, const float* x, float* y, void* stream);
+/* cudnnSoftmaxBackward (layer.cu:853-862): dx = y * (dy - sum_j dy_j y_j). */
+int vdnn_softmax_bwd(int rows, int cols, const float* y, const float* dy, float* dx, void* stream);
+/* calculateDiffTensor (network.cu:3-8): out = a - b. */
+int vdnn_sub(size_t count, const float* a, const float* b, float* out, void* stream);
+/* Cross-channel LRN, y = x * (k + alpha/win * sum x^2)^-beta.  No counterpart in the reference
+ * (its AlexNet omits LRN, network.cu:156-323); needed by the AlexNet benchmark configuration. */
+int vdnn_lrn_fwd(int n, int c, int hw, int win, float alpha, float beta, float k,
+                 const float* x, float* y, void* stream);
+int vdnn_lrn_bwd(int n, int c, int hw, int win, float alpha, float beta, float k,
+                 const float* x, const float* y, const float* dy, float* dx, void* stream);
+/* w += alpha * g (the SGD step the reference folds into its backward calls, layer.cu:593,712;
+ * used on its own when the gradient is all-reduced across ranks first). */
+int vdnn_axpy(size_t count, float alpha, const float* g, float* w, void* stream);
+/* out2[0] = 0.5 * sum((y - label)^2) / rows, out2[1] = -mean_rows log y[argmax label]; out2 is
+ * two doubles in device memory.  The reference computes no scalar loss (network.cu:1042-1054
+ * seeds backward with y - label directly); both figures are defined for parity reports. */
+int vdnn_loss(int rows, int cols, const float* y, const float* label, double* out2, void* stream);
+
+/* -------------------------------------------------------------------------------------------
+ * 3. Offload / prefetch  (reference: Layer::offloadSrcData, Layer::prefetchPreviousSrcData)
+ * ----------------------------------------------------------------------------------------- */
+
+/* cudaMemcpyAsync D2H of a layer's srcData into pinned memory (layer.cu:969-977).  The copy is
+ * enqueued on `copy_stream` after `ready_event` (cudaEvent_t as void*, may be NULL) and
+ * `done_event` (may be NULL) is recorded behind it. */
+int vdnn_offload(void* dst_pinned_h, const void* src, size_t bytes, void* ready_event,
+                 void* done_event, void* copy_stream);
+/* cudaMemcpyAsync H2D of an offloaded srcData into a fresh buffer (layer.cu:979-987). */
+int vdnn_prefetch(void* dst, const void* src_pinned_h, size_t bytes, void* ready_event,
+                  void* done_event, void* copy_stream);
+
+/* -------------------------------------------------------------------------------------------
+ * 4. Network driver  (reference: class Network, network.h:15-95, and main(), vdnn.cu:56-83)
+ *    The C++ classes Network and Layer of this library keep the reference's method names;
+ *    these entry points expose them to non-C++ hosts.
+ * ----------------------------------------------------------------------------------------- */
+
+/* Layer constructor arguments of the reference (layer.h:133-154). */
+typedef struct {
+    int type;                     /* Layer_t, vdnn.h:38-50; 9 = LRN */
+    int n, c, h, w;
+    int pad_h, pad_w, stride_h, stride_w;
+    int k, r, s;
+} vdnn_layer_spec;
+
+typedef struct {
+    int cnn_type;                 /* CNN_t, vdnn.h:52-61; 7 = ALEXNET with two LRN layers      */
+    int vdnn_type;                /* vdnn_t, vdnn.h:23-29                                       */
+    int algo_mode;                /* vdnnAlgoMode_t, vdnn.h:31-36                               */
+    int batch_size;               /* 0 = the reference default for the model (network.cu:142-147) */
+    int device;                   /* CUDA device ordinal (vdnn.h:5 hard-codes 0)                 */
+    size_t pool_bytes;            /* pool capacity; 0 = 24e9.  The reference takes all of the
+                                     device, rounded down to 1e9 (network.cu:49)                 */
+    float learning_rate;          /* vdnn.h:8 fixes 1e-5; <= 0 selects that value                */
+    int init_mode;                /* 0 = He-normal weights / zero bias, 1 = U(-0.01, 0.01) as
+                                     layer.cu:925-967 (seeded instead of std::random_device)     */
+    uint64_t weight_seed_base;    /* layer l uses weight_seed_base + l                           */
+    int fix_input_leak;           /* 1 = free the superseded input buffer (network.cu:1185 drops it) */
+    int host_sync_per_layer;      /* 1 = cudaStreamSynchronize both streams after every layer as
+                                     network.cu:1089-1091,1167-1169 do; 0 = event-ordered         */
+    int verbose;                  /* 1 = print the reference's banners and per-layer memory lines */
+    int capture;                  /* 1 = keep a host copy of every layer's dst / grad for parity  */
+    const vdnn_layer_spec* custom_layers;   /* CUSTOM_CNN topology (network.cu:815-817 is empty) */
+    int num_custom_layers;
+} vdnn_network_config;
+
+typedef struct vdnn_network vdnn_network;
+
+int vdnn_network_create(vdnn_network** out, const vdnn_network_config* cfg);
+int vdnn_network_destroy(vdnn_network* net);
+int vdnn_network_num_layers(const vdnn_network* net);
+int vdnn_network_layer_spec(const vdnn_network* net, int layer, vdnn_layer_spec* out);
+size_t vdnn_network_input_size(const vdnn_network* net);    /* Network::getInputSize  */
+size_t vdnn_network_output_size(const vdnn_network* net);   /* Network::getOutputSize */
+/* Copies one batch from host memory into inputData / labelData on the compute stream; replaces
+ * randomInitializeData (network.cu:819-829, 1045, 1059).  Pinned memory makes it asynchronous. */
+int vdnn_network_set_input(vdnn_network* net, const float* input_h, const float* label_h);
+/* Fills inputData / labelData on the host from the counter-based generator (input ~ N(0,1) with
+ * seed input_seed, one-hot labels with seed label_seed) and uploads them. */
+int vdnn_network_seed_input(vdnn_network* net, uint64_t input_seed, uint64_t label_seed);
+int vdnn_network_forward(vdnn_network* net);    /* Network::forwardPropagation,  network.cu:1056-1110 */
+int vdnn_network_backward(vdnn_network* net);   /* Network::backwardPropagation, network.cu:1112-1191 */
+int vdnn_network_synchronize(vdnn_network* net);
+/* Blocks until the loss of the last forward pass is on the host; out2 as in vdnn_loss. */
+int vdnn_network_loss(vdnn_network* net, double* out2);
+
+typedef enum { VDNN_TENSOR_DST = 0, VDNN_TENSOR_GRAD = 1, VDNN_TENSOR_WEIGHT = 2, VDNN_TENSOR_BIAS = 3 } vdnn_tensor_kind;
+size_t vdnn_network_tensor_size(const vdnn_network* net, int layer, int kind);
+/* WEIGHT / BIAS are read from the device; DST / GRAD come from the capture copies (capture = 1). */
+int vdnn_network_read_tensor(vdnn_network* net, int layer, int kind, float* dst_h, size_t count);
+int vdnn_network_write_tensor(vdnn_network* net, int layer, int kind, const float* src_h, size_t count);
+
+/* Allocation / offload / prefetch trace in program order. */
+typedef struct {
+    int kind;       /* 0 alloc, 1 free, 2 offload, 3 prefetch, 4 forward of `layer` done, 5 backward done */
+    int layer;
+    int tag;        /* 0 weight 1 bias 2 dst 3 diff 4 grad 5 src 6 workspace 7 ones 8 input 9 label 10 dx/dy 11 none */
+    int64_t bytes;
+    int64_t used;   /* pool bytes in use after the event (what total - free of cnmemMemGetInfo gives) */
+} vdnn_trace_event;
+int vdnn_network_trace(vdnn_network* net, vdnn_trace_event* out, int max_events, int* num_events);
+int vdnn_network_trace_reset(vdnn_network* net);
+
+typedef struct {
+    int64_t pool_peak_bytes;      /* allocator high-water mark                                   */
+    int64_t pool_used_bytes;
+    int64_t pool_capacity_bytes;
+    int64_t pinned_bytes;         /* host memory pinned for offload                              */
+    int64_t offload_bytes;        /* D2H bytes of the last forward                               */
+    int64_t prefetch_bytes;       /* H2D bytes of the last backward                              */
+    int64_t workspace_bytes_max;
+    int64_t grad_buffer_bytes;    /* data-parallel gradient staging (not part of the policy peak) */
+    float step_ms;                /* compute-stream time of the last forward + backward           */
+    float offload_ms;             /* sum of D2H copy durations                                   */
+    float prefetch_ms;            /* sum of H2D copy durations                                   */
+    float copy_overlap_ms;        /* part of the copy time that ran under compute kernels        */
+    int kernel_launches;          /* launches of this library's kernels in the last step         */
+} vdnn_network_stats;
+/* Fills timing fields only if profiling events were enabled with vdnn_network_set_profiling. */
+int vdnn_network_get_stats(vdnn_network* net, vdnn_network_stats* out);
+int vdnn_network_set_profiling(vdnn_network* net, int enabled);
+
+/* Data parallelism (no counterpart in the reference, which is single-device: vdnn.h:5).
+ * One process per GPU; gradients are written to a staging buffer, all-reduced (sum) with NCCL on
+ * a communication stream as each layer's backward finishes, then applied with vdnn_axpy. */
+int vdnn_dp_unique_id(char* out128);
+int vdnn_network_enable_dp(vdnn_network* net, int rank, int world_size, const char* unique_id128);
+/* 64-bit checksum of all weights and biases (order-dependent FNV over the raw bits). */
+int vdnn_network_weight_checksum(vdnn_network* net, uint64_t* out);
+
+/* Host-side generators used by vdnn_network_seed_input and the weight initialiser
+ * (Philox4x32-10, element index = counter). */
+void vdnn_host_fill_normal(float* dst_h, size_t count, uint64_t seed, float mean, float stddev);
+void vdnn_host_fill_uniform(float* dst_h, size_t count, uint64_t seed, float lo, float hi);
+void vdnn_host_fill_onehot(float* dst_h, int rows, int cols, uint64_t seed);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VDNN_B200_H_ */

@@ -1,0 +1,279 @@
+// C-ABI entry points for the contraction-shaped layers (CONV forward / data gradient / filter
+// gradient and SGEMM).  Each call builds the operand views of gemm_operands.cuh over the caller's
+// NCHW / KCRS tensors, plans a split along K when the output has too few tiles to fill the GPU,
+// and runs the selected engine.  Split results are combined either with fp32 atomics straight
+// into the output (MEMORY_OPT: no workspace) or through per-split partial tiles in the caller's
+// workspace followed by a fixed-order reduction (PERF_OPT: deterministic).
+#include "common.cuh"
+#include "gemm_ffma.cuh"
+#include "gemm_tc.cuh"
+
+namespace vdnn {
+namespace {
+
+int g_engine = VDNN_ENGINE_AUTO;
+
+struct SplitPlan { int splits; int k_chunk; };
+
+// Split K so that roughly two waves of 128x128 tiles exist, keeping at least 64 k per split.
+SplitPlan plan_split(int M, int N, int K) {
+    const long tiles = static_cast<long>(ceil_div(M, 128)) * ceil_div(N, 128);
+    const int sms = sm_count();
+    int splits = 1;
+    if (tiles < sms) {
+        splits = static_cast<int>(ceil_div<long>(2L * sms, tiles));
+        const int max_by_k = K / 64 > 0 ? K / 64 : 1;
+        if (splits > max_by_k) splits = max_by_k;
+        if (splits > 1024) splits = 1024;
+    }
+    int k_chunk = ceil_div(ceil_div(K, splits), 32) * 32;      // multiple of both engines' k tile
+    if (k_chunk < 32) k_chunk = 32;
+    SplitPlan p;
+    p.k_chunk = k_chunk;
+    p.splits = ceil_div(K, k_chunk);
+    return p;
+}
+
+__global__ void __launch_bounds__(256) scale_dense_kernel(size_t n, float beta, float* __restrict__ out) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
+        out[i] = beta == 0.0f ? 0.0f : beta * out[i];
+}
+
+__global__ void __launch_bounds__(256) scale_matrix_kernel(int rows, int cols, int ld, float beta, float* __restrict__ out) {
+    for (int j = blockIdx.y; j < cols; j += gridDim.y)
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < rows; i += gridDim.x * blockDim.x) {
+            float* p = out + static_cast<size_t>(j) * ld + i;
+            *p = beta == 0.0f ? 0.0f : beta * *p;
+        }
+}
+
+// out[i] = alpha * sum_s partial[s][i] + beta * out[i], splits summed in index order.
+__global__ void __launch_bounds__(256) reduce_partials_kernel(size_t n, int splits, float alpha, float beta,
+                                                              const float* __restrict__ partial, float* __restrict__ out) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride) {
+        float acc = 0.0f;
+        for (int s = 0; s < splits; ++s) acc += partial[static_cast<size_t>(s) * n + i];
+        float v = alpha * acc;
+        if (beta != 0.0f) v = fmaf(beta, out[i], v);
+        out[i] = v;
+    }
+}
+
+int stream_blocks(size_t n) {
+    size_t want = ceil_div<size_t>(n, 256);
+    const size_t cap = static_cast<size_t>(sm_count()) * 8;
+    if (want > cap) want = cap;
+    return want ? static_cast<int>(want) : 1;
+}
+
+template <class OpA, class OpB, bool AKC, bool BKC>
+int run_engine(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K, int splits, int k_chunk,
+               cudaStream_t stream) {
+    if (g_engine != VDNN_ENGINE_FFMA && tc::supported<OpA, OpB>(M, N, K)) {
+        return tc::launch<OpA, OpB, AKC, BKC>(a, b, epi, M, N, K, splits, k_chunk, stream);
+    }
+    if (g_engine == VDNN_ENGINE_TCGEN05) return VDNN_ERR_UNSUPPORTED;
+    return ffma::launch<OpA, OpB, AKC, BKC>(a, b, epi, M, N, K, splits, k_chunk, stream);
+}
+
+// `epi` arrives configured for a direct store (out, alpha, beta, bias, addressing).
+// dense_elems > 0 says the output is one dense block of that many floats (needed for PARTIAL).
+template <class OpA, class OpB, bool AKC, bool BKC>
+int contract(const OpA& a, const OpB& b, Epilogue epi, int M, int N, int K, size_t dense_elems, int ld_rows,
+             int algo_mode, void* ws, size_t ws_bytes, cudaStream_t stream) {
+    SplitPlan plan = plan_split(M, N, K);
+    if (epi.bias) { plan.splits = 1; plan.k_chunk = ceil_div(K, 32) * 32; }
+    if (plan.splits == 1) {
+        epi.mode = EPI_DIRECT;
+        return run_engine<OpA, OpB, AKC, BKC>(a, b, epi, M, N, K, 1, plan.k_chunk, stream);
+    }
+    if (algo_mode == VDNN_ALGO_PERF_OPT && dense_elems > 0) {
+        const size_t need = static_cast<size_t>(plan.splits) * dense_elems * sizeof(float);
+        if (!ws || ws_bytes < need) return VDNN_ERR_WORKSPACE;
+        Epilogue part = epi;
+        part.mode = EPI_PARTIAL;
+        part.out = static_cast<float*>(ws);
+        part.partial_stride = dense_elems;
+        int st = run_engine<OpA, OpB, AKC, BKC>(a, b, part, M, N, K, plan.splits, plan.k_chunk, stream);
+        if (st != VDNN_OK) return st;
+        reduce_partials_kernel<<<stream_blocks(dense_elems), 256, 0, stream>>>(dense_elems, plan.splits, epi.alpha, epi.beta,
+                                                                             static_cast<const float*>(ws), epi.out);
+        VDNN_LAUNCHED();
+        return VDNN_OK;
+    }
+    // zero-workspace path: out = beta * out, then every split adds alpha * partial atomically
+    if (epi.beta != 1.0f) {
+        if (dense_elems > 0) {
+            if (epi.beta == 0.0f) VDNN_CUDA(cudaMemsetAsync(epi.out, 0, dense_elems * sizeof(float), stream));
+            else {
+                scale_dense_kernel<<<stream_blocks(dense_elems), 256, 0, stream>>>(dense_elems, epi.beta, epi.out);
+                VDNN_LAUNCHED();
+            }
+        } else {
+            dim3 grid(ceil_div(M, 256), N < 65535 ? N : 65535);
+            scale_matrix_kernel<<<grid, 256, 0, stream>>>(M, N, ld_rows, epi.beta, epi.out);
+            VDNN_LAUNCHED();
+        }
+    }
+    epi.mode = EPI_ATOMIC;
+    return run_engine<OpA, OpB, AKC, BKC>(a, b, epi, M, N, K, plan.splits, plan.k_chunk, stream);
+}
+
+bool valid_desc(const vdnn_conv_desc* d, int* P, int* Q) {
+    if (!d || d->n <= 0 || d->c <= 0 || d->h <= 0 || d->w <= 0 || d->k <= 0 || d->r <= 0 || d->s <= 0 ||
+        d->pad_h < 0 || d->pad_w < 0 || d->stride_h <= 0 || d->stride_w <= 0)
+        return false;
+    if (d->h + 2 * d->pad_h < d->r || d->w + 2 * d->pad_w < d->s) return false;
+    *P = (d->h + 2 * d->pad_h - d->r) / d->stride_h + 1;
+    *Q = (d->w + 2 * d->pad_w - d->s) / d->stride_w + 1;
+    return true;
+}
+
+// Offsets are 32-bit inside the kernels: every tensor must stay below 2^31 elements.
+bool fits_int32(const vdnn_conv_desc* d, int P, int Q) {
+    const long long lim = 0x7fffffffLL;
+    return 1LL * d->n * d->c * d->h * d->w < lim && 1LL * d->n * d->k * P * Q < lim &&
+           1LL * d->k * d->c * d->r * d->s < lim;
+}
+
+XGather make_xgather(const vdnn_conv_desc* d, const float* x, int P, int Q) {
+    XGather g;
+    g.x = x; g.C = d->c; g.H = d->h; g.W = d->w; g.R = d->r; g.S = d->s;
+    g.pad_h = d->pad_h; g.pad_w = d->pad_w; g.stride_h = d->stride_h; g.stride_w = d->stride_w;
+    g.n_pix = d->n * P * Q; g.n_filt = d->c * d->r * d->s;
+    g.div_pq = FastDiv(P * Q); g.div_q = FastDiv(Q); g.div_rs = FastDiv(d->r * d->s); g.div_s = FastDiv(d->s);
+    g.chw = d->c * d->h * d->w; g.hw = d->h * d->w;
+    return g;
+}
+
+}  // namespace
+}  // namespace vdnn
+
+using namespace vdnn;
+
+extern "C" {
+
+int vdnn_set_engine(int engine) {
+    if (engine < VDNN_ENGINE_AUTO || engine > VDNN_ENGINE_TCGEN05) return VDNN_ERR_BAD_ARG;
+    const int prev = g_engine;
+    g_engine = engine;
+    return prev;
+}
+
+int vdnn_get_engine(void) { return g_engine; }
+
+int vdnn_conv_out_dims(const vdnn_conv_desc* d, int* p, int* q) {
+    int P, Q;
+    if (!p || !q || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
+    *p = P; *q = Q;
+    return VDNN_OK;
+}
+
+size_t vdnn_conv_workspace_bytes(int op, int algo_mode, const vdnn_conv_desc* d) {
+    int P, Q;
+    if (!valid_desc(d, &P, &Q) || algo_mode != VDNN_ALGO_PERF_OPT) return 0;
+    int M, N, K;
+    size_t out;
+    const int crs = d->c * d->r * d->s;
+    switch (op) {
+    case VDNN_CONV_FWD: M = d->n * P * Q; N = d->k; K = crs; out = static_cast<size_t>(M) * N; break;
+    case VDNN_CONV_BWD_DATA: M = d->n * d->h * d->w; N = d->c; K = d->k * d->r * d->s; out = static_cast<size_t>(M) * N; break;
+    case VDNN_CONV_BWD_FILTER: M = d->k; N = crs; K = d->n * P * Q; out = static_cast<size_t>(M) * N; break;
+    default: return 0;
+    }
+    const SplitPlan plan = plan_split(M, N, K);
+    return plan.splits > 1 ? static_cast<size_t>(plan.splits) * out * sizeof(float) : 0;
+}
+
+int vdnn_conv_fwd(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* x, const float* w,
+                  const float* bias, float beta, float* y, void* workspace, size_t workspace_bytes, void* stream) {
+    int P, Q;
+    if (!x || !w || !y || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
+    if (!fits_int32(d, P, Q)) return VDNN_ERR_UNSUPPORTED;
+    const int crs = d->c * d->r * d->s, pq = P * Q;
+    XGatherPixRows A; A.g = make_xgather(d, x, P, Q);
+    SplitDense B = make_dense(w, d->k, crs, crs, 1);
+    Epilogue e{};
+    e.out = y; e.bias = bias; e.alpha = alpha; e.beta = beta;
+    e.row_div = FastDiv(pq); e.row_hi = d->k * pq; e.row_lo = 1; e.col_stride = pq;
+    const int M = d->n * pq;
+    return contract<XGatherPixRows, SplitDense, false, true>(A, B, e, M, d->k, crs, static_cast<size_t>(M) * d->k, 0,
+                                                             algo_mode, workspace, workspace_bytes, as_stream(stream));
+}
+
+int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* w, const float* dy,
+                       float beta, float* dx, void* workspace, size_t workspace_bytes, void* stream) {
+    int P, Q;
+    if (!w || !dy || !dx || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
+    if (!fits_int32(d, P, Q)) return VDNN_ERR_UNSUPPORTED;
+    const int rs = d->r * d->s, hw = d->h * d->w, pq = P * Q;
+    DyGather A;
+    A.dy = dy; A.K = d->k; A.P = P; A.Q = Q; A.R = d->r; A.S = d->s;
+    A.pad_h = d->pad_h; A.pad_w = d->pad_w; A.stride_h = d->stride_h; A.stride_w = d->stride_w;
+    A.n_pix = d->n * hw; A.n_cols = d->k * rs;
+    A.div_hw = FastDiv(hw); A.div_w = FastDiv(d->w); A.div_rs = FastDiv(rs); A.div_s = FastDiv(d->s);
+    A.div_sh = FastDiv(d->stride_h); A.div_sw = FastDiv(d->stride_w);
+    A.kpq = d->k * pq; A.pq = pq;
+    // weights viewed as [c][(k, rs)]: offset = c*RS + k*C*RS + rs
+    SplitDense B;
+    B.p = w; B.rows = d->c; B.cols = d->k * rs;
+    B.row_div = FastDiv(1u << 30); B.row_hi = 0; B.row_lo = rs;
+    B.col_div = FastDiv(rs); B.col_hi = d->c * rs; B.col_lo = 1;
+    Epilogue e{};
+    e.out = dx; e.bias = nullptr; e.alpha = alpha; e.beta = beta;
+    e.row_div = FastDiv(hw); e.row_hi = d->c * hw; e.row_lo = 1; e.col_stride = hw;
+    const int M = d->n * hw;
+    return contract<DyGather, SplitDense, false, true>(A, B, e, M, d->c, d->k * rs, static_cast<size_t>(M) * d->c, 0,
+                                                       algo_mode, workspace, workspace_bytes, as_stream(stream));
+}
+
+int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* x, const float* dy,
+                         float beta, float* dw, void* workspace, size_t workspace_bytes, void* stream) {
+    int P, Q;
+    if (!x || !dy || !dw || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
+    if (!fits_int32(d, P, Q)) return VDNN_ERR_UNSUPPORTED;
+    const int crs = d->c * d->r * d->s, pq = P * Q;
+    // dy viewed as [k][(n, pq)]: offset = k*PQ + n*K*PQ + pq
+    SplitDense A;
+    A.p = dy; A.rows = d->k; A.cols = d->n * pq;
+    A.row_div = FastDiv(1u << 30); A.row_hi = 0; A.row_lo = pq;
+    A.col_div = FastDiv(pq); A.col_hi = d->k * pq; A.col_lo = 1;
+    XGatherFiltRows B; B.g = make_xgather(d, x, P, Q);
+    Epilogue e{};
+    e.out = dw; e.bias = nullptr; e.alpha = alpha; e.beta = beta;
+    e.row_div = FastDiv(1u << 30); e.row_hi = 0; e.row_lo = crs; e.col_stride = 1;
+    return contract<SplitDense, XGatherFiltRows, true, true>(A, B, e, d->k, crs, d->n * pq, static_cast<size_t>(d->k) * crs, 0,
+                                                             algo_mode, workspace, workspace_bytes, as_stream(stream));
+}
+
+size_t vdnn_sgemm_workspace_bytes(int algo_mode, int m, int n, int k) {
+    if (algo_mode != VDNN_ALGO_PERF_OPT || m <= 0 || n <= 0 || k <= 0) return 0;
+    const SplitPlan plan = plan_split(m, n, k);
+    return plan.splits > 1 ? static_cast<size_t>(plan.splits) * m * n * sizeof(float) : 0;
+}
+
+int vdnn_sgemm(int transa, int transb, int m, int n, int k, float alpha, const float* A, int lda, const float* B,
+               int ldb, float beta, float* C, int ldc, int algo_mode, void* workspace, size_t workspace_bytes,
+               void* stream) {
+    if (!A || !B || !C || m <= 0 || n <= 0 || k <= 0 || ldc < m) return VDNN_ERR_BAD_ARG;
+    if (lda < (transa ? k : m) || ldb < (transb ? n : k)) return VDNN_ERR_BAD_ARG;
+    const long long lim = 0x7fffffffLL;
+    if (1LL * lda * (transa ? m : k) >= lim || 1LL * ldb * (transb ? k : n) >= lim || 1LL * ldc * n >= lim)
+        return VDNN_ERR_UNSUPPORTED;
+    // A'(i, kk) = op(A)[i][kk], B'(j, kk) = op(B)[kk][j]
+    SplitDense a = transa ? make_dense(A, m, k, lda, 1) : make_dense(A, m, k, 1, lda);
+    SplitDense b = transb ? make_dense(B, n, k, 1, ldb) : make_dense(B, n, k, ldb, 1);
+    Epilogue e{};
+    e.out = C; e.bias = nullptr; e.alpha = alpha; e.beta = beta;
+    e.row_div = FastDiv(1u << 30); e.row_hi = 0; e.row_lo = 1; e.col_stride = ldc;
+    const size_t dense = (ldc == m) ? static_cast<size_t>(m) * n : 0;
+    cudaStream_t s = as_stream(stream);
+    if (transa && !transb) return contract<SplitDense, SplitDense, true, true>(a, b, e, m, n, k, dense, ldc, algo_mode, workspace, workspace_bytes, s);
+    if (!transa && !transb) return contract<SplitDense, SplitDense, false, true>(a, b, e, m, n, k, dense, ldc, algo_mode, workspace, workspace_bytes, s);
+    if (!transa && transb) return contract<SplitDense, SplitDense, false, false>(a, b, e, m, n, k, dense, ldc, algo_mode, workspace, workspace_bytes, s);
+    return contract<SplitDense, SplitDense, true, false>(a, b, e, m, n, k, dense, ldc, algo_mode, workspace, workspace_bytes, s);
+}
+
+}  // extern "C"

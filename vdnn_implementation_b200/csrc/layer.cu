@@ -1,0 +1,483 @@
+// Layer operators of the vDNN driver.  Method names and call order follow the reference's
+// layer.cu (cited per method); the arithmetic is delegated to this library's own sm_100a kernels
+// through the C ABI, and device memory is ordered with events instead of host synchronisation.
+#include "layer.h"
+
+#include <math.h>
+#include <string.h>
+
+#include <string>
+
+// Device work is skipped when the context replays the schedule without a GPU.
+#define DEV(call)                                         \
+    do {                                                  \
+        if (!handle->dry_run) {                           \
+            const int _st = (call);                       \
+            if (_st != VDNN_OK) return _st;               \
+        }                                                 \
+    } while (0)
+#define CU(call)                                                         \
+    do {                                                                 \
+        if (!handle->dry_run && (call) != cudaSuccess) {                 \
+            fprintf(stderr, "CUDA failure at %s:%d: %s\n", __FILE__, __LINE__, cudaGetErrorString(cudaGetLastError())); \
+            return VDNN_ERR_CUDA;                                        \
+        }                                                                \
+    } while (0)
+
+/* ------------------------------------------------------------------ context */
+
+void vdnnContext::record(int kind, int layer, int tag, int64_t bytes) {
+    if (!trace_enabled) return;
+    size_t free_b = 0, total_b = 0;
+    cnmemMemGetInfo(&free_b, &total_b, NULL);
+    vdnn_trace_event e;
+    e.kind = kind; e.layer = layer; e.tag = tag; e.bytes = bytes;
+    e.used = static_cast<int64_t>(total_b - free_b);
+    trace.push_back(e);
+}
+
+int vdnnContext::alloc(void** ptr, size_t bytes, int layer, int tag, bool isDynamic,
+                       std::initializer_list<cudaStream_t> streams) {
+    std::vector<cudaStream_t> s(streams);
+    const cnmemStatus_t st = vdnnPoolMallocFor(ptr, bytes, s.data(), dry_run ? 0 : static_cast<int>(s.size()));
+    if (st == CNMEM_STATUS_OUT_OF_MEMORY) {
+        if (isDynamic) return -1;                       // soft failure (layer.h:119-125)
+        fprintf(stderr, "\n[pool exhausted: %zu bytes for layer %d, tag %d]\n", bytes, layer, tag);
+        return VDNN_ERR_OUT_OF_MEMORY;
+    }
+    if (st != CNMEM_STATUS_SUCCESS) {
+        fprintf(stderr, "\n[pool allocation failed with %s]\n", cnmemGetErrorString(st));
+        return VDNN_ERR_CUDA;
+    }
+    record(0, layer, tag, static_cast<int64_t>(bytes));
+    return 0;
+}
+
+int vdnnContext::release(void* ptr, size_t bytes, int layer, int tag, std::initializer_list<cudaEvent_t> after) {
+    std::vector<cudaEvent_t> ev;
+    if (!dry_run && !host_sync_per_layer)
+        for (cudaEvent_t e : after) if (e) ev.push_back(e);
+    const cnmemStatus_t st = vdnnPoolFreeAfter(ptr, ev.data(), static_cast<int>(ev.size()));
+    if (st != CNMEM_STATUS_SUCCESS) {
+        fprintf(stderr, "\n[pool free failed with %s]\n", cnmemGetErrorString(st));
+        return VDNN_ERR_STATE;
+    }
+    record(1, layer, tag, static_cast<int64_t>(bytes));
+    return 0;
+}
+
+int vdnnContext::upload(void* dst, const void* src_h, size_t bytes) {
+    if (dry_run) return VDNN_OK;
+    return cudaMemcpy(dst, src_h, bytes, cudaMemcpyHostToDevice) == cudaSuccess ? VDNN_OK : VDNN_ERR_CUDA;
+}
+
+/* ------------------------------------------------------------------ construction (layer.cu:40-485) */
+
+static const char* type_name(Layer_t t) {
+    switch (t) {
+    case FC_GEMM: return "FC_GEMM";
+    case CONV: case FC_CONV: return "FC_CONV";     // the reference prints FC_CONV for both (layer.cu:152)
+    case RELU: return "RELU"; case TANH: return "TANH"; case SIGMOID: return "SIGMOID";
+    case SOFTMAX: return "SOFTMAX"; case POOL: return "POOL"; case LRN: return "LRN";
+    default: return "CONCATENATE";
+    }
+}
+
+Layer::Layer(vdnn_t _vdnnMode, vdnnAlgoMode_t _vdnnAlgoMode, Layer_t _layerType, vdnnHandle_t* _handle,
+             cudaStream_t* _stream_compute, cudaStream_t* _stream_memory, int _id,
+             int _n, int _c, int _h, int _w, int _pad_h, int _pad_w, int _stride_h, int _stride_w,
+             int _k, int _r, int _s)
+    : vdnnMode(_vdnnMode), vdnnAlgoMode(_vdnnAlgoMode), layerType(_layerType), layerId(_id), constructed(false),
+      n_in(_n), c_in(_c), h_in(_h), w_in(_w), pad_h(_pad_h), pad_w(_pad_w), stride_h(_stride_h), stride_w(_stride_w),
+      k(_k), r(_r), s(_s), n_out(_n), c_out(_c), h_out(_h), w_out(_w),
+      fwdWorkSpaceSize(0), bwdDataWorkSpaceSize(0), bwdFilterWorkSpaceSize(0),
+      stream_compute(_stream_compute), stream_memory(_stream_memory), handle(*_handle),
+      srcData(NULL), filterData(NULL), biasData(NULL), dstData(NULL), diffData(NULL), gradData(NULL),
+      gradFilter(NULL), gradBias(NULL) {
+    switch (layerType) {
+    case FC_GEMM:
+        if (!(h_in == 1 && w_in == 1 && r == 1 && s == 1)) { fprintf(stderr, "Invalid dimensions!\n"); return; }
+        c_out = k; h_out = 1; w_out = 1;
+        if (initializeFullyConnectedFilterAndBias() != 0) return;
+        break;
+    case CONV:
+    case FC_CONV: {
+        vdnn_conv_desc d = convDesc();
+        if (vdnn_conv_out_dims(&d, &h_out, &w_out) != VDNN_OK) { fprintf(stderr, "Invalid convolution!\n"); return; }
+        c_out = k;
+        if (initializeConvolutionFilterAndBias() != 0) return;
+        // algorithm choice + workspace query (layer.cu:256-294)
+        const int mode = vdnnAlgoMode == VDNN_PERF_OPT_ALGO ? VDNN_ALGO_PERF_OPT : VDNN_ALGO_MEMORY_OPT;
+        fwdWorkSpaceSize = vdnn_conv_workspace_bytes(VDNN_CONV_FWD, mode, &d);
+        bwdDataWorkSpaceSize = vdnn_conv_workspace_bytes(VDNN_CONV_BWD_DATA, mode, &d);
+        bwdFilterWorkSpaceSize = vdnn_conv_workspace_bytes(VDNN_CONV_BWD_FILTER, mode, &d);
+    } break;
+    case POOL:
+        if (vdnn_pool_out_dims(h_in, w_in, r, s, stride_h, stride_w, &h_out, &w_out) != VDNN_OK) {
+            fprintf(stderr, "Invalid pooling window!\n");
+            return;
+        }
+        break;
+    default: break;     // RELU, TANH, SIGMOID, SOFTMAX, LRN keep the input shape
+    }
+
+    if (vdnnMode == BASELINE && cnmemMallocDstData(false) != 0) return;     // layer.cu:94,472
+
+    if (handle->verbose) {
+        printf("----------------------- Layer %d -----------------------\n", layerId);
+        printf("Layer Type: %s\n", type_name(layerType));
+        printf("Input (n, c, h, w): (%d, %d, %d, %d)\n", n_in, c_in, h_in, w_in);
+        printf("Output (n, c, h, w): (%d, %d, %d, %d)\n", n_out, c_out, h_out, w_out);
+        printf("Filter (k, c, r, s): (%d, %d, %d, %d)\n", k, c_in, r, s);
+        printf("Stride: (%d, %d), Padding: (%d, %d)\n", stride_h, stride_w, pad_h, pad_w);
+        if (layerType == FC_CONV || layerType == CONV) {
+            printf("CONV Layer %d fwdWorkSpaceSize: %lu\n", layerId, (unsigned long)fwdWorkSpaceSize);
+            printf("CONV Layer %d bwdDataWorkSpaceSize: %lu\n", layerId, (unsigned long)bwdDataWorkSpaceSize);
+            printf("CONV Layer %d bwdFilterWorkSpaceSize: %lu\n", layerId, (unsigned long)bwdFilterWorkSpaceSize);
+        }
+    }
+    constructed = true;
+}
+
+Layer::~Layer() {}
+
+vdnn_conv_desc Layer::convDesc() const {
+    vdnn_conv_desc d;
+    d.n = n_in; d.c = c_in; d.h = h_in; d.w = w_in; d.k = k; d.r = r; d.s = s;
+    d.pad_h = pad_h; d.pad_w = pad_w; d.stride_h = stride_h; d.stride_w = stride_w;
+    return d;
+}
+
+void Layer::spec(vdnn_layer_spec* out) {
+    out->type = layerType; out->n = n_in; out->c = c_in; out->h = h_in; out->w = w_in;
+    out->pad_h = pad_h; out->pad_w = pad_w; out->stride_h = stride_h; out->stride_w = stride_w;
+    out->k = k; out->r = r; out->s = s;
+}
+
+// layer.cu:925-945 and 947-967 draw from an unseeded mt19937; here the values come from the
+// counter-based generator so that every build of the network starts from the same weights.
+static int init_weights(vdnnContext* ctx, int layerId, size_t filterCount, int biasCount, size_t fan_in,
+                        void** filterData, void** biasData) {
+    if (ctx->alloc(filterData, sizeof(DATATYPE) * filterCount, layerId, TAG_WEIGHT, false, {}) != 0) return -1;
+    if (ctx->alloc(biasData, sizeof(DATATYPE) * biasCount, layerId, TAG_BIAS, false, {}) != 0) return -1;
+    if (ctx->dry_run) return 0;
+    std::vector<DATATYPE> w(filterCount), b(biasCount, 0.0f);
+    const uint64_t seed = ctx->weight_seed_base + static_cast<uint64_t>(layerId);
+    if (ctx->init_mode == 0) {
+        vdnn_host_fill_normal(w.data(), filterCount, seed, 0.0f, sqrtf(2.0f / static_cast<float>(fan_in)));
+    } else {
+        vdnn_host_fill_uniform(w.data(), filterCount, seed, -(float)RANDOM_VALUE_LIMIT, (float)RANDOM_VALUE_LIMIT);
+        vdnn_host_fill_uniform(b.data(), biasCount, seed + 0x100000000ull, -(float)RANDOM_VALUE_LIMIT, (float)RANDOM_VALUE_LIMIT);
+    }
+    if (ctx->upload(*filterData, w.data(), sizeof(DATATYPE) * filterCount) != VDNN_OK) return -1;
+    if (ctx->upload(*biasData, b.data(), sizeof(DATATYPE) * biasCount) != VDNN_OK) return -1;
+    return 0;
+}
+
+int Layer::initializeConvolutionFilterAndBias() {
+    return init_weights(handle, layerId, static_cast<size_t>(FilterDataSize()), c_out,
+                        static_cast<size_t>(c_in) * r * s, &filterData, &biasData);
+}
+
+int Layer::initializeFullyConnectedFilterAndBias() {
+    return init_weights(handle, layerId, static_cast<size_t>(c_in) * c_out, c_out, static_cast<size_t>(c_in),
+                        &filterData, &biasData);
+}
+
+int Layer::enableGradientStaging() {
+    if (!HasWeights() || gradFilter || handle->dry_run) return VDNN_OK;
+    const size_t wn = static_cast<size_t>(FilterDataSize());
+    // One allocation for filter and bias gradients so that a single all-reduce covers both.
+    if (cudaMalloc(reinterpret_cast<void**>(&gradFilter), sizeof(float) * (wn + c_out)) != cudaSuccess) return VDNN_ERR_CUDA;
+    gradBias = gradFilter + wn;
+    return VDNN_OK;
+}
+
+/* ------------------------------------------------------------------ dispatch (layer.cu:489-537) */
+
+int Layer::forward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, void* workSpace, bool isDynamic) {
+    switch (layerType) {
+    case FC_GEMM: return fullyConnectedForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
+    case CONV: case FC_CONV: return convolutionForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
+    case RELU: return activationForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
+    case SOFTMAX: return softmaxForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
+    case POOL: return poolingForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
+    case LRN: return lrnForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
+    default: return VDNN_ERR_UNSUPPORTED;        // TANH, SIGMOID, CONCATENATE: used by no model
+    }
+}
+
+int Layer::backward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, void* _srcDataToPrefetch,
+                    unsigned long _prefetch_bytes, void* workSpace, bool isDynamic) {
+    switch (layerType) {
+    case FC_GEMM: return fullyConnectedBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
+    case CONV: case FC_CONV: return convolutionBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
+    case RELU: return activationBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
+    case SOFTMAX: return softmaxBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
+    case POOL: return poolingBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
+    case LRN: return lrnBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
+    default: return VDNN_ERR_UNSUPPORTED;
+    }
+}
+
+// Common prologue of every forward: dst allocation (layer.cu:553-556 and siblings).
+#define FWD_PROLOGUE()                                                              \
+    if (vdnnMode != BASELINE) { const int _a = cnmemMallocDstData(isDynamic); if (_a != 0) return _a; }
+// Common prologue of every backward: grad allocation, then the prefetch issue (layer.cu:596-603).
+#define BWD_PROLOGUE()                                                              \
+    if (vdnnMode != BASELINE) { const int _a = cnmemMallocGradData(isDynamic); if (_a != 0) return _a; }    \
+    if (vdnnMode != BASELINE && _layer_id_to_prefetch >= 0) {                       \
+        const int _p = prefetchPreviousSrcData(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes); \
+        if (_p != 0) return _p;                                                     \
+    }
+#define MARK(ev) CU(cudaEventRecord(handle->ev[layerId], *stream_compute))
+
+/* ------------------------------------------------------------------ CONV (layer.cu:539-665) */
+
+int Layer::convolutionForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, void* workSpace, bool isDynamic) {
+    void* curWorkSpace = NULL;
+    const int mode = vdnnAlgoMode == VDNN_PERF_OPT_ALGO ? VDNN_ALGO_PERF_OPT : VDNN_ALGO_MEMORY_OPT;
+    if (workSpace != NULL) curWorkSpace = workSpace;
+    else if (fwdWorkSpaceSize > 0) {
+        const int a = handle->alloc(&curWorkSpace, fwdWorkSpaceSize, layerId, TAG_WS, isDynamic, {*stream_compute});
+        if (a != 0) return a;
+    }
+    FWD_PROLOGUE();
+    const vdnn_conv_desc d = convDesc();
+    // convolution and bias in one pass (the reference: cudnnConvolutionForward + cudnnAddTensor)
+    DEV(vdnn_conv_fwd(&d, mode, 1.0f, (const float*)srcData, (const float*)filterData, (const float*)biasData, 0.0f,
+                      (float*)dstData, curWorkSpace, fwdWorkSpaceSize, *stream_compute));
+    if (_offloaded[layerId]) { const int o = offloadSrcData(_offloaded, _offloadedSrcData_h); if (o != 0) return o; }
+    MARK(ev_fwd_done);
+    if (workSpace == NULL && fwdWorkSpaceSize > 0)
+        return handle->release(curWorkSpace, fwdWorkSpaceSize, layerId, TAG_WS, {handle->ev_fwd_done[layerId]});
+    return 0;
+}
+
+int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, void* _srcDataToPrefetch,
+                               unsigned long _prefetch_bytes, void* workSpace, bool isDynamic) {
+    void* curWorkSpace = NULL;
+    const int mode = vdnnAlgoMode == VDNN_PERF_OPT_ALGO ? VDNN_ALGO_PERF_OPT : VDNN_ALGO_MEMORY_OPT;
+    const float lr = handle->learning_rate * -1.0f;
+    const bool staged = gradFilter != NULL;
+    BWD_PROLOGUE();
+    const vdnn_conv_desc d = convDesc();
+
+    if (workSpace != NULL) curWorkSpace = workSpace;
+    else if (bwdDataWorkSpaceSize > 0) {
+        const int a = handle->alloc(&curWorkSpace, bwdDataWorkSpaceSize, layerId, TAG_WS, isDynamic, {*stream_compute});
+        if (a != 0) return a;
+    }
+    // data gradient with the weights as they were in forward
+    DEV(vdnn_conv_bwd_data(&d, mode, 1.0f, (const float*)filterData, (const float*)diffData, 0.0f, (float*)gradData,
+                           curWorkSpace, bwdDataWorkSpaceSize, *stream_compute));
+    if (workSpace == NULL && bwdDataWorkSpaceSize > 0) {
+        MARK(ev_bwd_done);
+        const int f = handle->release(curWorkSpace, bwdDataWorkSpaceSize, layerId, TAG_WS, {handle->ev_bwd_done[layerId]});
+        if (f != 0) return f;
+    }
+    // bias, then filter: gradient folded into the parameters (alpha = -lr, beta = 1), or written to
+    // the staging buffer when gradients are all-reduced across ranks first
+    DEV(vdnn_conv_bwd_bias(n_out, c_out, h_out * w_out, staged ? 1.0f : lr, (const float*)diffData, staged ? 0.0f : 1.0f,
+                           staged ? gradBias : (float*)biasData, *stream_compute));
+    if (workSpace != NULL) curWorkSpace = workSpace;
+    else if (bwdFilterWorkSpaceSize > 0) {
+        const int a = handle->alloc(&curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, isDynamic, {*stream_compute});
+        if (a != 0) return a;
+    }
+    DEV(vdnn_conv_bwd_filter(&d, mode, staged ? 1.0f : lr, (const float*)srcData, (const float*)diffData,
+                             staged ? 0.0f : 1.0f, staged ? gradFilter : (float*)filterData, curWorkSpace,
+                             bwdFilterWorkSpaceSize, *stream_compute));
+    MARK(ev_bwd_done);
+    if (workSpace == NULL && bwdFilterWorkSpaceSize > 0)
+        return handle->release(curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, {handle->ev_bwd_done[layerId]});
+    return 0;
+}
+
+/* ------------------------------------------------------------------ FC_GEMM (layer.cu:667-764) */
+
+int Layer::fullyConnectedForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, void*, bool isDynamic) {
+    FWD_PROLOGUE();
+    DEV(vdnn_sgemm(1, 0, c_out, n_out, c_in, 1.0f, (const float*)filterData, c_in, (const float*)srcData, c_in, 0.0f,
+                   (float*)dstData, c_out, VDNN_ALGO_MEMORY_OPT, NULL, 0, *stream_compute));
+    if (_offloaded[layerId]) { const int o = offloadSrcData(_offloaded, _offloadedSrcData_h); if (o != 0) return o; }
+    // The reference adds the bias with a rank-1 GEMM against a vector of ones that it allocates and
+    // frees around the call (layer.cu:692-706).  The allocation is kept so that the pool trace is the
+    // same; the addition itself is a broadcast kernel.
+    void* oneVec = NULL;
+    const int a = handle->alloc(&oneVec, sizeof(DATATYPE) * n_out, layerId, TAG_ONES, isDynamic, {*stream_compute});
+    if (a != 0) return a;
+    DEV(vdnn_add_bias(n_out, c_out, 1, 1.0f, (const float*)biasData, (float*)dstData, *stream_compute));
+    MARK(ev_fwd_done);
+    return handle->release(oneVec, sizeof(DATATYPE) * n_out, layerId, TAG_ONES, {});
+}
+
+int Layer::fullyConnectedBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, void* _srcDataToPrefetch,
+                                  unsigned long _prefetch_bytes, void*, bool isDynamic) {
+    const float lr = handle->learning_rate * -1.0f;
+    const bool staged = gradFilter != NULL;
+    BWD_PROLOGUE();
+    // gradData = W^T-view * diffData with the pre-update weights (layer.cu:725-733)
+    DEV(vdnn_sgemm(0, 0, c_in, n_out, c_out, 1.0f, (const float*)filterData, c_in, (const float*)diffData, c_out, 0.0f,
+                   (float*)gradData, c_in, VDNN_ALGO_MEMORY_OPT, NULL, 0, *stream_compute));
+    // filterData += -lr * srcData * diffData^T (layer.cu:736-744)
+    DEV(vdnn_sgemm(0, 1, c_in, c_out, n_out, staged ? 1.0f : lr, (const float*)srcData, c_in, (const float*)diffData, c_out,
+                   staged ? 0.0f : 1.0f, staged ? gradFilter : (float*)filterData, c_in, VDNN_ALGO_MEMORY_OPT, NULL, 0,
+                   *stream_compute));
+    void* oneVec = NULL;
+    const int a = handle->alloc(&oneVec, sizeof(DATATYPE) * n_out, layerId, TAG_ONES, isDynamic, {*stream_compute});
+    if (a != 0) return a;
+    // biasData += -lr * diffData * 1 (layer.cu:752-760)
+    DEV(vdnn_conv_bwd_bias(n_out, c_out, 1, staged ? 1.0f : lr, (const float*)diffData, staged ? 0.0f : 1.0f,
+                           staged ? gradBias : (float*)biasData, *stream_compute));
+    MARK(ev_bwd_done);
+    return handle->release(oneVec, sizeof(DATATYPE) * n_out, layerId, TAG_ONES, {});
+}
+
+/* ------------------------------------------------------------------ ReLU (layer.cu:766-814) */
+
+int Layer::activationForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, void*, bool isDynamic) {
+    FWD_PROLOGUE();
+    DEV(vdnn_relu_fwd(static_cast<size_t>(SrcDataSize()), (const float*)srcData, (float*)dstData, *stream_compute));
+    if (_offloaded[layerId]) { const int o = offloadSrcData(_offloaded, _offloadedSrcData_h); if (o != 0) return o; }
+    MARK(ev_fwd_done);
+    return 0;
+}
+
+int Layer::activationBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, void* _srcDataToPrefetch,
+                              unsigned long _prefetch_bytes, void*, bool isDynamic) {
+    BWD_PROLOGUE();
+    DEV(vdnn_relu_bwd(static_cast<size_t>(SrcDataSize()), (const float*)dstData, (const float*)diffData,
+                      (const float*)srcData, (float*)gradData, *stream_compute));
+    MARK(ev_bwd_done);
+    return 0;
+}
+
+/* ------------------------------------------------------------------ softmax (layer.cu:816-865) */
+
+int Layer::softmaxForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, void*, bool isDynamic) {
+    FWD_PROLOGUE();
+    DEV(vdnn_softmax_fwd(n_in, c_in * h_in * w_in, (const float*)srcData, (float*)dstData, *stream_compute));
+    if (_offloaded[layerId]) { const int o = offloadSrcData(_offloaded, _offloadedSrcData_h); if (o != 0) return o; }
+    MARK(ev_fwd_done);
+    return 0;
+}
+
+int Layer::softmaxBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, void* _srcDataToPrefetch,
+                           unsigned long _prefetch_bytes, void*, bool isDynamic) {
+    BWD_PROLOGUE();
+    DEV(vdnn_softmax_bwd(n_in, c_in * h_in * w_in, (const float*)dstData, (const float*)diffData, (float*)gradData,
+                         *stream_compute));
+    MARK(ev_bwd_done);
+    return 0;
+}
+
+/* ------------------------------------------------------------------ max pooling (layer.cu:867-915) */
+
+int Layer::poolingForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, void*, bool isDynamic) {
+    FWD_PROLOGUE();
+    DEV(vdnn_maxpool_fwd(n_in, c_in, h_in, w_in, r, s, stride_h, stride_w, (const float*)srcData, (float*)dstData,
+                         *stream_compute));
+    if (_offloaded[layerId]) { const int o = offloadSrcData(_offloaded, _offloadedSrcData_h); if (o != 0) return o; }
+    MARK(ev_fwd_done);
+    return 0;
+}
+
+int Layer::poolingBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, void* _srcDataToPrefetch,
+                           unsigned long _prefetch_bytes, void*, bool isDynamic) {
+    BWD_PROLOGUE();
+    DEV(vdnn_maxpool_bwd(n_in, c_in, h_in, w_in, r, s, stride_h, stride_w, (const float*)dstData, (const float*)diffData,
+                         (const float*)srcData, (float*)gradData, *stream_compute));
+    MARK(ev_bwd_done);
+    return 0;
+}
+
+/* ------------------------------------------------------------------ LRN (no reference counterpart) */
+
+int Layer::lrnForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, void*, bool isDynamic) {
+    FWD_PROLOGUE();
+    DEV(vdnn_lrn_fwd(n_in, c_in, h_in * w_in, r, 1e-4f, 0.75f, 2.0f, (const float*)srcData, (float*)dstData, *stream_compute));
+    if (_offloaded[layerId]) { const int o = offloadSrcData(_offloaded, _offloadedSrcData_h); if (o != 0) return o; }
+    MARK(ev_fwd_done);
+    return 0;
+}
+
+int Layer::lrnBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, void* _srcDataToPrefetch,
+                       unsigned long _prefetch_bytes, void*, bool isDynamic) {
+    BWD_PROLOGUE();
+    DEV(vdnn_lrn_bwd(n_in, c_in, h_in * w_in, r, 1e-4f, 0.75f, 2.0f, (const float*)srcData, (const float*)dstData,
+                     (const float*)diffData, (float*)gradData, *stream_compute));
+    MARK(ev_bwd_done);
+    return 0;
+}
+
+/* ------------------------------------------------------------------ offload / prefetch (layer.cu:969-987) */
+
+// srcData of this layer was produced on the compute stream by the layer below (or by the input
+// upload); the copy stream waits for that, not for this layer's own kernels, so the transfer runs
+// under them.
+int Layer::offloadSrcData(bool* _offloaded, DATATYPE** _offloadedSrcData_h) {
+    (void)_offloaded;
+    const size_t bytes = static_cast<size_t>(SrcDataSize()) * sizeof(DATATYPE);
+    handle->record(2, layerId, TAG_SRC, static_cast<int64_t>(bytes));
+    handle->offload_bytes += static_cast<int64_t>(bytes);
+    if (handle->dry_run) return 0;
+    cudaEvent_t ready = layerId == 0 ? handle->ev_input_ready : handle->ev_fwd_done[layerId - 1];
+    if (handle->profiling) {
+        CU(cudaStreamWaitEvent(*stream_memory, ready, 0));
+        CU(cudaEventRecord(handle->pf_off_beg[layerId], *stream_memory));
+        ready = NULL;
+    }
+    DEV(vdnn_offload(_offloadedSrcData_h[layerId], srcData, bytes, ready, NULL, *stream_memory));
+    if (handle->profiling) CU(cudaEventRecord(handle->pf_off_end[layerId], *stream_memory));
+    CU(cudaEventRecord(handle->ev_offload_done[layerId], *stream_memory));
+    return 0;
+}
+
+// The host copy was written by the offload stream in forward; the prefetch stream waits for it.
+int Layer::prefetchPreviousSrcData(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h,
+                                   void* _srcDataToPrefetch, unsigned long _prefetch_bytes) {
+    handle->record(3, _layer_id_to_prefetch, TAG_SRC, static_cast<int64_t>(_prefetch_bytes));
+    handle->prefetch_bytes += static_cast<int64_t>(_prefetch_bytes);
+    if (handle->dry_run) return 0;
+    cudaEvent_t ready = handle->ev_offload_done[_layer_id_to_prefetch];
+    if (handle->profiling) {
+        CU(cudaStreamWaitEvent(handle->stream_h2d, ready, 0));
+        CU(cudaEventRecord(handle->pf_pre_beg[_layer_id_to_prefetch], handle->stream_h2d));
+        ready = NULL;
+    }
+    DEV(vdnn_prefetch(_srcDataToPrefetch, _prefetchedSrcData_h, _prefetch_bytes, ready, NULL, handle->stream_h2d));
+    if (handle->profiling) CU(cudaEventRecord(handle->pf_pre_end[_layer_id_to_prefetch], handle->stream_h2d));
+    CU(cudaEventRecord(handle->ev_prefetch_done[_layer_id_to_prefetch], handle->stream_h2d));
+    return 0;
+}
+
+/* ------------------------------------------------------------------ per-tensor allocation (layer.cu:989-1011) */
+
+int Layer::cnmemMallocSrcData(bool isDynamic) {
+    // target of a prefetch: first written by the H2D stream
+    return handle->alloc(&srcData, sizeof(DATATYPE) * SrcDataSize(), layerId, TAG_SRC, isDynamic, {handle->stream_h2d});
+}
+int Layer::cnmemMallocDstData(bool isDynamic) {
+    return handle->alloc(&dstData, sizeof(DATATYPE) * DstDataSize(), layerId, TAG_DST, isDynamic, {*stream_compute});
+}
+int Layer::cnmemMallocDiffData(bool isDynamic) {
+    return handle->alloc(&diffData, sizeof(DATATYPE) * SrcDataSize(), layerId, TAG_DIFF, isDynamic, {*stream_compute});
+}
+int Layer::cnmemMallocGradData(bool isDynamic) {
+    return handle->alloc(&gradData, sizeof(DATATYPE) * SrcDataSize(), layerId, TAG_GRAD, isDynamic, {*stream_compute});
+}
+
+/* ------------------------------------------------------------------ debugging (layer.cu:1149-1185) */
+
+static void print_head(const char* what, int id, const void* dev, size_t count) {
+    const size_t n = count < 16 ? count : 16;
+    float host[16];
+    if (!dev || cudaMemcpy(host, dev, n * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess) return;
+    printf("%s of layer %d:", what, id);
+    for (size_t i = 0; i < n; ++i) printf(" %g", host[i]);
+    printf("%s\n", count > n ? " ..." : "");
+}
+
+void Layer::printDstData() { if (!handle->dry_run) print_head("dstData", layerId, dstData, DstDataSize()); }
+void Layer::printFilterData() { if (!handle->dry_run && HasWeights()) print_head("filterData", layerId, filterData, FilterDataSize()); }

@@ -1,0 +1,78 @@
+// extern "C" face of class Network for hosts that are not C++ (section 4 of vdnn_b200.h).
+#include <new>
+
+#include "dp_nccl.h"
+#include "network.h"
+
+struct vdnn_network { Network* impl; };
+
+#define NET(n) do { if (!(n) || !(n)->impl) return VDNN_ERR_BAD_ARG; } while (0)
+
+extern "C" {
+
+// dry_run is requested by setting device to -1: the schedule is replayed against a bookkeeping-only
+// pool and no CUDA call is made.
+int vdnn_network_create(vdnn_network** out, const vdnn_network_config* cfg) {
+    if (!out || !cfg) return VDNN_ERR_BAD_ARG;
+    *out = nullptr;
+    vdnn_network_config c = *cfg;
+    const bool dry = c.device < 0;
+    Network* n = new (std::nothrow) Network(c, dry);
+    if (!n) return VDNN_ERR_OUT_OF_MEMORY;
+    if (n->status() != VDNN_OK) { const int st = n->status(); delete n; return st; }
+    vdnn_network* h = new (std::nothrow) vdnn_network;
+    if (!h) { delete n; return VDNN_ERR_OUT_OF_MEMORY; }
+    h->impl = n;
+    *out = h;
+    return VDNN_OK;
+}
+
+int vdnn_network_destroy(vdnn_network* net) {
+    if (!net) return VDNN_OK;
+    delete net->impl;
+    delete net;
+    return VDNN_OK;
+}
+
+int vdnn_network_num_layers(const vdnn_network* net) { return (net && net->impl) ? net->impl->numLayers_() : 0; }
+
+int vdnn_network_layer_spec(const vdnn_network* net, int layer, vdnn_layer_spec* out) {
+    NET(net);
+    if (!out || layer < 0 || layer >= net->impl->numLayers_()) return VDNN_ERR_BAD_ARG;
+    net->impl->layerArray()[layer]->spec(out);
+    return VDNN_OK;
+}
+
+size_t vdnn_network_input_size(const vdnn_network* net) { return (net && net->impl) ? net->impl->getInputSize() : 0; }
+size_t vdnn_network_output_size(const vdnn_network* net) { return (net && net->impl) ? net->impl->getOutputSize() : 0; }
+
+int vdnn_network_set_input(vdnn_network* net, const float* input_h, const float* label_h) { NET(net); return net->impl->setInput(input_h, label_h); }
+int vdnn_network_seed_input(vdnn_network* net, uint64_t a, uint64_t b) { NET(net); return net->impl->seedInput(a, b); }
+int vdnn_network_forward(vdnn_network* net) { NET(net); return net->impl->forwardPropagation(false); }
+int vdnn_network_backward(vdnn_network* net) { NET(net); return net->impl->backwardPropagation(false); }
+int vdnn_network_synchronize(vdnn_network* net) { NET(net); return net->impl->synchronize(); }
+int vdnn_network_loss(vdnn_network* net, double* out2) { NET(net); return net->impl->loss(out2); }
+
+size_t vdnn_network_tensor_size(const vdnn_network* net, int layer, int kind) {
+    return (net && net->impl) ? net->impl->tensorSize(layer, kind) : 0;
+}
+int vdnn_network_read_tensor(vdnn_network* net, int layer, int kind, float* dst_h, size_t count) { NET(net); return net->impl->readTensor(layer, kind, dst_h, count); }
+int vdnn_network_write_tensor(vdnn_network* net, int layer, int kind, const float* src_h, size_t count) { NET(net); return net->impl->writeTensor(layer, kind, src_h, count); }
+
+int vdnn_network_trace(vdnn_network* net, vdnn_trace_event* out, int max_events, int* num_events) {
+    NET(net);
+    const std::vector<vdnn_trace_event>& t = net->impl->context().trace;
+    if (num_events) *num_events = static_cast<int>(t.size());
+    if (out) for (int i = 0; i < max_events && i < static_cast<int>(t.size()); ++i) out[i] = t[i];
+    return VDNN_OK;
+}
+int vdnn_network_trace_reset(vdnn_network* net) { NET(net); net->impl->context().trace.clear(); return VDNN_OK; }
+
+int vdnn_network_get_stats(vdnn_network* net, vdnn_network_stats* out) { NET(net); return net->impl->getStats(out); }
+int vdnn_network_set_profiling(vdnn_network* net, int enabled) { NET(net); return net->impl->setProfiling(enabled != 0); }
+
+int vdnn_dp_unique_id(char* out128) { return vdnn::dp_unique_id(out128); }
+int vdnn_network_enable_dp(vdnn_network* net, int rank, int world, const char* id) { NET(net); return net->impl->enableDataParallel(rank, world, id); }
+int vdnn_network_weight_checksum(vdnn_network* net, uint64_t* out) { NET(net); return net->impl->weightChecksum(out); }
+
+}  // extern "C"

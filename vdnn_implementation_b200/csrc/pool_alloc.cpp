@@ -1,0 +1,239 @@
+// Pool sub-allocator behind the cnmem-compatible interface (include/cnmem/include/cnmem.h).
+// One root pool per process, reserved with a single cudaMalloc; blocks are kept in an
+// address-ordered map, allocation is best-fit, neighbours coalesce on free.
+#include "cnmem/include/cnmem.h"
+
+#include <cstdint>
+#include <cstdio>
+#include <cstdlib>
+#include <map>
+#include <mutex>
+#include <vector>
+
+namespace {
+
+constexpr size_t kGranularity = 512;   // cnmem rounds every request up to 512 bytes
+
+struct Block { size_t size; bool free; };
+struct Fence { size_t begin, end; cudaEvent_t event; };
+
+struct Pool {
+    std::mutex mu;
+    bool ready = false;
+    bool is_virtual = false;
+    int device = 0;
+    char* base = nullptr;
+    size_t capacity = 0, used = 0, peak = 0;
+    std::map<size_t, Block> blocks;     // offset -> block
+    std::vector<Fence> fences;
+    int fail_countdown = 0;
+};
+Pool g_pool;
+
+size_t round_up(size_t n) { return (n + kGranularity - 1) / kGranularity * kGranularity; }
+
+cnmemStatus_t alloc_locked(void** ptr, size_t size, size_t* off_out, size_t* len_out) {
+    if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
+    if (!ptr) return CNMEM_STATUS_INVALID_ARGUMENT;
+    if (size == 0) { *ptr = nullptr; return CNMEM_STATUS_SUCCESS; }
+    if (g_pool.fail_countdown > 0 && --g_pool.fail_countdown == 0) return CNMEM_STATUS_OUT_OF_MEMORY;
+    const size_t need = round_up(size);
+    auto best = g_pool.blocks.end();
+    for (auto it = g_pool.blocks.begin(); it != g_pool.blocks.end(); ++it)
+        if (it->second.free && it->second.size >= need &&
+            (best == g_pool.blocks.end() || it->second.size < best->second.size))
+            best = it;
+    if (best == g_pool.blocks.end()) return CNMEM_STATUS_OUT_OF_MEMORY;
+    const size_t off = best->first, rest = best->second.size - need;
+    best->second.size = need;
+    best->second.free = false;
+    if (rest) g_pool.blocks[off + need] = Block{rest, true};
+    g_pool.used += need;
+    if (g_pool.used > g_pool.peak) g_pool.peak = g_pool.used;
+    *ptr = g_pool.base + off;
+    if (off_out) { *off_out = off; *len_out = need; }
+    return CNMEM_STATUS_SUCCESS;
+}
+
+cnmemStatus_t free_locked(void* ptr, size_t* off_out, size_t* len_out) {
+    if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
+    if (!ptr) return CNMEM_STATUS_SUCCESS;
+    const size_t off = static_cast<char*>(ptr) - g_pool.base;
+    auto it = g_pool.blocks.find(off);
+    if (it == g_pool.blocks.end() || it->second.free) return CNMEM_STATUS_INVALID_ARGUMENT;
+    if (off_out) { *off_out = off; *len_out = it->second.size; }
+    g_pool.used -= it->second.size;
+    it->second.free = true;
+    auto next = std::next(it);
+    if (next != g_pool.blocks.end() && next->second.free) {
+        it->second.size += next->second.size;
+        g_pool.blocks.erase(next);
+    }
+    if (it != g_pool.blocks.begin()) {
+        auto prev = std::prev(it);
+        if (prev->second.free) {
+            prev->second.size += it->second.size;
+            g_pool.blocks.erase(it);
+        }
+    }
+    return CNMEM_STATUS_SUCCESS;
+}
+
+void drop_finished_fences_locked() {
+    size_t keep = 0;
+    for (size_t i = 0; i < g_pool.fences.size(); ++i)
+        if (cudaEventQuery(g_pool.fences[i].event) == cudaErrorNotReady)
+            g_pool.fences[keep++] = g_pool.fences[i];
+    (void)cudaGetLastError();           // cudaErrorNotReady is sticky-free but clear it anyway
+    g_pool.fences.resize(keep);
+}
+
+}  // namespace
+
+extern "C" {
+
+cnmemStatus_t cnmemInit(int numDevices, const cnmemDevice_t* devices, unsigned) {
+    if (numDevices != 1 || !devices) return CNMEM_STATUS_INVALID_ARGUMENT;
+    std::lock_guard<std::mutex> lock(g_pool.mu);
+    if (g_pool.ready) return CNMEM_STATUS_INVALID_ARGUMENT;
+    size_t size = devices[0].size;
+    if (const char* cap = std::getenv("VDNN_POOL_BYTES")) {
+        const size_t limit = std::strtoull(cap, nullptr, 10);
+        if (limit && limit < size) size = limit;
+    }
+    size = size / kGranularity * kGranularity;
+    if (size == 0) return CNMEM_STATUS_INVALID_ARGUMENT;
+    if (cudaSetDevice(devices[0].device) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
+    void* p = nullptr;
+    if (cudaMalloc(&p, size) != cudaSuccess) { (void)cudaGetLastError(); return CNMEM_STATUS_OUT_OF_MEMORY; }
+    g_pool.base = static_cast<char*>(p);
+    g_pool.is_virtual = false;
+    g_pool.device = devices[0].device;
+    g_pool.capacity = size;
+    g_pool.used = g_pool.peak = 0;
+    g_pool.blocks.clear();
+    g_pool.blocks[0] = Block{size, true};
+    g_pool.fences.clear();
+    g_pool.fail_countdown = 0;
+    g_pool.ready = true;
+    return CNMEM_STATUS_SUCCESS;
+}
+
+cnmemStatus_t cnmemFinalize(void) {
+    std::lock_guard<std::mutex> lock(g_pool.mu);
+    if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
+    cudaError_t e = g_pool.is_virtual ? cudaSuccess : cudaFree(g_pool.base);
+    g_pool.base = nullptr;
+    g_pool.blocks.clear();
+    g_pool.fences.clear();
+    g_pool.capacity = g_pool.used = 0;
+    g_pool.ready = false;
+    return e == cudaSuccess ? CNMEM_STATUS_SUCCESS : CNMEM_STATUS_CUDA_ERROR;
+}
+
+cnmemStatus_t cnmemMalloc(void** ptr, size_t size, cudaStream_t) {
+    std::lock_guard<std::mutex> lock(g_pool.mu);
+    return alloc_locked(ptr, size, nullptr, nullptr);
+}
+
+cnmemStatus_t cnmemFree(void* ptr, cudaStream_t) {
+    std::lock_guard<std::mutex> lock(g_pool.mu);
+    return free_locked(ptr, nullptr, nullptr);
+}
+
+cnmemStatus_t cnmemMemGetInfo(size_t* freeMem, size_t* totalMem, cudaStream_t) {
+    std::lock_guard<std::mutex> lock(g_pool.mu);
+    if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
+    if (!freeMem || !totalMem) return CNMEM_STATUS_INVALID_ARGUMENT;
+    *totalMem = g_pool.capacity;
+    *freeMem = g_pool.capacity - g_pool.used;
+    return CNMEM_STATUS_SUCCESS;
+}
+
+cnmemStatus_t cnmemPrintMemoryState(FILE* file, cudaStream_t) {
+    std::lock_guard<std::mutex> lock(g_pool.mu);
+    if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
+    if (!file) return CNMEM_STATUS_INVALID_ARGUMENT;
+    std::fprintf(file, "pool device=%d capacity=%zu used=%zu peak=%zu blocks=%zu\n", g_pool.device,
+                 g_pool.capacity, g_pool.used, g_pool.peak, g_pool.blocks.size());
+    for (const auto& kv : g_pool.blocks)
+        std::fprintf(file, "  [%12zu, %12zu) %s\n", kv.first, kv.first + kv.second.size,
+                     kv.second.free ? "free" : "used");
+    return CNMEM_STATUS_SUCCESS;
+}
+
+cnmemStatus_t cnmemRegisterStream(cudaStream_t) { return CNMEM_STATUS_SUCCESS; }
+
+const char* cnmemGetErrorString(cnmemStatus_t status) {
+    switch (status) {
+    case CNMEM_STATUS_SUCCESS: return "CNMEM_STATUS_SUCCESS";
+    case CNMEM_STATUS_CUDA_ERROR: return "CNMEM_STATUS_CUDA_ERROR";
+    case CNMEM_STATUS_INVALID_ARGUMENT: return "CNMEM_STATUS_INVALID_ARGUMENT";
+    case CNMEM_STATUS_NOT_INITIALIZED: return "CNMEM_STATUS_NOT_INITIALIZED";
+    case CNMEM_STATUS_OUT_OF_MEMORY: return "CNMEM_STATUS_OUT_OF_MEMORY";
+    default: return "CNMEM_STATUS_UNKNOWN_ERROR";
+    }
+}
+
+cnmemStatus_t vdnnPoolFreeAfter(void* ptr, const cudaEvent_t* events, int numEvents) {
+    std::lock_guard<std::mutex> lock(g_pool.mu);
+    size_t off = 0, len = 0;
+    cnmemStatus_t st = free_locked(ptr, &off, &len);
+    if (st != CNMEM_STATUS_SUCCESS || !ptr) return st;
+    for (int i = 0; i < numEvents && !g_pool.is_virtual; ++i)
+        if (events[i]) g_pool.fences.push_back(Fence{off, off + len, events[i]});
+    return CNMEM_STATUS_SUCCESS;
+}
+
+cnmemStatus_t vdnnPoolMallocFor(void** ptr, size_t size, const cudaStream_t* streams, int numStreams) {
+    std::lock_guard<std::mutex> lock(g_pool.mu);
+    size_t off = 0, len = 0;
+    cnmemStatus_t st = alloc_locked(ptr, size, &off, &len);
+    if (st != CNMEM_STATUS_SUCCESS || size == 0) return st;
+    if (g_pool.is_virtual) return CNMEM_STATUS_SUCCESS;
+    drop_finished_fences_locked();
+    for (const Fence& f : g_pool.fences)
+        if (f.begin < off + len && off < f.end)
+            for (int s = 0; s < numStreams; ++s)
+                if (cudaStreamWaitEvent(streams[s], f.event, 0) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
+    return CNMEM_STATUS_SUCCESS;
+}
+
+cnmemStatus_t vdnnPoolHighWater(size_t* peakBytes, int reset) {
+    std::lock_guard<std::mutex> lock(g_pool.mu);
+    if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
+    if (peakBytes) *peakBytes = g_pool.peak;
+    if (reset) g_pool.peak = g_pool.used;
+    return CNMEM_STATUS_SUCCESS;
+}
+
+cnmemStatus_t vdnnPoolFailAfter(int k) {
+    std::lock_guard<std::mutex> lock(g_pool.mu);
+    g_pool.fail_countdown = k > 0 ? k : 0;
+    return CNMEM_STATUS_SUCCESS;
+}
+
+cnmemStatus_t vdnnPoolInitVirtual(size_t size) {
+    std::lock_guard<std::mutex> lock(g_pool.mu);
+    if (g_pool.ready) return CNMEM_STATUS_INVALID_ARGUMENT;
+    size = size / kGranularity * kGranularity;
+    if (size == 0) return CNMEM_STATUS_INVALID_ARGUMENT;
+    g_pool.base = reinterpret_cast<char*>(static_cast<uintptr_t>(1) << 40);
+    g_pool.is_virtual = true;
+    g_pool.device = -1;
+    g_pool.capacity = size;
+    g_pool.used = g_pool.peak = 0;
+    g_pool.blocks.clear();
+    g_pool.blocks[0] = Block{size, true};
+    g_pool.fences.clear();
+    g_pool.fail_countdown = 0;
+    g_pool.ready = true;
+    return CNMEM_STATUS_SUCCESS;
+}
+
+int vdnnPoolIsInitialized(void) {
+    std::lock_guard<std::mutex> lock(g_pool.mu);
+    return g_pool.ready ? 1 : 0;
+}
+
+}  // extern "C"

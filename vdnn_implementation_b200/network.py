@@ -1,0 +1,158 @@
+"""Python mirror of the driver's Network class (reference network.h:15-95) over the C ABI."""
+import ctypes as C
+
+import numpy as np
+
+from . import abi
+from .abi import check, lib
+
+
+class Network:
+    """Builds one of the reference topologies (or a custom layer list) under a vDNN policy.
+
+    forwardPropagation / backwardPropagation keep the reference's names.  `device=-1` makes a
+    dry-run network: the allocation / offload / prefetch schedule is replayed against a
+    bookkeeping-only pool and nothing touches a GPU.
+    """
+
+    def __init__(self, cnn_type, vdnn_type, algo_mode, batch_size=0, device=0, pool_bytes=0, learning_rate=0.0,
+                 init_mode=0, weight_seed_base=3000, fix_input_leak=True, host_sync_per_layer=False,
+                 verbose=False, capture=False, custom_layers=None):
+        cnn_type = abi.CNN_NAMES.get(cnn_type, cnn_type)
+        vdnn_type = abi.VDNN_NAMES.get(vdnn_type, vdnn_type)
+        algo_mode = abi.ALGO_NAMES.get(algo_mode, algo_mode)
+        cfg = abi.NetworkConfig()
+        cfg.cnn_type, cfg.vdnn_type, cfg.algo_mode, cfg.batch_size = cnn_type, vdnn_type, algo_mode, batch_size
+        cfg.device, cfg.pool_bytes, cfg.learning_rate = device, int(pool_bytes), learning_rate
+        cfg.init_mode, cfg.weight_seed_base = init_mode, weight_seed_base
+        cfg.fix_input_leak, cfg.host_sync_per_layer = int(fix_input_leak), int(host_sync_per_layer)
+        cfg.verbose, cfg.capture = int(verbose), int(capture)
+        self._custom = None
+        if custom_layers is not None:
+            self._custom = (abi.LayerSpec * len(custom_layers))()
+            for i, s in enumerate(custom_layers):
+                self._custom[i] = s if isinstance(s, abi.LayerSpec) else abi.LayerSpec(*s)
+            cfg.custom_layers = self._custom
+            cfg.num_custom_layers = len(custom_layers)
+        self._h = C.c_void_p()
+        check(lib().vdnn_network_create(C.byref(self._h), C.byref(cfg)), "vdnn_network_create")
+        self.num_layers = lib().vdnn_network_num_layers(self._h)
+        self.input_size = lib().vdnn_network_input_size(self._h)
+        self.output_size = lib().vdnn_network_output_size(self._h)
+        self.dry_run = device < 0
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().vdnn_network_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def layer_spec(self, layer):
+        s = abi.LayerSpec()
+        check(lib().vdnn_network_layer_spec(self._h, layer, C.byref(s)), "layer_spec")
+        return s
+
+    def layer_specs(self):
+        return [self.layer_spec(i) for i in range(self.num_layers)]
+
+    def set_input(self, input_h, label_h):
+        """input_h / label_h: contiguous float32 host arrays (numpy, or pinned torch CPU tensors)."""
+        pi, pl = _host_ptr(input_h, self.input_size), _host_ptr(label_h, self.output_size)
+        check(lib().vdnn_network_set_input(self._h, pi, pl), "set_input")
+
+    def seed_input(self, input_seed, label_seed):
+        check(lib().vdnn_network_seed_input(self._h, input_seed, label_seed), "seed_input")
+
+    def forwardPropagation(self):
+        check(lib().vdnn_network_forward(self._h), "forwardPropagation")
+
+    def backwardPropagation(self):
+        check(lib().vdnn_network_backward(self._h), "backwardPropagation")
+
+    def step(self):
+        self.forwardPropagation()
+        self.backwardPropagation()
+
+    def synchronize(self):
+        check(lib().vdnn_network_synchronize(self._h), "synchronize")
+
+    def loss(self):
+        out = (C.c_double * 2)()
+        check(lib().vdnn_network_loss(self._h, out), "loss")
+        return out[0], out[1]
+
+    def tensor_size(self, layer, kind):
+        return lib().vdnn_network_tensor_size(self._h, layer, kind)
+
+    def read_tensor(self, layer, kind):
+        n = self.tensor_size(layer, kind)
+        if n == 0:
+            return None
+        out = np.empty(n, np.float32)
+        check(lib().vdnn_network_read_tensor(self._h, layer, kind, out.ctypes.data_as(C.c_void_p), n), "read_tensor")
+        return out
+
+    def write_tensor(self, layer, kind, values):
+        v = np.ascontiguousarray(values, np.float32).ravel()
+        check(lib().vdnn_network_write_tensor(self._h, layer, kind, v.ctypes.data_as(C.c_void_p), v.size), "write_tensor")
+
+    def dst(self, layer):
+        return self.read_tensor(layer, abi.TENSOR_DST)
+
+    def grad(self, layer):
+        return self.read_tensor(layer, abi.TENSOR_GRAD)
+
+    def weights(self, layer):
+        return self.read_tensor(layer, abi.TENSOR_WEIGHT)
+
+    def bias(self, layer):
+        return self.read_tensor(layer, abi.TENSOR_BIAS)
+
+    def trace(self):
+        n = C.c_int()
+        check(lib().vdnn_network_trace(self._h, None, 0, C.byref(n)), "trace")
+        buf = (abi.TraceEvent * max(n.value, 1))()
+        check(lib().vdnn_network_trace(self._h, buf, n.value, C.byref(n)), "trace")
+        return [(e.kind, e.layer, e.tag, e.bytes, e.used) for e in buf[:n.value]]
+
+    def trace_reset(self):
+        check(lib().vdnn_network_trace_reset(self._h), "trace_reset")
+
+    def set_profiling(self, enabled=True):
+        check(lib().vdnn_network_set_profiling(self._h, int(enabled)), "set_profiling")
+
+    def stats(self):
+        s = abi.NetworkStats()
+        check(lib().vdnn_network_get_stats(self._h, C.byref(s)), "get_stats")
+        return s.asdict()
+
+    def enable_dp(self, rank, world_size, unique_id):
+        check(lib().vdnn_network_enable_dp(self._h, rank, world_size, unique_id), "enable_dp")
+
+    def weight_checksum(self):
+        out = C.c_uint64()
+        check(lib().vdnn_network_weight_checksum(self._h, C.byref(out)), "weight_checksum")
+        return out.value
+
+
+def dp_unique_id():
+    buf = C.create_string_buffer(128)
+    check(lib().vdnn_dp_unique_id(buf), "dp_unique_id")
+    return buf.raw
+
+
+def _host_ptr(a, expect):
+    if isinstance(a, np.ndarray):
+        assert a.dtype == np.float32 and a.flags["C_CONTIGUOUS"] and a.size == expect
+        return a.ctypes.data_as(C.c_void_p)
+    # torch CPU tensor (possibly pinned)
+    assert a.device.type == "cpu" and a.is_contiguous() and a.numel() == expect and a.element_size() == 4
+    return C.c_void_p(a.data_ptr())
