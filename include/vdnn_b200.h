@@ -208,6 +208,14 @@ int vdnn_network_seed_input(vdnn_network* net, uint64_t input_seed, uint64_t lab
 int vdnn_network_forward(vdnn_network* net);    /* Network::forwardPropagation,  network.cu:1056-1110 */
 int vdnn_network_backward(vdnn_network* net);   /* Network::backwardPropagation, network.cu:1112-1191 */
 int vdnn_network_synchronize(vdnn_network* net);
+/* The streams the network enqueues on (cudaStream_t as void*): 0 compute, 1 offload (D2H), 2 prefetch
+ * (H2D), 3 collectives.  The reference keeps its two streams private (network.h:67-68). */
+void* vdnn_network_stream(vdnn_network* net, int which);
+/* Makes the compute stream wait, on the device, for everything enqueued so far on the other three
+ * streams; an event recorded on the compute stream afterwards marks the end of all the work. */
+int vdnn_network_join(vdnn_network* net);
+/* Number of kernels this library has launched in this process (all entry points). */
+unsigned long long vdnn_kernel_launch_count(void);
 /* Blocks until the loss of the last forward pass is on the host; out2 as in vdnn_loss. */
 int vdnn_network_loss(vdnn_network* net, double* out2);
 
@@ -242,6 +250,11 @@ typedef struct {
     float prefetch_ms;            /* sum of H2D copy durations                                   */
     float copy_overlap_ms;        /* part of the copy time that ran under compute kernels        */
     int kernel_launches;          /* launches of this library's kernels in the last step         */
+    float contraction_ms;         /* compute-stream time spent in CONV / FC layers (forward + backward) */
+    float elementwise_ms;         /* ... in ReLU / pool / LRN / softmax layers                    */
+    double contraction_flops;     /* algorithmic FLOPs of those CONV / FC layers: 2*M*N*K each for forward,
+                                     data gradient and filter gradient                             */
+    double elementwise_bytes;     /* algorithmic bytes of the bandwidth-bound layers, forward + backward */
 } vdnn_network_stats;
 /* Fills timing fields only if profiling events were enabled with vdnn_network_set_profiling. */
 int vdnn_network_get_stats(vdnn_network* net, vdnn_network_stats* out);

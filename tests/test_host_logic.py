@@ -1,0 +1,178 @@
+"""Host-side logic of the product library, exercised without a GPU: exported symbols, the pool
+allocator, the host generators, and the Network's allocation / offload / prefetch schedule
+(dry-run networks against the oracle's schedule simulator)."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol(vdnn):
+    header = open(os.path.join(ROOT, "include", "vdnn_b200.h")).read()
+    declared = set(re.findall(r"\b(vdnn_[a-z0-9_]+)\s*\(", header))
+    declared -= {"vdnn_status", "vdnn_network"}        # type names followed by '(' never occur, but be safe
+    assert len(declared) >= 50
+    L = C.CDLL(vdnn.lib_path())
+    missing = [n for n in sorted(declared) if not hasattr(L, n)]
+    assert not missing, missing
+    from vdnn_implementation_b200 import abi
+    assert declared == set(abi.SIGNATURES), declared ^ set(abi.SIGNATURES)
+    pool_header = open(os.path.join(ROOT, "include", "cnmem", "include", "cnmem.h")).read()
+    for name in set(re.findall(r"\b((?:cnmem|vdnnPool)[A-Za-z]+)\s*\(", pool_header)):
+        assert hasattr(L, name), name
+
+
+def test_status_strings_and_bad_arguments(vdnn):
+    L = vdnn.lib()
+    assert L.vdnn_status_string(0) == b"VDNN_OK"
+    assert L.vdnn_status_string(-3) == b"VDNN_ERR_WORKSPACE"
+    assert b"sm_100a" in L.vdnn_build_info()
+    # argument validation happens before any CUDA call
+    assert L.vdnn_relu_fwd(16, None, None, None) == -1
+    d = vdnn.ConvDesc(1, 1, 2, 2, 1, 3, 3, 0, 0, 1, 1)          # filter larger than the padded input
+    p, q = C.c_int(), C.c_int()
+    assert L.vdnn_conv_out_dims(C.byref(d), C.byref(p), C.byref(q)) == -1
+    d = vdnn.ConvDesc(128, 3, 227, 227, 96, 11, 11, 0, 0, 4, 4)
+    assert L.vdnn_conv_out_dims(C.byref(d), C.byref(p), C.byref(q)) == 0 and (p.value, q.value) == (55, 55)
+    assert L.vdnn_pool_out_dims(55, 55, 3, 3, 2, 2, C.byref(p), C.byref(q)) == 0 and (p.value, q.value) == (27, 27)
+    assert L.vdnn_conv_workspace_bytes(0, 0, C.byref(d)) == 0     # MEMORY_OPT never needs workspace
+    assert L.vdnn_set_engine(7) == -1
+
+
+def test_host_generators_match_oracle_bit_for_bit(vdnn, oracle):
+    L = vdnn.lib()
+    n = 100003
+    a = np.empty(n, np.float32)
+    L.vdnn_host_fill_normal(a.ctypes.data_as(C.c_void_p), n, 1234, 0.0, 1.0)
+    assert np.array_equal(a, oracle.fill_normal(n, 1234))
+    L.vdnn_host_fill_normal(a.ctypes.data_as(C.c_void_p), n, 3001, 0.0, float(np.sqrt(np.float32(2.0) / np.float32(27))))
+    assert np.array_equal(a, oracle.fill_normal(n, 3001, 0.0, float(np.sqrt(np.float32(2.0) / np.float32(27)))))
+    L.vdnn_host_fill_uniform(a.ctypes.data_as(C.c_void_p), n, 77, -0.01, 0.01)
+    assert np.array_equal(a, oracle.fill_uniform(n, 77, -0.01, 0.01))
+    oh = np.empty((128, 1000), np.float32)
+    L.vdnn_host_fill_onehot(oh.ctypes.data_as(C.c_void_p), 128, 1000, 2000)
+    assert np.array_equal(oh, oracle.fill_onehot(128, 1000, 2000))
+
+
+def test_pool_allocator_bookkeeping(vdnn):
+    L = C.CDLL(vdnn.lib_path())
+    L.vdnnPoolInitVirtual.argtypes = [C.c_size_t]
+    L.cnmemMalloc.argtypes = [C.POINTER(C.c_void_p), C.c_size_t, C.c_void_p]
+    L.cnmemFree.argtypes = [C.c_void_p, C.c_void_p]
+    L.cnmemMemGetInfo.argtypes = [C.POINTER(C.c_size_t), C.POINTER(C.c_size_t), C.c_void_p]
+    L.cnmemGetErrorString.restype = C.c_char_p
+    assert L.cnmemMalloc(C.byref(C.c_void_p()), 16, None) == 3            # NOT_INITIALIZED
+    assert L.vdnnPoolInitVirtual(1 << 20) == 0
+    try:
+        free, total = C.c_size_t(), C.c_size_t()
+
+        def used():
+            L.cnmemMemGetInfo(C.byref(free), C.byref(total), None)
+            return total.value - free.value
+
+        a, b, c = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        assert L.cnmemMalloc(C.byref(a), 1, None) == 0 and used() == 512          # 512-byte granularity
+        assert L.cnmemMalloc(C.byref(b), 513, None) == 0 and used() == 512 + 1024
+        assert L.cnmemMalloc(C.byref(c), 1 << 20, None) == 4                       # OUT_OF_MEMORY
+        assert L.cnmemGetErrorString(4) == b"CNMEM_STATUS_OUT_OF_MEMORY"
+        assert L.cnmemFree(a, None) == 0 and used() == 1024
+        assert L.cnmemFree(a, None) == 2                                           # double free rejected
+        # best fit: a 512-byte request goes back into the 512-byte hole, not the big tail
+        d = C.c_void_p()
+        assert L.cnmemMalloc(C.byref(d), 100, None) == 0 and d.value == a.value
+        assert L.cnmemFree(d, None) == 0 and L.cnmemFree(b, None) == 0 and used() == 0
+        # coalescing: the whole pool is one block again
+        assert L.cnmemMalloc(C.byref(c), 1 << 20, None) == 0 and L.cnmemFree(c, None) == 0
+        peak = C.c_size_t()
+        assert L.vdnnPoolHighWater(C.byref(peak), 1) == 0 and peak.value == 1 << 20
+        # host-side fault injection for the soft out-of-memory path
+        assert L.vdnnPoolFailAfter(2) == 0
+        assert L.cnmemMalloc(C.byref(a), 16, None) == 0
+        assert L.cnmemMalloc(C.byref(b), 16, None) == 4
+        assert L.cnmemMalloc(C.byref(b), 16, None) == 0
+    finally:
+        assert L.cnmemFinalize() == 0
+
+
+MODELS = [("ALEXNET", 128), ("ALEXNET_LRN", 128), ("OVERFEAT", 128), ("VGG16_64", 64), ("VGG16_128", 128)]
+
+
+@pytest.mark.parametrize("model,batch", MODELS)
+@pytest.mark.parametrize("policy", [0, 1, 2, 3])
+def test_network_schedule_equals_reference_schedule(vdnn, oracle, model, batch, policy):
+    """Event-for-event: every pool allocation and release, every offload and prefetch, and the pool
+    usage after each of them, over two iterations."""
+    for fix in (True, False):
+        net = vdnn.Network(model, policy, vdnn.VDNN_MEMORY_OPT_ALGO, device=-1, pool_bytes=40e9, fix_input_leak=fix)
+        try:
+            specs = [s.astuple() for s in net.layer_specs()]
+            assert specs == [s.astuple() for s in oracle.model_layers(getattr(oracle, model), batch)]
+            net.step()
+            net.step()
+            ev, summ = oracle.policy_trace(specs, policy, iterations=2, fix_input_leak=fix)
+            assert net.trace() == ev
+            st = net.stats()
+            assert st["pool_peak_bytes"] == summ.peak_bytes
+            assert st["pinned_bytes"] == summ.pinned_bytes
+            assert st["offload_bytes"] * 2 == summ.offload_bytes and st["prefetch_bytes"] * 2 == summ.prefetch_bytes
+        finally:
+            net.close()
+
+
+def test_perf_opt_workspace_enters_the_schedule(vdnn, oracle):
+    net = vdnn.Network("VGG16_64", "VDNN_ALL", "VDNN_PERF_OPT_ALGO", device=-1, pool_bytes=40e9)
+    try:
+        specs = [s.astuple() for s in net.layer_specs()]
+        L = vdnn.lib()
+        ws = []
+        for s in specs:
+            if s[0] in (1, 2):
+                d = vdnn.ConvDesc(s[1], s[2], s[3], s[4], s[9], s[10], s[11], s[5], s[6], s[7], s[8])
+                ws.append([L.vdnn_conv_workspace_bytes(op, 1, C.byref(d)) for op in range(3)])
+            else:
+                ws.append([0, 0, 0])
+        assert any(w[2] > 0 for w in ws)            # filter gradients of the wide layers split along K
+        net.step()
+        ev, summ = oracle.policy_trace(specs, oracle.VDNN_ALL, ws=ws, fix_input_leak=True)
+        assert net.trace() == ev and net.stats()["pool_peak_bytes"] == summ.peak_bytes
+    finally:
+        net.close()
+
+
+def test_pool_too_small_is_reported_not_fatal(vdnn):
+    net = vdnn.Network("VGG16_128", "VDNN_NONE", "VDNN_MEMORY_OPT_ALGO", device=-1, pool_bytes=12e9)
+    try:
+        with pytest.raises(vdnn.VdnnError) as e:
+            net.step()
+        assert e.value.status == -5
+    finally:
+        net.close()        # the pool is per process: one network at a time, as with the reference's cnmem
+    # the same model fits under VDNN_ALL, which is the point of the policy
+    net = vdnn.Network("VGG16_128", "VDNN_ALL", "VDNN_MEMORY_OPT_ALGO", device=-1, pool_bytes=12e9)
+    net.step()
+    net.close()
+
+
+def test_unsupported_modes_are_refused(vdnn):
+    with pytest.raises(vdnn.VdnnError):
+        vdnn.Network("GOOGLENET", "BASELINE", "VDNN_MEMORY_OPT_ALGO", device=-1)
+    with pytest.raises(vdnn.VdnnError):
+        vdnn.Network("ALEXNET", "BASELINE", "VDNN_DYNAMIC_ALGO", device=-1)
+    with pytest.raises(vdnn.VdnnError):
+        vdnn.Network("CUSTOM_CNN", "BASELINE", "VDNN_MEMORY_OPT_ALGO", device=-1)
+
+
+def test_custom_topology_dry_run(vdnn, oracle):
+    from helpers import tiny_net
+    specs = tiny_net(4, with_lrn=True)
+    net = vdnn.Network("CUSTOM_CNN", "VDNN_CONV", "VDNN_MEMORY_OPT_ALGO", device=-1, custom_layers=specs)
+    try:
+        net.step()
+        ev, _ = oracle.policy_trace(specs, oracle.VDNN_CONV, fix_input_leak=True)
+        assert net.trace() == ev
+    finally:
+        net.close()

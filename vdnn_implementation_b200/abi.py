@@ -56,7 +56,8 @@ class NetworkStats(C.Structure):
                 ("pinned_bytes", C.c_int64), ("offload_bytes", C.c_int64), ("prefetch_bytes", C.c_int64),
                 ("workspace_bytes_max", C.c_int64), ("grad_buffer_bytes", C.c_int64), ("step_ms", C.c_float),
                 ("offload_ms", C.c_float), ("prefetch_ms", C.c_float), ("copy_overlap_ms", C.c_float),
-                ("kernel_launches", C.c_int)]
+                ("kernel_launches", C.c_int), ("contraction_ms", C.c_float), ("elementwise_ms", C.c_float),
+                ("contraction_flops", C.c_double), ("elementwise_bytes", C.c_double)]
 
     def asdict(self):
         return {f: getattr(self, f) for f, _ in self._fields_}
@@ -111,6 +112,9 @@ SIGNATURES = {
     "vdnn_network_forward": (_I, [_P]),
     "vdnn_network_backward": (_I, [_P]),
     "vdnn_network_synchronize": (_I, [_P]),
+    "vdnn_network_stream": (_P, [_P, _I]),
+    "vdnn_network_join": (_I, [_P]),
+    "vdnn_kernel_launch_count": (C.c_ulonglong, []),
     "vdnn_network_loss": (_I, [_P, C.POINTER(C.c_double)]),
     "vdnn_network_tensor_size": (_Z, [_P, _I, _I]),
     "vdnn_network_read_tensor": (_I, [_P, _I, _I, _P, _Z]),

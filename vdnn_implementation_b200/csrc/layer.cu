@@ -250,7 +250,7 @@ int Layer::convolutionForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, 
     if (_offloaded[layerId]) { const int o = offloadSrcData(_offloaded, _offloadedSrcData_h); if (o != 0) return o; }
     MARK(ev_fwd_done);
     if (workSpace == NULL && fwdWorkSpaceSize > 0)
-        return handle->release(curWorkSpace, fwdWorkSpaceSize, layerId, TAG_WS, {handle->ev_fwd_done[layerId]});
+        return handle->release(curWorkSpace, fwdWorkSpaceSize, layerId, TAG_WS, {handle->event(handle->ev_fwd_done, layerId)});
     return 0;
 }
 
@@ -273,7 +273,7 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
                            curWorkSpace, bwdDataWorkSpaceSize, *stream_compute));
     if (workSpace == NULL && bwdDataWorkSpaceSize > 0) {
         MARK(ev_bwd_done);
-        const int f = handle->release(curWorkSpace, bwdDataWorkSpaceSize, layerId, TAG_WS, {handle->ev_bwd_done[layerId]});
+        const int f = handle->release(curWorkSpace, bwdDataWorkSpaceSize, layerId, TAG_WS, {handle->event(handle->ev_bwd_done, layerId)});
         if (f != 0) return f;
     }
     // bias, then filter: gradient folded into the parameters (alpha = -lr, beta = 1), or written to
@@ -290,7 +290,7 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
                              bwdFilterWorkSpaceSize, *stream_compute));
     MARK(ev_bwd_done);
     if (workSpace == NULL && bwdFilterWorkSpaceSize > 0)
-        return handle->release(curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, {handle->ev_bwd_done[layerId]});
+        return handle->release(curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, {handle->event(handle->ev_bwd_done, layerId)});
     return 0;
 }
 

@@ -53,6 +53,8 @@ struct vdnnContext {
     int dp_rank = 0, dp_world = 1;
     void* nccl_comm = nullptr;
 
+    // NULL when the context runs without a device (no events exist)
+    static cudaEvent_t event(const std::vector<cudaEvent_t>& v, int id) { return v.empty() ? nullptr : v[id]; }
     void record(int kind, int layer, int tag, int64_t bytes);
     // Pool allocation for use on `streams`; emits a trace event.  Returns 0, -1 (out of memory with
     // isDynamic, as layer.h:119-125) or VDNN_ERR_OUT_OF_MEMORY.

@@ -615,6 +615,17 @@ int Network::synchronize() {
     return VDNN_OK;
 }
 
+// Device-side join: the compute stream waits for the tails of the copy and collective streams.
+int Network::join() {
+    if (ctx.dry_run) return VDNN_OK;
+    cudaStream_t others[3] = {stream_memory, ctx.stream_h2d, ctx.stream_comm};
+    for (cudaStream_t s : others) {
+        NET_CU(cudaEventRecord(ev_step_end, s));
+        NET_CU(cudaStreamWaitEvent(stream_compute, ev_step_end, 0));
+    }
+    return VDNN_OK;
+}
+
 int Network::loss(double* out2) {
     if (!out2) return VDNN_ERR_BAD_ARG;
     if (ctx.dry_run) { out2[0] = out2[1] = 0.0; return VDNN_OK; }
@@ -694,6 +705,21 @@ int Network::getStats(vdnn_network_stats* out) {
     out->kernel_launches = static_cast<int>(launchesLastStep);
     for (int l = 0; l < numLayers; ++l)
         if (layer[l]->GradFilter()) out->grad_buffer_bytes += static_cast<int64_t>(sizeof(float)) * (tensorSize(l, VDNN_TENSOR_WEIGHT) + tensorSize(l, VDNN_TENSOR_BIAS));
+    for (int l = 0; l < numLayers; ++l) {
+        Layer* L = layer[l];
+        const double src = L->SrcDataSize(), dst = L->DstDataSize();
+        switch (L->LayerType()) {
+        case FC_GEMM: case CONV: case FC_CONV:
+            // forward, data gradient and filter gradient are each one M x N x K contraction
+            out->contraction_flops += 3.0 * 2.0 * dst * (static_cast<double>(L->FilterDataSize()) / L->OutputC());
+            break;
+        case RELU: out->elementwise_bytes += 4.0 * (2.0 * src + 3.0 * src); break;      // fwd r+w, bwd x,dy -> dx
+        case POOL: out->elementwise_bytes += 4.0 * ((src + dst) + (2.0 * src + dst)); break;
+        case LRN: out->elementwise_bytes += 4.0 * (2.0 * src + 4.0 * src); break;
+        case SOFTMAX: out->elementwise_bytes += 4.0 * (2.0 * src + 3.0 * src); break;
+        default: break;
+        }
+    }
     if (!ctx.profiling || ctx.dry_run || stepCounter == 0) return VDNN_OK;
     NET_TRY(synchronize());
     // interval lists relative to the step's first event
@@ -704,8 +730,9 @@ int Network::getStats(vdnn_network_stats* out) {
     if (at(ctx.pf_step_end, &t_end)) out->step_ms = t_end;
     for (int l = 0; l < numLayers; ++l) {
         Iv f, b;
-        if (at(ctx.pf_fwd_beg[l], &f.a) && at(ctx.pf_fwd_end[l], &f.b)) compute.push_back(f);
-        if (at(ctx.pf_bwd_beg[l], &b.a) && at(ctx.pf_bwd_end[l], &b.b)) compute.push_back(b);
+        float* bucket = layer[l]->HasWeights() ? &out->contraction_ms : &out->elementwise_ms;
+        if (at(ctx.pf_fwd_beg[l], &f.a) && at(ctx.pf_fwd_end[l], &f.b)) { compute.push_back(f); *bucket += f.b - f.a; }
+        if (at(ctx.pf_bwd_beg[l], &b.a) && at(ctx.pf_bwd_end[l], &b.b)) { compute.push_back(b); *bucket += b.b - b.a; }
         if (isOffload[l]) {
             Iv o, p;
             if (at(ctx.pf_off_beg[l], &o.a) && at(ctx.pf_off_end[l], &o.b)) { copies.push_back(o); out->offload_ms += o.b - o.a; }

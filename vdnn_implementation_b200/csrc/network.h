@@ -52,6 +52,7 @@ public:
     int             setInput(const float* input_h, const float* label_h);
     int             seedInput(uint64_t input_seed, uint64_t label_seed);
     int             synchronize();
+    int             join();
     int             loss(double* out2);
     size_t          tensorSize(int layerId, int kind);
     int             readTensor(int layerId, int kind, float* dst_h, size_t count);

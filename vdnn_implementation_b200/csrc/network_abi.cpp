@@ -4,6 +4,8 @@
 #include "dp_nccl.h"
 #include "network.h"
 
+namespace vdnn { extern unsigned long long g_kernel_launches; }
+
 struct vdnn_network { Network* impl; };
 
 #define NET(n) do { if (!(n) || !(n)->impl) return VDNN_ERR_BAD_ARG; } while (0)
@@ -51,6 +53,19 @@ int vdnn_network_seed_input(vdnn_network* net, uint64_t a, uint64_t b) { NET(net
 int vdnn_network_forward(vdnn_network* net) { NET(net); return net->impl->forwardPropagation(false); }
 int vdnn_network_backward(vdnn_network* net) { NET(net); return net->impl->backwardPropagation(false); }
 int vdnn_network_synchronize(vdnn_network* net) { NET(net); return net->impl->synchronize(); }
+void* vdnn_network_stream(vdnn_network* net, int which) {
+    if (!net || !net->impl) return nullptr;
+    vdnnContext& c = net->impl->context();
+    switch (which) {
+    case 0: return c.stream_compute;
+    case 1: return c.stream_d2h;
+    case 2: return c.stream_h2d;
+    case 3: return c.stream_comm;
+    default: return nullptr;
+    }
+}
+int vdnn_network_join(vdnn_network* net) { NET(net); return net->impl->join(); }
+unsigned long long vdnn_kernel_launch_count(void) { return vdnn::g_kernel_launches; }
 int vdnn_network_loss(vdnn_network* net, double* out2) { NET(net); return net->impl->loss(out2); }
 
 size_t vdnn_network_tensor_size(const vdnn_network* net, int layer, int kind) {

@@ -84,6 +84,13 @@ class Network:
     def synchronize(self):
         check(lib().vdnn_network_synchronize(self._h), "synchronize")
 
+    def stream(self, which=0):
+        """Raw cudaStream_t (int) of the compute (0), offload (1), prefetch (2) or collective (3) stream."""
+        return lib().vdnn_network_stream(self._h, which) or 0
+
+    def join(self):
+        check(lib().vdnn_network_join(self._h), "join")
+
     def loss(self):
         out = (C.c_double * 2)()
         check(lib().vdnn_network_loss(self._h, out), "loss")
