@@ -54,6 +54,10 @@ typedef enum { VDNN_CONV_FWD = 0, VDNN_CONV_BWD_DATA = 1, VDNN_CONV_BWD_FILTER =
 typedef enum { VDNN_ENGINE_AUTO = 0, VDNN_ENGINE_FFMA = 1, VDNN_ENGINE_TCGEN05 = 2 } vdnn_engine;
 int vdnn_set_engine(int engine);   /* process-wide; returns the previous value */
 int vdnn_get_engine(void);
+/* Health of the tensor-core engine.  Its kernels wait on shared-memory barriers with an iteration
+ * limit; a wait that expires records a code (101 producer, 102 MMA issuer, 103 epilogue) instead of
+ * spinning for ever.  Synchronises the device, stores the code (0 = healthy) and clears it. */
+int vdnn_engine_status(int* code);
 
 /* Shape of one convolution: what the reference spreads over srcTensorDesc, filterDesc and
  * convDesc (layer.cu:152-204).  Dilation is 1, mode is cross-correlation (vdnn.h:20). */

@@ -35,11 +35,11 @@ CONV_CASES = [  # n, c, h, w, k, r, pad, stride
     (3, 3, 32, 32, 64, 3, 1, 1),       # first-layer shape (C = 3, K = 27)
     (2, 130, 7, 7, 130, 3, 1, 1),      # ragged tile edges in every dimension
 ]
-ENGINES = ["ffma", "auto"]
+ENGINES = ["ffma", "tcgen05"]
 
 
 def _engine(vdnn, name):
-    vdnn.ops.set_engine({"ffma": vdnn.ENGINE_FFMA, "auto": vdnn.ENGINE_AUTO}[name])
+    vdnn.ops.set_engine({"ffma": vdnn.ENGINE_FFMA, "tcgen05": vdnn.ENGINE_TCGEN05, "auto": vdnn.ENGINE_AUTO}[name])
 
 
 @pytest.mark.parametrize("engine", ENGINES)
@@ -89,6 +89,7 @@ def test_convolution_trio(vdnn, oracle, case, algo, engine):
         bupd = dev(bias)
         ops.conv_bwd_bias(n, k, P * Q, dyd, bupd, alpha=-lr, beta=1.0)
         assert rel_err(host(bupd), oracle.conv_bwd_bias(dy, alpha=-lr, beta=1.0, db=bias)) < TOL
+        assert ops.engine_status() == 0
     finally:
         _engine(vdnn, "auto")
 
@@ -151,6 +152,7 @@ def test_sgemm(vdnn, oracle, case, algo, engine):
             # only the m x n window is defined; the padding rows of C must be untouched
             assert rel_err(got.reshape(n, ldc)[:, :m], want.reshape(n, ldc)[:, :m]) < TOL
             assert np.array_equal(got.reshape(n, ldc)[:, m:], C0.reshape(n, ldc)[:, m:])
+        assert ops.engine_status() == 0
     finally:
         _engine(vdnn, "auto")
 

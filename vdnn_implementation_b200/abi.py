@@ -77,6 +77,7 @@ SIGNATURES = {
     "vdnn_build_info": (C.c_char_p, []),
     "vdnn_set_engine": (_I, [_I]),
     "vdnn_get_engine": (_I, []),
+    "vdnn_engine_status": (_I, [C.POINTER(_I)]),
     "vdnn_conv_out_dims": (_I, [_D, C.POINTER(_I), C.POINTER(_I)]),
     "vdnn_pool_out_dims": (_I, [_I] * 6 + [C.POINTER(_I), C.POINTER(_I)]),
     "vdnn_conv_workspace_bytes": (_Z, [_I, _I, _D]),

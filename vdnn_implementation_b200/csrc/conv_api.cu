@@ -164,6 +164,11 @@ int vdnn_set_engine(int engine) {
 
 int vdnn_get_engine(void) { return g_engine; }
 
+int vdnn_engine_status(int* code) {
+    if (!code) return VDNN_ERR_BAD_ARG;
+    return tc::take_error(code);
+}
+
 int vdnn_conv_out_dims(const vdnn_conv_desc* d, int* p, int* q) {
     int P, Q;
     if (!p || !q || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;

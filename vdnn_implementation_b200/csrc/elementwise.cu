@@ -279,6 +279,15 @@ __global__ void __launch_bounds__(kThreads) maxpool_bwd_2x2(size_t pairs, int w,
 }
 
 // ---------------------------------------------------------------- softmax (one warp per row)
+__device__ __forceinline__ double warp_sum_f64(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// The row sums are carried in double: with saturated outputs (y close to one-hot) the backward
+// expression dy - sum(dy*y) cancels almost completely, and a float sum would leave only a few
+// correct bits.  The tensors stay fp32; the extra cost on N x 1000 elements is nil.
 __global__ void __launch_bounds__(128) softmax_fwd_kernel(int rows, int cols, const float* __restrict__ x,
                                                           float* __restrict__ y) {
     const int row = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -288,10 +297,10 @@ __global__ void __launch_bounds__(128) softmax_fwd_kernel(int rows, int cols, co
     float m = -INFINITY;
     for (int j = lane; j < cols; j += 32) m = fmaxf(m, xr[j]);
     m = warp_max(m);
-    float s = 0.0f;
-    for (int j = lane; j < cols; j += 32) s += expf(xr[j] - m);
-    s = warp_sum(s);
-    for (int j = lane; j < cols; j += 32) yr[j] = expf(xr[j] - m) / s;
+    double s = 0.0;
+    for (int j = lane; j < cols; j += 32) s += static_cast<double>(expf(xr[j] - m));
+    s = warp_sum_f64(s);
+    for (int j = lane; j < cols; j += 32) yr[j] = static_cast<float>(static_cast<double>(expf(xr[j] - m)) / s);
 }
 
 __global__ void __launch_bounds__(128) softmax_bwd_kernel(int rows, int cols, const float* __restrict__ y,
@@ -301,10 +310,11 @@ __global__ void __launch_bounds__(128) softmax_bwd_kernel(int rows, int cols, co
     const float* yr = y + static_cast<size_t>(row) * cols;
     const float* dr = dy + static_cast<size_t>(row) * cols;
     float* xr = dx + static_cast<size_t>(row) * cols;
-    float dot = 0.0f;
-    for (int j = lane; j < cols; j += 32) dot = fmaf(yr[j], dr[j], dot);
-    dot = warp_sum(dot);
-    for (int j = lane; j < cols; j += 32) xr[j] = yr[j] * (dr[j] - dot);
+    double dot = 0.0;
+    for (int j = lane; j < cols; j += 32) dot += static_cast<double>(yr[j]) * static_cast<double>(dr[j]);
+    dot = warp_sum_f64(dot);
+    for (int j = lane; j < cols; j += 32)
+        xr[j] = static_cast<float>(static_cast<double>(yr[j]) * (static_cast<double>(dr[j]) - dot));
 }
 
 // ---------------------------------------------------------------- loss (single block)

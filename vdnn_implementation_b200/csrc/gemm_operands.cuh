@@ -65,6 +65,11 @@ struct XGatherPixRows {            // rows are pixels, columns are filter taps (
     typedef FiltCoord Col;
     __device__ __forceinline__ Row row(int i) const { return g.pix(i); }
     __device__ __forceinline__ Col col(int kk) const { return g.filt(kk); }
+    // column kk + 1 from column kk without a division
+    __device__ __forceinline__ void next_col(Col& c, int kk_next) const {
+        if (++c.s == g.S) { c.s = 0; if (++c.r == g.R) { c.r = 0; c.off += g.hw; } }
+        c.valid = kk_next < g.n_filt;
+    }
     __device__ __forceinline__ float load(const Row& r, const Col& c) const { return g.at(r, c); }
 };
 
@@ -74,6 +79,7 @@ struct XGatherFiltRows {           // rows are filter taps, columns are pixels (
     typedef PixCoord Col;
     __device__ __forceinline__ Row row(int i) const { return g.filt(i); }
     __device__ __forceinline__ Col col(int kk) const { return g.pix(kk); }
+    __device__ __forceinline__ void next_col(Col& c, int kk_next) const { c = g.pix(kk_next); }
     __device__ __forceinline__ float load(const Row& r, const Col& c) const { return g.at(c, r); }
 };
 
@@ -111,6 +117,10 @@ struct DyGather {
         fc.valid = j < n_cols;
         return fc;
     }
+    __device__ __forceinline__ void next_col(Col& c, int kk_next) const {
+        if (++c.s == S) { c.s = 0; if (++c.r == R) { c.r = 0; c.off += pq; } }
+        c.valid = kk_next < n_cols;
+    }
     __device__ __forceinline__ float load(const Row& pc, const Col& fc) const {
         const int t = pc.ih0 - fc.r, u = pc.iw0 - fc.s;
         if (!(pc.valid && fc.valid) || t < 0 || u < 0) return 0.0f;
@@ -131,7 +141,7 @@ struct SplitDense {
     int row_hi, row_lo, col_hi, col_lo;
 
     struct Row { int off; int valid; };
-    typedef Row Col;
+    struct Col { int off; int valid; int rem; };
     __device__ __forceinline__ Row row(int i) const {
         uint32_t a, b;
         row_div.divmod(static_cast<uint32_t>(i), a, b);
@@ -146,7 +156,13 @@ struct SplitDense {
         Col c;
         c.off = static_cast<int>(a) * col_hi + static_cast<int>(b) * col_lo;
         c.valid = kk < cols;
+        c.rem = static_cast<int>(b);
         return c;
+    }
+    __device__ __forceinline__ void next_col(Col& c, int kk_next) const {
+        if (++c.rem == static_cast<int>(col_div.d)) { c.rem = 0; c.off += col_hi - (static_cast<int>(col_div.d) - 1) * col_lo; }
+        else c.off += col_lo;
+        c.valid = kk_next < cols;
     }
     __device__ __forceinline__ float load(const Row& r, const Col& c) const {
         return (r.valid && c.valid) ? __ldg(p + r.off + c.off) : 0.0f;

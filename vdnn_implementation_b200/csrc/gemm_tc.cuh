@@ -1,5 +1,22 @@
-// tcgen05 contraction engine (placeholder until the kernel lands: reports every shape as
-// unsupported so that the dispatcher uses the FFMA engine).
+// tcgen05 contraction engine for sm_100a: fp32-accurate products on the 5th-generation tensor
+// cores by the 3xTF32 split
+//        a*b ~= a_hi*b_hi + a_hi*b_lo + a_lo*b_hi,      x_hi = tf32(x), x_lo = x - x_hi  (exact),
+// with fp32 accumulation in tensor memory (TMEM).
+//
+// One CTA computes a 128 x BN tile of D (BN = 64 or 128) over a K range in steps of 32:
+//   warps 0-7  producers: gather the 128 x 32 A tile and BN x 32 B tile straight from the NCHW /
+//              KCRS tensors (gemm_operands.cuh), split every value into hi / lo, and store both
+//              into shared memory in the K-major, 128-byte-swizzled layout tcgen05.mma reads;
+//              they also collect the per-stage sums from TMEM (tcgen05.ld) and run the epilogue:
+//              alpha / beta / bias / split-K handling, coalesced stores.
+//   warp 8     allocates TMEM; one elected lane issues tcgen05.mma (3 per 8-wide k slice, 12 per
+//              stage) into one of two TMEM accumulator buffers and tcgen05.commit to hand the stage
+//              back and to publish that buffer.  The producers add each finished buffer into fp32
+//              registers (round-to-nearest adds), so no accumulation chain inside the tensor core
+//              is longer than one stage.
+// Stages are handed over with mbarriers (full: 256 producer arrivals, empty: one commit).  Every
+// wait is bounded: on expiry the thread records an error code in g_tc_error, stops waiting, and
+// the CTA still runs its common exit path (barrier, TMEM release).
 #pragma once
 
 #include "gemm_operands.cuh"
@@ -7,12 +24,335 @@
 namespace vdnn {
 namespace tc {
 
-template <class OpA, class OpB>
-inline bool supported(int, int, int) { return false; }
+constexpr int BM = 128, BK = 32, PRODUCERS = 256, THREADS = PRODUCERS + 32;
+constexpr int A_TILE_BYTES = BM * BK * 4;              // 16 KB, one per hi / lo
+constexpr unsigned long long SPIN_CYCLES = 4000000000ull;   // ~2 s at 1.9 GHz
+constexpr unsigned SPIN_TRIES = 1u << 26;
 
+// 0 = healthy; otherwise 100 + role of the first wait that expired (1 producer, 2 mma, 3 epilogue).
+__device__ int g_tc_error = 0;
+
+template <int BN> struct Config {
+    static constexpr int B_TILE_BYTES = BN * BK * 4;
+    static constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;
+    static constexpr int STAGES = BN == 128 ? 3 : 4;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
+    static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                                      (static_cast<uint32_t>(BM >> 4) << 24);
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait for the phase with the given parity.  Returns false when the limit expired.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    const unsigned long long t0 = clock64();
+    for (unsigned it = 0; it < SPIN_TRIES; ++it) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 1023u) == 1023u && clock64() - t0 > SPIN_CYCLES) break;
+    }
+    return false;
+}
+
+// K-major operand tile with 128-byte swizzle: row r is 128 bytes (32 fp32), 8 rows form a 1 KB atom,
+// the 16-byte chunk index is XORed with (r & 7).
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+    return static_cast<uint32_t>((row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+// Shared-memory matrix descriptor: start address, stride between 8-row atoms = 1024 B, descriptor
+// version 1 (sm_100), layout = SWIZZLE_128B.  The leading-dimension offset is unused for a K-major
+// tile that is exactly one swizzle atom wide.
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+__device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// x = hi + lo with hi representable in tf32 (10 explicit mantissa bits, round to nearest).
+__device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
+    hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+    lo = x - hi;
+}
+
+// Gathers a ROWS x 32 operand tile into registers and stores its hi / lo images.
+//   KC = true : the operand is contiguous along k.  Thread t handles the 16-byte chunk (t & 7) of rows
+//               (t >> 3) + 32*j: a quarter warp reads one 128-byte row segment.
+//   KC = false: the operand is contiguous along its rows.  Thread t handles row t % ROWS and a run of
+//               32 / (256 / ROWS) consecutive k: a warp reads 32 consecutive rows of one k.
+template <class Op, bool KC, int ROWS>
+struct Gather {
+    static constexpr int PASSES = ROWS / 32;                 // KC
+    static constexpr int KRUN = BK / (PRODUCERS / ROWS);     // !KC: 16 (ROWS = 128) or 8 (ROWS = 64)
+    static constexpr int COUNT = KC ? PASSES * 4 : KRUN;
+    typename Op::Row rows[KC ? PASSES : 1];
+    float v[COUNT];
+
+    __device__ __forceinline__ void init(const Op& op, int row0, int t) {
+        if (KC) {
+#pragma unroll
+            for (int j = 0; j < PASSES; ++j) rows[j] = op.row(row0 + (t >> 3) + 32 * j);
+        } else {
+            rows[0] = op.row(row0 + t % ROWS);
+        }
+    }
+    __device__ __forceinline__ void fetch(const Op& op, int k0, int kend, int t) {
+        if (KC) {
+            typename Op::Col c[4];
+            const int kk = k0 + (t & 7) * 4;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) { c[e] = op.col(kk + e); c[e].valid = c[e].valid && (kk + e) < kend; }
+#pragma unroll
+            for (int j = 0; j < PASSES; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[j * 4 + e] = op.load(rows[j], c[e]);
+        } else {
+            int kk = k0 + (t / ROWS) * KRUN;
+            typename Op::Col c = op.col(kk);
+#pragma unroll
+            for (int e = 0; e < KRUN; ++e) {
+                typename Op::Col ce = c;
+                ce.valid = ce.valid && kk < kend;
+                v[e] = op.load(rows[0], ce);
+                ++kk;
+                if (e + 1 < KRUN) op.next_col(c, kk);
+            }
+        }
+    }
+    __device__ __forceinline__ void stash(char* hi_tile, char* lo_tile, int t) const {
+        if (KC) {
+#pragma unroll
+            for (int j = 0; j < PASSES; ++j) {
+                float4 h, l;
+                split_tf32(v[j * 4 + 0], h.x, l.x); split_tf32(v[j * 4 + 1], h.y, l.y);
+                split_tf32(v[j * 4 + 2], h.z, l.z); split_tf32(v[j * 4 + 3], h.w, l.w);
+                const uint32_t o = swz((t >> 3) + 32 * j, t & 7);
+                *reinterpret_cast<float4*>(hi_tile + o) = h;
+                *reinterpret_cast<float4*>(lo_tile + o) = l;
+            }
+        } else {
+            const int row = t % ROWS, chunk0 = (t / ROWS) * (KRUN / 4);
+#pragma unroll
+            for (int q = 0; q < KRUN / 4; ++q) {
+                float4 h, l;
+                split_tf32(v[q * 4 + 0], h.x, l.x); split_tf32(v[q * 4 + 1], h.y, l.y);
+                split_tf32(v[q * 4 + 2], h.z, l.z); split_tf32(v[q * 4 + 3], h.w, l.w);
+                const uint32_t o = swz(row, chunk0 + q);
+                *reinterpret_cast<float4*>(hi_tile + o) = h;
+                *reinterpret_cast<float4*>(lo_tile + o) = l;
+            }
+        }
+    }
+};
+
+template <class OpA, class OpB, bool AKC, bool BKC, int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int K, int k_chunk) {
+    typedef Config<BN> Cfg;
+    constexpr int S = Cfg::STAGES;
+    extern __shared__ char smem_raw[];
+    // operand tiles need 1 KB alignment (swizzle atoms); barriers and the TMEM slot follow them
+    char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + S * Cfg::STAGE_BYTES);
+    // bars[0..S) stage full, bars[S..2S) stage empty, bars[2S..2S+2) accumulator buffer ready; then the TMEM base
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2);
+
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int kbeg = blockIdx.z * k_chunk;
+    const int kend = min(K, kbeg + k_chunk);
+    const int nkb = kbeg < kend ? (kend - kbeg + BK - 1) / BK : 0;
+
+    if (t == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(smem_u32(&bars[s]), PRODUCERS);
+            mbar_init(smem_u32(&bars[S + s]), 1);
+        }
+        mbar_init(smem_u32(&bars[2 * S]), 1);
+        mbar_init(smem_u32(&bars[2 * S + 1]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // Two accumulator buffers of BN columns each: the tensor core sums one 32-wide k block into a
+    // buffer (a chain of 12 MMAs) while the previous block's buffer is added into fp32 registers.
+    // Keeping the in-TMEM chains short matters for accuracy: the tensor core truncates when it adds
+    // into its accumulator, and over thousands of chained MMAs that bias reaches 1e-5 relative.
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 8) {
+        // ------------------------------------------------------------------ producers
+        Gather<OpA, AKC, BM> ga;
+        Gather<OpB, BKC, BN> gb;
+        ga.init(opa, m0, t);
+        gb.init(opb, n0, t);
+        // this thread owns row (warp & 3) * 32 + lane of the tile and half of its columns
+        constexpr int NACC = BN / 2;
+        const int col_beg = (warp >> 2) * NACC;
+        const uint32_t tmem_mine = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(col_beg);
+        float acc[NACC];
+#pragma unroll
+        for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
+        bool alive = true;
+
+        // adds the finished k block `blk` from its TMEM buffer into the register accumulators
+        auto drain = [&](int blk) {
+            const int b = blk & 1;
+            bool ok = mbar_wait(smem_u32(&bars[2 * S + b]), static_cast<uint32_t>(blk >> 1) & 1u);
+            ok = __all_sync(0xffffffffu, ok);               // tcgen05.ld is warp-collective
+            if (!ok) { atomicCAS(&g_tc_error, 0, 103); alive = false; return; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < NACC; c += 16) {
+                float v[16];
+                tmem_ld16(tmem_mine + static_cast<uint32_t>(b * BN + c), v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[c + j] += v[j];
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        };
+
+        if (nkb > 0) { ga.fetch(opa, kbeg, kend, t); gb.fetch(opb, kbeg, kend, t); }
+        for (int i = 0; i < nkb && alive; ++i) {
+            const int s = i % S;
+            const uint32_t phase = static_cast<uint32_t>(i / S) & 1u;
+            // block i reuses the accumulator buffer of block i - 2: empty it first (every producer does,
+            // and the MMA of block i cannot start before all of them have arrived on full[s])
+            if (i >= 2) { drain(i - 2); if (!alive) break; }
+            bool ok = mbar_wait(smem_u32(&bars[S + s]), phase ^ 1u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { atomicCAS(&g_tc_error, 0, 101); alive = false; break; }
+            char* st = tiles + s * Cfg::STAGE_BYTES;
+            ga.stash(st, st + A_TILE_BYTES, t);
+            gb.stash(st + 2 * A_TILE_BYTES, st + 2 * A_TILE_BYTES + Cfg::B_TILE_BYTES, t);
+            // make the generic-proxy stores visible to the tensor core (async proxy), then publish
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(smem_u32(&bars[s]));
+            if (i + 1 < nkb) {
+                ga.fetch(opa, kbeg + (i + 1) * BK, kend, t);
+                gb.fetch(opb, kbeg + (i + 1) * BK, kend, t);
+            }
+        }
+        if (alive && nkb >= 2) drain(nkb - 2);
+        if (alive && nkb >= 1) drain(nkb - 1);
+
+        // ------------------------------------------------------------------ epilogue
+        const int m = m0 + (warp & 3) * 32 + lane;
+        if (alive && m < M) {
+            const int roff = epi.row_off(m);
+#pragma unroll
+            for (int j = 0; j < NACC; ++j) {
+                const int n = n0 + col_beg + j;
+                if (n < N) epi.store(roff, n, acc[j], blockIdx.z);
+            }
+        }
+    } else if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % S;
+            const uint32_t phase = static_cast<uint32_t>(i / S) & 1u;
+            if (!mbar_wait(smem_u32(&bars[s]), phase)) { atomicCAS(&g_tc_error, 0, 102); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_hi = smem_u32(tiles + s * Cfg::STAGE_BYTES);
+            const uint32_t a_lo = a_hi + A_TILE_BYTES;
+            const uint32_t b_hi = a_hi + 2 * A_TILE_BYTES;
+            const uint32_t b_lo = b_hi + Cfg::B_TILE_BYTES;
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((i & 1) * BN);
+#pragma unroll
+            for (int ks = 0; ks < BK / 8; ++ks) {
+                // one k slice = 8 tf32 = 32 bytes inside the swizzle atom
+                const uint64_t dah = make_desc(a_hi + ks * 32), dal = make_desc(a_lo + ks * 32);
+                const uint64_t dbh = make_desc(b_hi + ks * 32), dbl = make_desc(b_lo + ks * 32);
+                mma_tf32(d_tmem, dal, dbh, Cfg::IDESC, ks != 0 ? 1u : 0u);     // small terms first
+                mma_tf32(d_tmem, dah, dbl, Cfg::IDESC, 1u);
+                mma_tf32(d_tmem, dah, dbh, Cfg::IDESC, 1u);
+            }
+            mma_commit(smem_u32(&bars[S + s]));             // stage s may be overwritten once these finish
+            mma_commit(smem_u32(&bars[2 * S + (i & 1)]));   // and this block's sums may be collected
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 8) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    }
+}
+
+template <class OpA, class OpB>
+inline bool supported(int M, int N, int K) { return M >= 1 && N >= 1 && K >= 1; }
+
+template <class OpA, class OpB, bool AKC, bool BKC, int BN>
+int launch_bn(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K, int splits, int k_chunk, cudaStream_t stream) {
+    typedef Config<BN> Cfg;
+    static bool configured[16] = {false};
+    int dev = 0;
+    VDNN_CUDA(cudaGetDevice(&dev));
+    auto kern = gemm_kernel<OpA, OpB, AKC, BKC, BN>;
+    if (dev < 16 && !configured[dev]) {
+        VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        configured[dev] = true;
+    }
+    dim3 grid(ceil_div(M, BM), ceil_div(N, BN), splits);
+    if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
+    kern<<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(a, b, epi, M, N, K, k_chunk);
+    VDNN_LAUNCHED();
+    return VDNN_OK;
+}
+
+// k_chunk must be a multiple of 32.
 template <class OpA, class OpB, bool AKC, bool BKC>
-int launch(const OpA&, const OpB&, const Epilogue&, int, int, int, int, int, cudaStream_t) {
-    return VDNN_ERR_UNSUPPORTED;
+int launch(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K, int splits, int k_chunk, cudaStream_t stream) {
+    if (N <= 64) return launch_bn<OpA, OpB, AKC, BKC, 64>(a, b, epi, M, N, K, splits, k_chunk, stream);
+    return launch_bn<OpA, OpB, AKC, BKC, 128>(a, b, epi, M, N, K, splits, k_chunk, stream);
+}
+
+// Reads and clears the device-side error word (synchronises the device).
+inline int take_error(int* code) {
+    int v = 0, zero = 0;
+    VDNN_CUDA(cudaDeviceSynchronize());
+    VDNN_CUDA(cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)));
+    if (v != 0) VDNN_CUDA(cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int)));
+    *code = v;
+    return VDNN_OK;
 }
 
 }  // namespace tc

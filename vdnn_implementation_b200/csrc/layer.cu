@@ -222,14 +222,16 @@ int Layer::backward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, v
 
 // Common prologue of every forward: dst allocation (layer.cu:553-556 and siblings).
 #define FWD_PROLOGUE()                                                              \
-    if (vdnnMode != BASELINE) { const int _a = cnmemMallocDstData(isDynamic); if (_a != 0) return _a; }
+    if (vdnnMode != BASELINE) { const int _a = cnmemMallocDstData(isDynamic); if (_a != 0) return _a; }         \
+    if (handle->profiling) CU(cudaEventRecord(handle->pf_fwd_beg[layerId], *stream_compute));
 // Common prologue of every backward: grad allocation, then the prefetch issue (layer.cu:596-603).
 #define BWD_PROLOGUE()                                                              \
     if (vdnnMode != BASELINE) { const int _a = cnmemMallocGradData(isDynamic); if (_a != 0) return _a; }    \
     if (vdnnMode != BASELINE && _layer_id_to_prefetch >= 0) {                       \
         const int _p = prefetchPreviousSrcData(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes); \
         if (_p != 0) return _p;                                                     \
-    }
+    }                                                                               \
+    if (handle->profiling) CU(cudaEventRecord(handle->pf_bwd_beg[layerId], *stream_compute));
 #define MARK(ev) CU(cudaEventRecord(handle->ev[layerId], *stream_compute))
 
 /* ------------------------------------------------------------------ CONV (layer.cu:539-665) */

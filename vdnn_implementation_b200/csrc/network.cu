@@ -481,7 +481,6 @@ int Network::forwardPropagation(bool isDynamic) {
             NET_CU(cudaStreamWaitEvent(stream_compute, ctx.ev_weights_ready[l], 0));
             ctx.weights_pending[l] = 0;
         }
-        if (ctx.profiling) NET_CU(cudaEventRecord(ctx.pf_fwd_beg[l], stream_compute));
         NET_TRY(layer[l]->forward(isOffload, offloadedSrcData_h, workSpace, isDynamic));
         if (ctx.profiling) NET_CU(cudaEventRecord(ctx.pf_fwd_end[l], stream_compute));
 
@@ -537,7 +536,6 @@ int Network::backwardPropagation(bool isDynamic) {
         for (int l = last; l >= 0; l--) {
             if (l == last) { layer[l]->copyDiffData(networkDiffData); layer[l]->copyGradData(networkGradData); }
             else { layer[l]->copyDiffData(layer[l + 1]->GradData()); layer[l]->copyGradData(layer[l + 1]->DiffData()); }
-            if (ctx.profiling) NET_CU(cudaEventRecord(ctx.pf_bwd_beg[l], stream_compute));
             NET_TRY(layer[l]->backward(-1, NULL, NULL, 0, workSpace, isDynamic));
             if (ctx.profiling) NET_CU(cudaEventRecord(ctx.pf_bwd_end[l], stream_compute));
             NET_TRY(reduceAndApply(l));
@@ -559,7 +557,6 @@ int Network::backwardPropagation(bool isDynamic) {
             // this layer reads its own srcData: if that came back from the host, wait for the copy
             if (isOffload[l] && isPrefetched[l] && !ctx.dry_run)
                 NET_CU(cudaStreamWaitEvent(stream_compute, ctx.ev_prefetch_done[l], 0));
-            if (ctx.profiling) NET_CU(cudaEventRecord(ctx.pf_bwd_beg[l], stream_compute));
 
             const int prefId = l > 0 ? findPrefetchLayer(l) : -1;
             if (prefId >= 0) {

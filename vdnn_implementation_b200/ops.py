@@ -122,3 +122,10 @@ def set_engine(engine):
 
 def get_engine():
     return lib().vdnn_get_engine()
+
+
+def engine_status():
+    """Synchronises the device; returns the tensor-core engine's error code (0 = healthy) and clears it."""
+    code = C.c_int()
+    check(lib().vdnn_engine_status(C.byref(code)), "engine_status")
+    return code.value
