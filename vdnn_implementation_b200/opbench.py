@@ -1,0 +1,81 @@
+"""Per-call timing of the contraction engines on the convolution shapes of VGG16.
+
+    python -m vdnn_implementation_b200.opbench --engine tcgen05 --batch 32
+    python -m vdnn_implementation_b200.opbench --engine tcgen05 --batch 32 --layer 5 --op fwd --reps 3   (one kernel, for ncu)
+
+Times vdnn_conv_fwd / vdnn_conv_bwd_data / vdnn_conv_bwd_filter through the C ABI with CUDA events on
+the launching stream; PyTorch only owns the buffers.  Prints algorithmic TFLOP/s (2*M*N*K per call).
+"""
+import argparse
+
+import torch
+
+import vdnn_implementation_b200 as v
+
+SHAPES = [(3, 64, 224), (64, 64, 224), (64, 128, 112), (128, 128, 112), (128, 256, 56), (256, 256, 56),
+          (256, 512, 28), (512, 512, 28), (512, 512, 14)]
+
+
+def timeit(fn, reps):
+    fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--engine", default="tcgen05", choices=["ffma", "tcgen05"])
+    ap.add_argument("--batch", type=int, default=32)
+    ap.add_argument("--layer", type=int, default=-1, help="index into the VGG16 shape list; -1 = all")
+    ap.add_argument("--op", default="all", choices=["all", "fwd", "dgrad", "wgrad"])
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--algo", type=int, default=1, help="0 MEMORY_OPT, 1 PERF_OPT")
+    args = ap.parse_args()
+    ops = v.ops
+    ops.set_engine({"ffma": v.ENGINE_FFMA, "tcgen05": v.ENGINE_TCGEN05}[args.engine])
+    n = args.batch
+    total = {"fwd": 0.0, "dgrad": 0.0, "wgrad": 0.0}
+    flops = 0.0
+    for idx, (c, k, h) in enumerate(SHAPES):
+        if args.layer >= 0 and idx != args.layer:
+            continue
+        d = ops.conv_desc(n, c, h, h, k, 3, 3, (1, 1), (1, 1))
+        x = torch.randn(n, c, h, h, device="cuda")
+        w = torch.randn(k, c, 3, 3, device="cuda") * 0.05
+        y = torch.empty(n, k, h, h, device="cuda")
+        dy = torch.randn(n, k, h, h, device="cuda")
+        dx = torch.empty_like(x)
+        dw = torch.empty_like(w)
+        bias = torch.zeros(k, device="cuda")
+        need = max(ops.conv_workspace_bytes(op, args.algo, d) for op in range(3))
+        ws = torch.empty(max(need, 4) // 4, device="cuda")
+        calls = {
+            "fwd": lambda: ops.conv_fwd(d, x, w, y, bias=bias, algo_mode=args.algo, workspace=ws, workspace_bytes=need),
+            "dgrad": lambda: ops.conv_bwd_data(d, w, dy, dx, algo_mode=args.algo, workspace=ws, workspace_bytes=need),
+            "wgrad": lambda: ops.conv_bwd_filter(d, x, dy, dw, alpha=-0.01, beta=1.0, algo_mode=args.algo, workspace=ws,
+                                                 workspace_bytes=need),
+        }
+        fl = 2.0 * n * h * h * k * c * 9
+        flops += fl
+        line = f"conv {c:4d}->{k:4d} @{h:3d}x{h:<3d} batch {n}:"
+        for name, fn in calls.items():
+            if args.op not in ("all", name):
+                continue
+            ms = timeit(fn, args.reps)
+            total[name] += ms
+            line += f"  {name} {ms:8.3f} ms {fl / ms / 1e9:7.1f} TFLOP/s"
+        print(line, flush=True)
+    for name, ms in total.items():
+        if ms > 0:
+            print(f"{name}: {ms:.2f} ms, {flops / ms / 1e9:.1f} TFLOP/s")
+    print("engine status", ops.engine_status())
+
+
+if __name__ == "__main__":
+    main()
