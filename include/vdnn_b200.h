@@ -32,7 +32,8 @@ typedef enum {
     VDNN_ERR_UNSUPPORTED = -4,    /* shape outside what the selected engine implements       */
     VDNN_ERR_OUT_OF_MEMORY = -5,  /* pool exhausted (network-level calls only)               */
     VDNN_ERR_TIMEOUT = -6,        /* a bounded device-side wait expired                      */
-    VDNN_ERR_STATE = -7           /* call order violated (e.g. backward before forward)      */
+    VDNN_ERR_STATE = -7,          /* call order violated (e.g. backward before forward)      */
+    VDNN_ERR_SCRATCH_LIMIT = -8   /* problem needs more than the library's built-in scratch  */
 } vdnn_status;
 
 const char* vdnn_status_string(int status);
@@ -100,6 +101,29 @@ int vdnn_conv_bwd_bias(int n, int k, int pq, float alpha, const float* dy, float
 int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* x,
                          const float* dy, float beta, float* dw,
                          void* workspace, size_t workspace_bytes, void* stream);
+
+/* Filter gradient for callers that cannot provide workspace.  No counterpart in the reference.
+ *
+ * Same result as vdnn_conv_bwd_filter with VDNN_ALGO_PERF_OPT (fixed-order, deterministic split-K
+ * sums), but the per-split partial sums live in a scratch array that is part of the library image
+ * (a file-scope __device__ array of VDNN_STATIC_SCRATCH_BYTES = 24 MiB, resident on every GPU that
+ * loads the library until the process exits) instead of caller-provided workspace.  It is meant for
+ * hosts that fix their device-memory budget at start-up and must not allocate afterwards -- a
+ * plugin loaded into a process whose allocator it cannot reach, or a steady-state loop that must
+ * not hit the device-wide synchronisation an allocation or release implies -- and so have no
+ * buffer to pass as `workspace`.  The entry point calls no cudaMalloc / cudaFree and no routine
+ * that allocates.
+ *   - Shapes whose partial sums exceed the array (vdnn_conv_workspace_bytes(VDNN_CONV_BWD_FILTER,
+ *     VDNN_ALGO_PERF_OPT, d) > VDNN_STATIC_SCRATCH_BYTES) are refused with VDNN_ERR_SCRATCH_LIMIT;
+ *     nothing is launched.
+ *   - The first call on a device looks up the array's device address (once per device, with that
+ *     device current).  Make that first call before any stream capture begins.
+ *   - All calls on a device share the one array, which keeps whatever the last call left in it.
+ *     Every element a call reads was written by that same call, so nothing has to be cleared; but
+ *     two calls that overlap on the GPU (different streams without ordering) race on it. */
+#define VDNN_STATIC_SCRATCH_BYTES (24u << 20)
+int vdnn_conv_bwd_filter_static(const vdnn_conv_desc* d, float alpha, const float* x, const float* dy,
+                                float beta, float* dw, void* stream);
 
 /* cublasSgemm (layer.cu:677-685, 697-705, 725-733, 736-744, 752-760): column-major
  * C(m x n) = alpha * op(A) * op(B) + beta * C, transa/transb: 0 = N, 1 = T. */

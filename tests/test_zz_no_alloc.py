@@ -1,0 +1,64 @@
+"""The workspace-free filter gradient (vdnn_conv_bwd_filter_static) against the ordinary entry point.
+
+Some hosts of this library cannot allocate device memory once they are running: their memory budget
+is fixed at start-up, or they sit inside a process whose allocator they cannot reach, or an
+allocation's implicit device-wide synchronisation is not acceptable in their steady-state loop.
+They have no buffer to pass as `workspace`, so this entry point keeps the split-K partial sums in a
+24 MiB array that is part of the library image.  The file is named so that pytest collects it last.
+"""
+import numpy as np
+import pytest
+import torch
+
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(vdnn, n, c, h, k, seed):
+    ops = vdnn.ops
+    d = ops.conv_desc(n, c, h, h, k, 3, 3, (1, 1), (1, 1))
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(n, c, h, h, device="cuda", generator=g)
+    dy = torch.randn(n, k, h, h, device="cuda", generator=g)
+    w0 = torch.randn(k, c, 3, 3, device="cuda", generator=g)
+    return ops, d, x, dy, w0
+
+
+def test_static_scratch_matches_workspace_entry_point_twice(vdnn):
+    results = []
+    # two calls in a row with different shapes and data: the second reuses the array the first left dirty
+    for (n, c, h, k, seed) in [(8, 32, 28, 32, 1), (4, 64, 14, 48, 2)]:
+        ops, d, x, dy, w0 = _case(vdnn, n, c, h, k, seed)
+        need = ops.conv_workspace_bytes(2, 1, d)
+        assert 0 < need <= ops.STATIC_SCRATCH_BYTES          # the shape really does use scratch
+        ws = torch.empty(need // 4, device="cuda")
+        want = w0.clone()
+        ops.conv_bwd_filter(d, x, dy, want, alpha=-0.01, beta=1.0, algo_mode=1, workspace=ws, workspace_bytes=need)
+        got = w0.clone()
+        ops.conv_bwd_filter_static(d, x, dy, got, alpha=-0.01, beta=1.0)
+        torch.cuda.synchronize()
+        assert rel_err(got.cpu().numpy(), want.cpu().numpy()) < 1e-4
+        assert torch.equal(got, want)                         # same kernels, fixed summation order
+        # plain gradient (alpha = 1, beta = 0) as well
+        ops.conv_bwd_filter(d, x, dy, want, algo_mode=1, workspace=ws, workspace_bytes=need)
+        ops.conv_bwd_filter_static(d, x, dy, got)
+        torch.cuda.synchronize()
+        assert rel_err(got.cpu().numpy(), want.cpu().numpy()) < 1e-4
+        results.append(float(got.abs().sum()))
+    assert all(np.isfinite(results)) and ops.engine_status() == 0
+
+
+def test_static_scratch_refuses_what_does_not_fit(vdnn):
+    ops = vdnn.ops
+    # 512 -> 512 channels at 14x14: few output tiles, many splits, 27 MiB of partial sums, beyond the 24 MiB array
+    d = ops.conv_desc(8, 512, 14, 14, 512, 3, 3, (1, 1), (1, 1))
+    assert ops.conv_workspace_bytes(2, 1, d) > ops.STATIC_SCRATCH_BYTES
+    x = torch.zeros(8, 512, 14, 14, device="cuda")
+    dy = torch.zeros(8, 512, 14, 14, device="cuda")
+    dw = torch.full((512, 512, 3, 3), 3.0, device="cuda")
+    with pytest.raises(vdnn.VdnnError) as e:
+        ops.conv_bwd_filter_static(d, x, dy, dw)
+    assert e.value.status == -8 and "SCRATCH_LIMIT" in str(e.value)
+    torch.cuda.synchronize()
+    assert bool((dw == 3.0).all())                            # nothing was launched

@@ -253,6 +253,47 @@ int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, co
                                                              algo_mode, workspace, workspace_bytes, as_stream(stream));
 }
 
+}  // extern "C"
+
+namespace {
+
+// Scratch for vdnn_conv_bwd_filter_static.  In host code this name is only a handle for the
+// symbol, not a device address: the address comes from cudaGetSymbolAddress, per device.
+static __device__ __align__(256) float g_static_scratch[VDNN_STATIC_SCRATCH_BYTES / sizeof(float)];
+float* g_static_scratch_addr[16] = {nullptr};
+
+// Device address of the scratch array on the current device; resolved on first use per device.
+int static_scratch_address(float** out) {
+    int dev = 0;
+    VDNN_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 16) return VDNN_ERR_UNSUPPORTED;
+    if (!g_static_scratch_addr[dev]) {
+        void* p = nullptr;
+        VDNN_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        g_static_scratch_addr[dev] = static_cast<float*>(p);
+    }
+    *out = g_static_scratch_addr[dev];
+    return VDNN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int vdnn_conv_bwd_filter_static(const vdnn_conv_desc* d, float alpha, const float* x, const float* dy, float beta,
+                                float* dw, void* stream) {
+    int P, Q;
+    if (!x || !dy || !dw || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
+    const size_t need = vdnn_conv_workspace_bytes(VDNN_CONV_BWD_FILTER, VDNN_ALGO_PERF_OPT, d);
+    if (need > VDNN_STATIC_SCRATCH_BYTES) return VDNN_ERR_SCRATCH_LIMIT;
+    float* scratch = nullptr;
+    const int st = static_scratch_address(&scratch);
+    if (st != VDNN_OK) return st;
+    // The partial sums of every split are written in full before the reduction reads them, so the
+    // array's previous contents never matter.
+    return vdnn_conv_bwd_filter(d, VDNN_ALGO_PERF_OPT, alpha, x, dy, beta, dw, scratch, VDNN_STATIC_SCRATCH_BYTES, stream);
+}
+
 size_t vdnn_sgemm_workspace_bytes(int algo_mode, int m, int n, int k) {
     if (algo_mode != VDNN_ALGO_PERF_OPT || m <= 0 || n <= 0 || k <= 0) return 0;
     const SplitPlan plan = plan_split(m, n, k);

@@ -600,6 +600,7 @@ const char* vdnn_status_string(int status) {
     case VDNN_ERR_OUT_OF_MEMORY: return "VDNN_ERR_OUT_OF_MEMORY";
     case VDNN_ERR_TIMEOUT: return "VDNN_ERR_TIMEOUT";
     case VDNN_ERR_STATE: return "VDNN_ERR_STATE";
+    case VDNN_ERR_SCRATCH_LIMIT: return "VDNN_ERR_SCRATCH_LIMIT";
     default: return "VDNN_ERR_UNKNOWN";
     }
 }
