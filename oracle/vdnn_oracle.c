@@ -743,7 +743,8 @@ int orc_policy_trace(const orc_layer_spec* specs, int L, int vdnn_type, const in
     int64_t* srcB = malloc(sizeof(int64_t) * L); int64_t* dstB = malloc(sizeof(int64_t) * L);
     int* types = malloc(sizeof(int) * L);
     unsigned char* off = calloc(L, 1); unsigned char* pre = calloc(L, 1);
-    int64_t max_dxdy = 0, max_ws = 0, pinned = 0, offB = 0, preB = 0;
+    int64_t max_dxdy = 0, pinned = 0, offB = 0, preB = 0;
+    int32_t max_ws = 0;    /* network.cu:1025-1040 keeps the maximum in an int: sizes wrap at 2^31 */
     for (int l = 0; l < L; ++l) {
         int n, c, h, w; orc_layer_out_dims(&specs[l], &n, &c, &h, &w);
         srcB[l] = 4 * (int64_t)src_size(&specs[l]); dstB[l] = 4 * (int64_t)n * c * h * w;
@@ -760,13 +761,16 @@ int orc_policy_trace(const orc_layer_spec* specs, int L, int vdnn_type, const in
         }
         if (vdnn_type == ORC_BASELINE) emit(&t, ORC_EV_ALLOC, l, ORC_TAG_DST, dstB[l]);
         if (srcB[l] > max_dxdy) max_dxdy = srcB[l];
-        if (IS_C(l)) for (int j = 0; j < 3; ++j) if (WS(l, j) > max_ws) max_ws = WS(l, j);
+        if (IS_C(l)) for (int j = 0; j < 3; ++j) {
+            int32_t temp = (int32_t)(uint32_t)(uint64_t)WS(l, j);
+            if (max_ws < temp) max_ws = temp;
+        }
     }
     if (dstB[L - 1] > max_dxdy) max_dxdy = dstB[L - 1];
     if (vdnn_type == ORC_BASELINE) {                       /* network.cu:894-906 */
         emit(&t, ORC_EV_ALLOC, -1, ORC_TAG_DXDY, max_dxdy);
         emit(&t, ORC_EV_ALLOC, -1, ORC_TAG_DXDY, max_dxdy);
-        if (max_ws > 0) emit(&t, ORC_EV_ALLOC, -1, ORC_TAG_WS, max_ws);
+        if (max_ws > 0) emit(&t, ORC_EV_ALLOC, -1, ORC_TAG_WS, (int64_t)max_ws);
     } else if (vdnn_type == ORC_VDNN_ALL) {                /* network.cu:913-923 */
         for (int l = 0; l < L - 1; ++l) { off[l] = 1; pinned += srcB[l]; }
     } else if (vdnn_type == ORC_VDNN_CONV) {               /* network.cu:926-938 */

@@ -7,10 +7,13 @@
  * by the tests, by the smoke check and by the CPU-baseline leg of the
  * benchmark, never by the product library.
  *
- * Parity status: the reference ships no golden vectors and its arithmetic
- * lives in closed libraries (cuDNN, cuBLAS).  This oracle is pinned against
- * tensors dumped from the reference's own Layer class run on a B200 (see
- * tests/golden/); where a fixture is absent the case is "parity unpinned".
+ * Parity status: pinned.  The reference ships no golden vectors and its
+ * arithmetic lives in closed libraries (cuDNN, cuBLAS), so the pins were made
+ * by running the reference itself: tensors computed by its own Layer class on
+ * cuDNN 9.10 / cuBLAS on a B200 and the memory lines its program prints are
+ * committed under tests/golden/ (see tests/golden/make_golden.py) and checked by
+ * tests/test_golden.py.  LRN has no counterpart in the reference; it is pinned
+ * against PyTorch's local_response_norm only.
  *
  * Storage is fp32 NCHW / KCRS (vdnn.h:11,19); accumulation type is
  * ORC_ACC (double for the checker build, float for the timed baseline build).

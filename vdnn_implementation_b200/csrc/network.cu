@@ -386,13 +386,17 @@ int Network::findMaxDxDySize() {            // network.cu:1010-1023 (bytes)
     return ret * static_cast<int>(sizeof(DATATYPE));
 }
 
-int Network::findMaxWorkSpaceSize() {       // network.cu:1025-1040
-    size_t ret = 0;
+int Network::findMaxWorkSpaceSize() {       // network.cu:1025-1040: the maximum is kept in an int
+    int ret = 0;
     for (int i = 0; i < numLayers; i++)
-        if (layer[i]->LayerType() == FC_CONV || layer[i]->LayerType() == CONV)
-            ret = std::max(ret, std::max(layer[i]->FwdWorkSpaceSize(),
-                                         std::max(layer[i]->BwdDataWorkSpaceSize(), layer[i]->BwdFilterWorkSpaceSize())));
-    return static_cast<int>(ret);
+        if (layer[i]->LayerType() == FC_CONV || layer[i]->LayerType() == CONV) {
+            const size_t sizes[3] = {layer[i]->FwdWorkSpaceSize(), layer[i]->BwdDataWorkSpaceSize(), layer[i]->BwdFilterWorkSpaceSize()};
+            for (size_t v : sizes) {
+                const int temp = static_cast<int>(static_cast<unsigned>(v));
+                if (ret < temp) ret = temp;
+            }
+        }
+    return ret;
 }
 
 void Network::resetIsPrefetchedArray() {
