@@ -84,15 +84,62 @@ def host_threads():
         return os.cpu_count() or 1
 
 
+def run_reference_binary(args, exe):
+    """One forward + backward of the unmodified reference program per step; it times itself (vdnn.cu:72-79:
+    wall clock around forwardPropagation + backwardPropagation, host-side input generation included) and
+    prints microseconds.  Returns (images/s, mean seconds, steps used) or None if it could not run."""
+    import re
+    batch = MODELS[args.model][0]
+    env = dict(os.environ, VDNN_POOL_BYTES=str(int(max(args.pool_gb, 24.0) * 1e9)))
+    runs = max(1, min(args.steps, 5))           # every run re-initialises the network (seconds): keep the arm bounded
+    warm = 1 if args.warmup > 0 else 0
+    times = []
+    for i in range(warm + runs):
+        try:
+            out = subprocess.run([exe, args.model, args.policy, args.algo], stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                                 text=True, env=env, timeout=600).stdout
+        except Exception:
+            return None
+        m = re.search(r"Elapsed Time: (\d+)", out)
+        if not m:
+            return None
+        if i >= warm:
+            times.append(int(m.group(1)) / 1e6)
+    mean = sum(times) / len(times)
+    return batch / mean, mean, runs, warm
+
+
 def run_reference(args):
-    """Reference arm.  The reference has no CPU path and its cuDNN build needs libraries that are not
-    in its tree, so this arm times the CPU restatement of the same layer math (oracle port)."""
+    """Reference arm.  When the reference was built here (oracle/_ref/vdnn_ref, its unmodified sources on
+    cuDNN / cuBLAS) and a GPU is present, the reference program itself is run and timed by its own clock.
+    Otherwise the CPU restatement of the same layer math (oracle port) is timed on the host cores."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    exe = os.path.join(ROOT, "oracle", "_ref", "vdnn_ref")
+    res = None
+    if os.path.exists(exe) and subprocess.run(["nvidia-smi", "-L"], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL).returncode == 0:
+        res = run_reference_binary(args, exe)
+    cores = host_threads()
+    if res:
+        value, step_s, runs, warm = res
+        batch = MODELS[args.model][0]
+        line = {
+            "impl": "reference", "metric": "train images/s", "value": value, "unit": "images/s", "n_gpus": 1,
+            "steps": runs, "warmup": warm, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.model} {args.policy} {args.algo}, batch {batch}, the reference program on cuDNN/cuBLAS "
+                                   f"(one iteration per process, timed by its own clock incl. host input generation)"},
+            "cpu_baseline": {"value": value, "unit": "images/s", "cores": 1, "kind": "reference",
+                             "sample": f"{runs} runs of oracle/_ref/vdnn_ref {args.model} {args.policy} {args.algo} (unmodified reference "
+                                       f"sources, cuDNN default math, one host thread driving the same GPU)"},
+            "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0,
+        }
+        print(json.dumps(line), flush=True)
+        return
     batch = args.cpu_batch or 1
     value, step_s = cpu_step_rate(args.model, batch, max(args.steps, 1), min(args.warmup, 1), args.lr)
-    cores = host_threads()
     line = {
         "impl": "reference", "metric": "train images/s", "value": value, "unit": "images/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": step_s * 1e3, "higher_is_better": True,
@@ -279,7 +326,7 @@ def run_b200(args):
         line["vdnn"]["weights_identical_across_ranks"] = len(set(sums)) == 1
     net.close()
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu_batch = args.cpu_batch or (1 if args.model.startswith("VGG") else 8)
+        cpu_batch = args.cpu_batch or (8 if args.model.startswith("VGG") else 64)
         v, step_s = cpu_step_rate(args.model, cpu_batch, 1, 1, args.lr)
         line["cpu_baseline"] = {"value": v, "unit": "images/s", "cores": host_threads(), "kind": "port",
                                 "sample": f"{args.model} batch {cpu_batch}: 1 warm-up + 1 timed step ({step_s:.1f} s) of the CPU "
