@@ -2,7 +2,8 @@
 """Benchmark of the vDNN training hot path on B200.
 
     python bench.py --gpus N --steps K --warmup W            this library (CUDA, sm_100a)
-    python bench.py --impl reference --steps K --warmup W    the straightforward CPU implementation
+    python bench.py --impl reference --steps K --warmup W    the reference program itself (oracle/_ref, cuDNN build)
+                                                             where it was built, else the CPU restatement
 
 One "step" is forward + backward (SGD folded into backward) of the named network under the named
 vDNN policy on one synthetic batch per GPU.  Prints ONE JSON line on rank 0.
@@ -42,6 +43,8 @@ def parse():
     ap.add_argument("--lr", type=float, default=0.01)
     ap.add_argument("--engine", default="auto", choices=["auto", "ffma", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--reference-kind", default="auto", choices=["auto", "cpu"],
+                    help="--impl reference: auto = the built reference program when present and a GPU is visible, else the CPU port")
     ap.add_argument("--cpu-batch", type=int, default=0, help="images in the CPU sample (0 = sized for ~10-30 s)")
     return ap.parse_args()
 
@@ -118,7 +121,10 @@ def run_reference(args):
         return
     exe = os.path.join(ROOT, "oracle", "_ref", "vdnn_ref")
     res = None
-    if os.path.exists(exe) and subprocess.run(["nvidia-smi", "-L"], stdout=subprocess.DEVNULL, stderr=subprocess.DEVNULL).returncode == 0:
+    import shutil
+    has_gpu = bool(shutil.which("nvidia-smi")) and subprocess.run(["nvidia-smi", "-L"], stdout=subprocess.DEVNULL,
+                                                                 stderr=subprocess.DEVNULL).returncode == 0
+    if os.path.exists(exe) and has_gpu and args.reference_kind != "cpu":
         res = run_reference_binary(args, exe)
     cores = host_threads()
     if res:
