@@ -40,7 +40,7 @@ def parse():
     ap.add_argument("--algo", default="VDNN_PERF_OPT_ALGO", choices=["VDNN_MEMORY_OPT_ALGO", "VDNN_PERF_OPT_ALGO"])
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch (0 = the model's own)")
     ap.add_argument("--pool-gb", type=float, default=24.0, help="device pool capacity (BASELINE config: 24 GB cap)")
-    ap.add_argument("--lr", type=float, default=0.01)
+    ap.add_argument("--lr", type=float, default=1e-5, help="the reference's LEARNING_RATE (vdnn.h:8); gradients are batch sums")
     ap.add_argument("--engine", default="auto", choices=["auto", "ffma", "tcgen05"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--reference-kind", default="auto", choices=["auto", "cpu"],

@@ -56,13 +56,14 @@ cnmemStatus_t cnmemRegisterStream(cudaStream_t stream);
 const char* cnmemGetErrorString(cnmemStatus_t status);                         /* layer.h:114 */
 
 /* ---- extensions --------------------------------------------------------------------------- */
-/* Same as cnmemFree, but remembers that the bytes are still in use on the device until every
- * event in `events` has completed.  A later allocation that lands on those bytes makes its
- * streams wait for the events first, so the host can free in the reference's order without
- * synchronising. */
-cnmemStatus_t vdnnPoolFreeAfter(void* ptr, const cudaEvent_t* events, int numEvents);
+/* Same as cnmemFree, but remembers that the bytes are still in use on the device until everything
+ * enqueued so far on each of `streams` has completed (the pool records a private event on each).  A later
+ * allocation that lands on those bytes makes its streams wait for those events first, so the host can
+ * free in the reference's order without synchronising. */
+cnmemStatus_t vdnnPoolFreeAfter(void* ptr, const cudaStream_t* streams, int numStreams);
 /* cnmemMalloc followed by cudaStreamWaitEvent(streams[i], e) for every pending event e that
- * covers part of the returned block. */
+ * covers part of the returned block.  Among the free blocks that fit, the one that becomes usable
+ * soonest is chosen (no pending event, else the oldest pending events), then the tightest fit. */
 cnmemStatus_t vdnnPoolMallocFor(void** ptr, size_t size, const cudaStream_t* streams, int numStreams);
 cnmemStatus_t vdnnPoolHighWater(size_t* peakBytes, int reset);
 /* Makes the k-th allocation from now fail with CNMEM_STATUS_OUT_OF_MEMORY (k >= 1; 0 disarms).

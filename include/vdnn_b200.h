@@ -287,6 +287,11 @@ typedef struct {
 /* Fills timing fields only if profiling events were enabled with vdnn_network_set_profiling. */
 int vdnn_network_get_stats(vdnn_network* net, vdnn_network_stats* out);
 int vdnn_network_set_profiling(vdnn_network* net, int enabled);
+/* Per-layer timeline of the last profiled step, in milliseconds from the step's first event:
+ * out[8*l + 0..7] = forward begin, forward end, offload begin, offload end, backward begin, backward end,
+ * prefetch begin, prefetch end of layer l (negative where the layer has no such event).  `out` holds
+ * 8 * vdnn_network_num_layers floats.  Synchronises the network. */
+int vdnn_network_timeline(vdnn_network* net, float* out);
 
 /* Data parallelism (no counterpart in the reference, which is single-device: vdnn.h:5).
  * One process per GPU; gradients are written to a staging buffer, all-reduced (sum) with NCCL on

@@ -35,7 +35,7 @@ def batches(world, per_rank, steps, in_per_image, classes):
 
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
-    model, policy, per_rank, steps, lr = sys.argv[1], sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), 0.01
+    model, policy, per_rank, steps, lr = sys.argv[1], sys.argv[2], int(sys.argv[3]), int(sys.argv[4]), float(sys.argv[5])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     net = vdnn.Network(model, policy, "VDNN_PERF_OPT_ALGO", batch_size=per_rank, device=local, pool_bytes=8e9,

@@ -21,12 +21,12 @@ def _port():
     return p
 
 
-@pytest.mark.parametrize("model,policy,per_rank,steps", [("ALEXNET", "VDNN_CONV", 4, 10), ("VGG16_64", "VDNN_ALL", 2, 3)])
-def test_two_gpu_data_parallel(vdnn, model, policy, per_rank, steps):
+@pytest.mark.parametrize("model,policy,per_rank,steps,lr", [("ALEXNET", "VDNN_CONV", 4, 10, 0.01), ("VGG16_64", "VDNN_ALL", 2, 1, 1e-4)])
+def test_two_gpu_data_parallel(vdnn, model, policy, per_rank, steps, lr):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
-           "--master-port", str(_port()), os.path.join(HERE, "dp_worker.py"), model, policy, str(per_rank), str(steps)]
+           "--master-port", str(_port()), os.path.join(HERE, "dp_worker.py"), model, policy, str(per_rank), str(steps), str(lr)]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     p = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=600, env=env)
     assert p.returncode == 0, p.stdout[-3000:]

@@ -104,6 +104,27 @@ def test_policies_agree_at_full_width(vdnn):
             assert rel_err(a, b) < 1e-5, policy
 
 
+def test_resident_batch_is_reused_correctly_across_steps(vdnn):
+    """Several steps on one uploaded batch.  Under VDNN_ALL / VDNN_CONV layer 0 is offloaded too, and the
+    prefetched copy becomes the next step's input buffer (network.cu:1185): the next offload of layer 0
+    must wait for that prefetch.  Compared with VDNN_NONE, which never moves the input."""
+    import ctypes as C
+    res = {}
+    for policy in ("VDNN_NONE", "VDNN_ALL", "VDNN_CONV"):
+        net = vdnn.Network("ALEXNET", policy, "VDNN_PERF_OPT_ALGO", batch_size=16, pool_bytes=4e9, learning_rate=1e-4)
+        try:
+            net.seed_input(1000, 2000)
+            for _ in range(4):
+                net.step()
+            res[policy] = ([net.weights(l) for l in (0, 3, 17)], [net.bias(l) for l in (0, 17)], net.loss())
+        finally:
+            net.close()
+    for policy in ("VDNN_ALL", "VDNN_CONV"):
+        for a, b in zip(res[policy][0] + res[policy][1], res["VDNN_NONE"][0] + res["VDNN_NONE"][1]):
+            assert rel_err(a, b) < 1e-4, policy
+        assert abs(res[policy][2][0] - res["VDNN_NONE"][2][0]) < 1e-4
+
+
 def test_offload_bytes_and_overlap_are_reported(vdnn, oracle):
     net = vdnn.Network("VGG16_64", "VDNN_ALL", "VDNN_MEMORY_OPT_ALGO", batch_size=8, pool_bytes=6e9)
     try:

@@ -53,11 +53,11 @@ int vdnnContext::alloc(void** ptr, size_t bytes, int layer, int tag, bool isDyna
     return 0;
 }
 
-int vdnnContext::release(void* ptr, size_t bytes, int layer, int tag, std::initializer_list<cudaEvent_t> after) {
-    std::vector<cudaEvent_t> ev;
+int vdnnContext::release(void* ptr, size_t bytes, int layer, int tag, std::initializer_list<cudaStream_t> after) {
+    std::vector<cudaStream_t> st_list;
     if (!dry_run && !host_sync_per_layer)
-        for (cudaEvent_t e : after) if (e) ev.push_back(e);
-    const cnmemStatus_t st = vdnnPoolFreeAfter(ptr, ev.data(), static_cast<int>(ev.size()));
+        for (cudaStream_t s : after) if (s) st_list.push_back(s);
+    const cnmemStatus_t st = vdnnPoolFreeAfter(ptr, st_list.data(), static_cast<int>(st_list.size()));
     if (st != CNMEM_STATUS_SUCCESS) {
         fprintf(stderr, "\n[pool free failed with %s]\n", cnmemGetErrorString(st));
         return VDNN_ERR_STATE;
@@ -252,7 +252,7 @@ int Layer::convolutionForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, 
     if (_offloaded[layerId]) { const int o = offloadSrcData(_offloaded, _offloadedSrcData_h); if (o != 0) return o; }
     MARK(ev_fwd_done);
     if (workSpace == NULL && fwdWorkSpaceSize > 0)
-        return handle->release(curWorkSpace, fwdWorkSpaceSize, layerId, TAG_WS, {handle->event(handle->ev_fwd_done, layerId)});
+        return handle->release(curWorkSpace, fwdWorkSpaceSize, layerId, TAG_WS, {*stream_compute});
     return 0;
 }
 
@@ -275,7 +275,7 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
                            curWorkSpace, bwdDataWorkSpaceSize, *stream_compute));
     if (workSpace == NULL && bwdDataWorkSpaceSize > 0) {
         MARK(ev_bwd_done);
-        const int f = handle->release(curWorkSpace, bwdDataWorkSpaceSize, layerId, TAG_WS, {handle->event(handle->ev_bwd_done, layerId)});
+        const int f = handle->release(curWorkSpace, bwdDataWorkSpaceSize, layerId, TAG_WS, {*stream_compute});
         if (f != 0) return f;
     }
     // bias, then filter: gradient folded into the parameters (alpha = -lr, beta = 1), or written to
@@ -292,7 +292,7 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
                              bwdFilterWorkSpaceSize, *stream_compute));
     MARK(ev_bwd_done);
     if (workSpace == NULL && bwdFilterWorkSpaceSize > 0)
-        return handle->release(curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, {handle->event(handle->ev_bwd_done, layerId)});
+        return handle->release(curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, {*stream_compute});
     return 0;
 }
 
@@ -424,15 +424,16 @@ int Layer::offloadSrcData(bool* _offloaded, DATATYPE** _offloadedSrcData_h) {
     handle->record(2, layerId, TAG_SRC, static_cast<int64_t>(bytes));
     handle->offload_bytes += static_cast<int64_t>(bytes);
     if (handle->dry_run) return 0;
+    cudaStream_t lane = *stream_memory;
     cudaEvent_t ready = layerId == 0 ? handle->ev_input_ready : handle->ev_fwd_done[layerId - 1];
     if (handle->profiling) {
-        CU(cudaStreamWaitEvent(*stream_memory, ready, 0));
-        CU(cudaEventRecord(handle->pf_off_beg[layerId], *stream_memory));
+        CU(cudaStreamWaitEvent(lane, ready, 0));
+        CU(cudaEventRecord(handle->pf_off_beg[layerId], lane));
         ready = NULL;
     }
-    DEV(vdnn_offload(_offloadedSrcData_h[layerId], srcData, bytes, ready, NULL, *stream_memory));
-    if (handle->profiling) CU(cudaEventRecord(handle->pf_off_end[layerId], *stream_memory));
-    CU(cudaEventRecord(handle->ev_offload_done[layerId], *stream_memory));
+    DEV(vdnn_offload(_offloadedSrcData_h[layerId], srcData, bytes, ready, NULL, lane));
+    if (handle->profiling) CU(cudaEventRecord(handle->pf_off_end[layerId], lane));
+    CU(cudaEventRecord(handle->ev_offload_done[layerId], lane));
     return 0;
 }
 

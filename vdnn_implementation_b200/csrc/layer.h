@@ -59,7 +59,8 @@ struct vdnnContext {
     // Pool allocation for use on `streams`; emits a trace event.  Returns 0, -1 (out of memory with
     // isDynamic, as layer.h:119-125) or VDNN_ERR_OUT_OF_MEMORY.
     int alloc(void** ptr, size_t bytes, int layer, int tag, bool isDynamic, std::initializer_list<cudaStream_t> streams);
-    int release(void* ptr, size_t bytes, int layer, int tag, std::initializer_list<cudaEvent_t> after);
+    // Returns the block to the pool; its bytes stay fenced until the work enqueued so far on `after` is done.
+    int release(void* ptr, size_t bytes, int layer, int tag, std::initializer_list<cudaStream_t> after);
     int upload(void* dst, const void* src_h, size_t bytes);        // synchronous H2D (initialisation)
 };
 typedef vdnnContext* vdnnHandle_t;

@@ -497,7 +497,7 @@ int Network::forwardPropagation(bool isDynamic) {
                copy and the kernels that read it have finished */
             if (l != 0 && isOffload[l])
                 NET_TRY(ctx.release(layer[l]->SrcData(), sizeof(DATATYPE) * layer[l]->SrcDataSize(), l, TAG_SRC,
-                                    {ctx.dry_run ? NULL : ctx.ev_offload_done[l], ctx.dry_run ? NULL : ctx.ev_fwd_done[l]}));
+                                    {stream_memory, stream_compute}));
         }
         if (ctx.capture) NET_TRY(captureTensor(capDst[l], layer[l]->DstData(), layer[l]->DstDataSize()));
         ctx.record(4, l, TAG_NONE, 0);
@@ -582,20 +582,21 @@ int Network::backwardPropagation(bool isDynamic) {
             if (ctx.capture) NET_TRY(captureTensor(capGrad[l], layer[l]->GradData(), layer[l]->SrcDataSize()));
 
             /* Release dstData and diffData (network.cu:1172-1173) */
-            cudaEvent_t done = ctx.dry_run ? NULL : ctx.ev_bwd_done[l];
-            NET_TRY(ctx.release(layer[l]->DstData(), sizeof(DATATYPE) * layer[l]->DstDataSize(), l, TAG_DST, {done}));
-            NET_TRY(ctx.release(layer[l]->DiffData(), sizeof(DATATYPE) * layer[l]->DstDataSize(), l, TAG_DIFF, {done}));
+            NET_TRY(ctx.release(layer[l]->DstData(), sizeof(DATATYPE) * layer[l]->DstDataSize(), l, TAG_DST, {stream_compute}));
+            NET_TRY(ctx.release(layer[l]->DiffData(), sizeof(DATATYPE) * layer[l]->DstDataSize(), l, TAG_DIFF, {stream_compute}));
             ctx.record(5, l, TAG_NONE, 0);
             memoryLine("Bwd", l, layer[l]->BwdDataWorkSpaceSize() + layer[l]->BwdFilterWorkSpaceSize());
         }
-        cudaEvent_t done0 = ctx.dry_run ? NULL : ctx.ev_bwd_done[0];
-        NET_TRY(ctx.release(layer[0]->GradData(), sizeof(DATATYPE) * layer[0]->SrcDataSize(), 0, TAG_GRAD, {done0}));
+        NET_TRY(ctx.release(layer[0]->GradData(), sizeof(DATATYPE) * layer[0]->SrcDataSize(), 0, TAG_GRAD, {stream_compute}));
         // network.cu:1185 adopts the prefetched copy of layer 0 as the new input and forgets the old
         // buffer; unless that leak is asked for, the old buffer goes back to the pool here.
         if (supersededInput && ctx.fix_input_leak)
             NET_TRY(ctx.release(supersededInput, sizeof(DATATYPE) * getInputSize(), -1, TAG_INPUT,
-                                {ctx.dry_run ? NULL : ctx.ev_fwd_done[0], ctx.dry_run ? NULL : ctx.ev_offload_done[0]}));
+                                {stream_compute, stream_memory}));
         inputData = layer[0]->SrcData();
+        // The adopted buffer was filled by the prefetch stream; backward of layer 0 waited for that copy on
+        // the compute stream, so "input ready" is now: the next forward's offload of layer 0 must not read it earlier.
+        if (!ctx.dry_run) NET_CU(cudaEventRecord(ctx.ev_input_ready, stream_compute));
     }
     if (ctx.profiling) NET_CU(cudaEventRecord(ctx.pf_step_end, stream_compute));
     if (!ctx.dry_run) NET_CU(cudaEventRecord(ev_step_end, stream_compute));
@@ -746,6 +747,24 @@ int Network::getStats(vdnn_network_stats* out) {
             const float lo = std::max(c.a, k.a), hi = std::min(c.b, k.b);
             if (hi > lo) out->copy_overlap_ms += hi - lo;
         }
+    return VDNN_OK;
+}
+
+int Network::timeline(float* out) {
+    if (!out) return VDNN_ERR_BAD_ARG;
+    for (int i = 0; i < 8 * numLayers; ++i) out[i] = -1.0f;
+    if (!ctx.profiling || ctx.dry_run || stepCounter == 0) return VDNN_ERR_STATE;
+    NET_TRY(synchronize());
+    for (int l = 0; l < numLayers; ++l) {
+        cudaEvent_t ev[8] = {ctx.pf_fwd_beg[l], ctx.pf_fwd_end[l], isOffload[l] ? ctx.pf_off_beg[l] : NULL,
+                             isOffload[l] ? ctx.pf_off_end[l] : NULL, ctx.pf_bwd_beg[l], ctx.pf_bwd_end[l],
+                             isOffload[l] ? ctx.pf_pre_beg[l] : NULL, isOffload[l] ? ctx.pf_pre_end[l] : NULL};
+        for (int j = 0; j < 8; ++j) {
+            float ms = 0.0f;
+            if (ev[j] && cudaEventElapsedTime(&ms, ctx.pf_step_beg, ev[j]) == cudaSuccess) out[8 * l + j] = ms;
+        }
+    }
+    (void)cudaGetLastError();
     return VDNN_OK;
 }
 

@@ -59,6 +59,7 @@ public:
     int             writeTensor(int layerId, int kind, const float* src_h, size_t count);
     int             getStats(vdnn_network_stats* out);
     int             setProfiling(bool enabled);
+    int             timeline(float* out);
     int             enableDataParallel(int rank, int world, const char* unique_id128);
     int             weightChecksum(uint64_t* out);
 

@@ -86,6 +86,8 @@ int vdnn_network_trace_reset(vdnn_network* net) { NET(net); net->impl->context()
 int vdnn_network_get_stats(vdnn_network* net, vdnn_network_stats* out) { NET(net); return net->impl->getStats(out); }
 int vdnn_network_set_profiling(vdnn_network* net, int enabled) { NET(net); return net->impl->setProfiling(enabled != 0); }
 
+int vdnn_network_timeline(vdnn_network* net, float* out) { NET(net); return net->impl->timeline(out); }
+
 int vdnn_dp_unique_id(char* out128) { return vdnn::dp_unique_id(out128); }
 int vdnn_network_enable_dp(vdnn_network* net, int rank, int world, const char* id) { NET(net); return net->impl->enableDataParallel(rank, world, id); }
 int vdnn_network_weight_checksum(vdnn_network* net, uint64_t* out) { NET(net); return net->impl->weightChecksum(out); }

@@ -15,7 +15,7 @@ namespace {
 constexpr size_t kGranularity = 512;   // cnmem rounds every request up to 512 bytes
 
 struct Block { size_t size; bool free; };
-struct Fence { size_t begin, end; cudaEvent_t event; };
+struct Fence { size_t begin, end; cudaEvent_t event; unsigned long long seq; cudaStream_t stream; };
 
 struct Pool {
     std::mutex mu;
@@ -27,22 +27,56 @@ struct Pool {
     std::map<size_t, Block> blocks;     // offset -> block
     std::vector<Fence> fences;
     int fail_countdown = 0;
+    unsigned long long next_seq = 1;
+    std::vector<cudaEvent_t> spare_events;   // recycled fence events
 };
 Pool g_pool;
 
+void drop_finished_fences_locked();
+
 size_t round_up(size_t n) { return (n + kGranularity - 1) / kGranularity * kGranularity; }
 
-cnmemStatus_t alloc_locked(void** ptr, size_t size, size_t* off_out, size_t* len_out) {
+// 0 when no pending event covers any byte of [begin, end); otherwise the issue number of the youngest
+// such event.  Events are issued in program order, so a smaller number means "usable sooner".
+// Events recorded on one of the consumer's own streams cost nothing (stream order already covers them).
+bool is_consumer(cudaStream_t s, const cudaStream_t* consumers, int n) {
+    for (int i = 0; i < n; ++i) if (consumers[i] == s) return true;
+    return false;
+}
+
+unsigned long long range_readiness_locked(size_t begin, size_t end, const cudaStream_t* consumers, int n) {
+    unsigned long long youngest = 0;
+    for (const Fence& f : g_pool.fences)
+        if (f.begin < end && begin < f.end && f.seq > youngest && !is_consumer(f.stream, consumers, n)) youngest = f.seq;
+    return youngest;
+}
+
+// Best fit.  With consumer streams given, the block whose bytes those streams can use soonest wins even
+// when it is larger: first blocks with no pending event on another stream, then those whose youngest such
+// event was issued earliest.  The consumer then starts at once, or waits for old work that has probably
+// finished, instead of queueing behind the copy or kernel that just released the tightest-fitting block
+// (a prefetch target must not wait for compute, nor an activation for an offload).  The byte accounting
+// (used / peak) is the same either way; only the placement differs.
+cnmemStatus_t alloc_locked(void** ptr, size_t size, size_t* off_out, size_t* len_out,
+                           const cudaStream_t* consumers = nullptr, int num_consumers = 0) {
     if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
     if (!ptr) return CNMEM_STATUS_INVALID_ARGUMENT;
     if (size == 0) { *ptr = nullptr; return CNMEM_STATUS_SUCCESS; }
     if (g_pool.fail_countdown > 0 && --g_pool.fail_countdown == 0) return CNMEM_STATUS_OUT_OF_MEMORY;
     const size_t need = round_up(size);
     auto best = g_pool.blocks.end();
-    for (auto it = g_pool.blocks.begin(); it != g_pool.blocks.end(); ++it)
-        if (it->second.free && it->second.size >= need &&
-            (best == g_pool.blocks.end() || it->second.size < best->second.size))
+    unsigned long long best_ready = 0;
+    const bool rank = num_consumers > 0 && !g_pool.fences.empty();
+    for (auto it = g_pool.blocks.begin(); it != g_pool.blocks.end(); ++it) {
+        if (!it->second.free || it->second.size < need) continue;
+        // only the first `need` bytes of the block would be handed out
+        const unsigned long long ready = rank ? range_readiness_locked(it->first, it->first + need, consumers, num_consumers) : 0;
+        if (best == g_pool.blocks.end() || ready < best_ready ||
+            (ready == best_ready && it->second.size < best->second.size)) {
             best = it;
+            best_ready = ready;
+        }
+    }
     if (best == g_pool.blocks.end()) return CNMEM_STATUS_OUT_OF_MEMORY;
     const size_t off = best->first, rest = best->second.size - need;
     best->second.size = need;
@@ -81,11 +115,19 @@ cnmemStatus_t free_locked(void* ptr, size_t* off_out, size_t* len_out) {
 
 void drop_finished_fences_locked() {
     size_t keep = 0;
-    for (size_t i = 0; i < g_pool.fences.size(); ++i)
-        if (cudaEventQuery(g_pool.fences[i].event) == cudaErrorNotReady)
-            g_pool.fences[keep++] = g_pool.fences[i];
-    (void)cudaGetLastError();           // cudaErrorNotReady is sticky-free but clear it anyway
+    for (size_t i = 0; i < g_pool.fences.size(); ++i) {
+        if (cudaEventQuery(g_pool.fences[i].event) == cudaErrorNotReady) g_pool.fences[keep++] = g_pool.fences[i];
+        else g_pool.spare_events.push_back(g_pool.fences[i].event);
+    }
+    (void)cudaGetLastError();
     g_pool.fences.resize(keep);
+}
+
+void destroy_events_locked() {
+    for (const Fence& f : g_pool.fences) cudaEventDestroy(f.event);
+    for (cudaEvent_t e : g_pool.spare_events) cudaEventDestroy(e);
+    g_pool.fences.clear();
+    g_pool.spare_events.clear();
 }
 
 }  // namespace
@@ -122,6 +164,7 @@ cnmemStatus_t cnmemInit(int numDevices, const cnmemDevice_t* devices, unsigned) 
 cnmemStatus_t cnmemFinalize(void) {
     std::lock_guard<std::mutex> lock(g_pool.mu);
     if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
+    if (!g_pool.is_virtual) destroy_events_locked();
     cudaError_t e = g_pool.is_virtual ? cudaSuccess : cudaFree(g_pool.base);
     g_pool.base = nullptr;
     g_pool.blocks.clear();
@@ -175,27 +218,35 @@ const char* cnmemGetErrorString(cnmemStatus_t status) {
     }
 }
 
-cnmemStatus_t vdnnPoolFreeAfter(void* ptr, const cudaEvent_t* events, int numEvents) {
+cnmemStatus_t vdnnPoolFreeAfter(void* ptr, const cudaStream_t* streams, int numStreams) {
     std::lock_guard<std::mutex> lock(g_pool.mu);
     size_t off = 0, len = 0;
     cnmemStatus_t st = free_locked(ptr, &off, &len);
-    if (st != CNMEM_STATUS_SUCCESS || !ptr) return st;
-    for (int i = 0; i < numEvents && !g_pool.is_virtual; ++i)
-        if (events[i]) g_pool.fences.push_back(Fence{off, off + len, events[i]});
+    if (st != CNMEM_STATUS_SUCCESS || !ptr || g_pool.is_virtual) return st;
+    // one private event per stream, recorded now: it stands for "everything enqueued on that stream so far".
+    // Private events are never re-recorded while a fence holds them, so a fence cannot be extended by
+    // later work.
+    for (int i = 0; i < numStreams; ++i) {
+        cudaEvent_t ev = nullptr;
+        if (!g_pool.spare_events.empty()) { ev = g_pool.spare_events.back(); g_pool.spare_events.pop_back(); }
+        else if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
+        if (cudaEventRecord(ev, streams[i]) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
+        g_pool.fences.push_back(Fence{off, off + len, ev, g_pool.next_seq++, streams[i]});
+    }
     return CNMEM_STATUS_SUCCESS;
 }
 
 cnmemStatus_t vdnnPoolMallocFor(void** ptr, size_t size, const cudaStream_t* streams, int numStreams) {
     std::lock_guard<std::mutex> lock(g_pool.mu);
     size_t off = 0, len = 0;
-    cnmemStatus_t st = alloc_locked(ptr, size, &off, &len);
+    if (!g_pool.is_virtual && g_pool.ready) drop_finished_fences_locked();
+    cnmemStatus_t st = alloc_locked(ptr, size, &off, &len, streams, g_pool.is_virtual ? 0 : numStreams);
     if (st != CNMEM_STATUS_SUCCESS || size == 0) return st;
     if (g_pool.is_virtual) return CNMEM_STATUS_SUCCESS;
-    drop_finished_fences_locked();
     for (const Fence& f : g_pool.fences)
         if (f.begin < off + len && off < f.end)
             for (int s = 0; s < numStreams; ++s)
-                if (cudaStreamWaitEvent(streams[s], f.event, 0) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
+                if (streams[s] != f.stream && cudaStreamWaitEvent(streams[s], f.event, 0) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
     return CNMEM_STATUS_SUCCESS;
 }
 

@@ -136,6 +136,12 @@ class Network:
     def set_profiling(self, enabled=True):
         check(lib().vdnn_network_set_profiling(self._h, int(enabled)), "set_profiling")
 
+    def timeline(self):
+        """(num_layers, 8) array of ms since step start: fwd beg/end, offload beg/end, bwd beg/end, prefetch beg/end."""
+        out = np.empty(8 * self.num_layers, np.float32)
+        check(lib().vdnn_network_timeline(self._h, out.ctypes.data_as(C.c_void_p)), "timeline")
+        return out.reshape(self.num_layers, 8)
+
     def stats(self):
         s = abi.NetworkStats()
         check(lib().vdnn_network_get_stats(self._h, C.byref(s)), "get_stats")
