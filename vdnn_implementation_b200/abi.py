@@ -64,7 +64,8 @@ class NetworkStats(C.Structure):
 
 
 def lib_path():
-    return os.path.join(PKG, "libvdnn_b200.so")
+    """The in-tree shared object; VDNN_B200_LIB may point at another build of the same library."""
+    return os.environ.get("VDNN_B200_LIB") or os.path.join(PKG, "libvdnn_b200.so")
 
 
 _lib = None
@@ -145,6 +146,8 @@ def lib():
                               "(the package has no CPU or PyTorch fallback)")
         L = C.CDLL(path, mode=C.RTLD_GLOBAL)
         for name, (res, args) in SIGNATURES.items():
+            if os.environ.get("VDNN_B200_LIB") and not hasattr(L, name):
+                continue        # an experimental build may lack the newest entry points
             fn = getattr(L, name)
             fn.restype = res
             fn.argtypes = args

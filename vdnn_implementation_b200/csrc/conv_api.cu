@@ -61,6 +61,24 @@ __global__ void __launch_bounds__(256) reduce_partials_kernel(size_t n, int spli
     }
 }
 
+// wp[(tap*K + ko)*C + c] = w[(ko*C + c)*RS + tap]: the filter bank with the tap outermost, so that for one tap
+// the channels of an output filter are contiguous (what a tap-major reduction wants to read).
+__global__ void __launch_bounds__(256) pack_weights_tap_major(int K, int C, int RS, const float* __restrict__ w,
+                                                              float* __restrict__ wp) {
+    const size_t total = static_cast<size_t>(K) * C * RS;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int c = static_cast<int>(i % C);
+        const size_t t = i / C;
+        const int ko = static_cast<int>(t % K), tap = static_cast<int>(t / K);
+        wp[i] = w[(static_cast<size_t>(ko) * C + c) * RS + tap];
+    }
+}
+
+size_t packed_weight_bytes(const vdnn_conv_desc* d) {
+    return (static_cast<size_t>(d->k) * d->c * d->r * d->s * sizeof(float) + 255) / 256 * 256;
+}
+
 int stream_blocks(size_t n) {
     size_t want = ceil_div<size_t>(n, 256);
     const size_t cap = static_cast<size_t>(sm_count()) * 8;
@@ -143,7 +161,9 @@ XGather make_xgather(const vdnn_conv_desc* d, const float* x, int P, int Q) {
     g.x = x; g.C = d->c; g.H = d->h; g.W = d->w; g.R = d->r; g.S = d->s;
     g.pad_h = d->pad_h; g.pad_w = d->pad_w; g.stride_h = d->stride_h; g.stride_w = d->stride_w;
     g.n_pix = d->n * P * Q; g.n_filt = d->c * d->r * d->s;
+    g.Q = Q;
     g.div_pq = FastDiv(P * Q); g.div_q = FastDiv(Q); g.div_rs = FastDiv(d->r * d->s); g.div_s = FastDiv(d->s);
+    g.div_c = FastDiv(d->c);
     g.chw = d->c * d->h * d->w; g.hw = d->h * d->w;
     return g;
 }
@@ -189,7 +209,9 @@ size_t vdnn_conv_workspace_bytes(int op, int algo_mode, const vdnn_conv_desc* d)
     default: return 0;
     }
     const SplitPlan plan = plan_split(M, N, K);
-    return plan.splits > 1 ? static_cast<size_t>(plan.splits) * out * sizeof(float) : 0;
+    size_t bytes = plan.splits > 1 ? static_cast<size_t>(plan.splits) * out * sizeof(float) : 0;
+    if (op == VDNN_CONV_FWD) bytes += packed_weight_bytes(d);      // tap-major copy of the filter bank
+    return bytes;
 }
 
 int vdnn_conv_fwd(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* x, const float* w,
@@ -197,15 +219,29 @@ int vdnn_conv_fwd(const vdnn_conv_desc* d, int algo_mode, float alpha, const flo
     int P, Q;
     if (!x || !w || !y || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
     if (!fits_int32(d, P, Q)) return VDNN_ERR_UNSUPPORTED;
-    const int crs = d->c * d->r * d->s, pq = P * Q;
-    XGatherPixRows A; A.g = make_xgather(d, x, P, Q);
-    SplitDense B = make_dense(w, d->k, crs, crs, 1);
+    const int crs = d->c * d->r * d->s, pq = P * Q, rs = d->r * d->s;
     Epilogue e{};
     e.out = y; e.bias = bias; e.alpha = alpha; e.beta = beta;
     e.row_div = FastDiv(pq); e.row_hi = d->k * pq; e.row_lo = 1; e.col_stride = pq;
     const int M = d->n * pq;
+    cudaStream_t s = as_stream(stream);
+    if (algo_mode == VDNN_ALGO_PERF_OPT) {
+        // workspace variant: reduce tap-major (k = tap*C + c) against a tap-major copy of the weights
+        const size_t pack = packed_weight_bytes(d);
+        if (!workspace || workspace_bytes < pack) return VDNN_ERR_WORKSPACE;
+        float* wp = static_cast<float*>(workspace);
+        pack_weights_tap_major<<<stream_blocks(static_cast<size_t>(d->k) * crs), 256, 0, s>>>(d->k, d->c, rs, w, wp);
+        VDNN_LAUNCHED();
+        XGatherPixRowsTap A; A.g = make_xgather(d, x, P, Q);
+        SplitDense B = make_dense(wp, d->k, crs, d->c, 1);          // row ko at ko*C, k = (tap, c) at tap*K*C + c
+        B.col_div = FastDiv(d->c); B.col_hi = d->k * d->c; B.col_lo = 1;
+        return contract<XGatherPixRowsTap, SplitDense, false, true>(A, B, e, M, d->k, crs, static_cast<size_t>(M) * d->k, 0, algo_mode,
+                                                                    static_cast<char*>(workspace) + pack, workspace_bytes - pack, s);
+    }
+    XGatherPixRows A; A.g = make_xgather(d, x, P, Q);
+    SplitDense B = make_dense(w, d->k, crs, crs, 1);
     return contract<XGatherPixRows, SplitDense, false, true>(A, B, e, M, d->k, crs, static_cast<size_t>(M) * d->k, 0,
-                                                             algo_mode, workspace, workspace_bytes, as_stream(stream));
+                                                             algo_mode, workspace, workspace_bytes, s);
 }
 
 int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* w, const float* dy,
@@ -218,19 +254,21 @@ int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, cons
     A.dy = dy; A.K = d->k; A.P = P; A.Q = Q; A.R = d->r; A.S = d->s;
     A.pad_h = d->pad_h; A.pad_w = d->pad_w; A.stride_h = d->stride_h; A.stride_w = d->stride_w;
     A.n_pix = d->n * hw; A.n_cols = d->k * rs;
-    A.div_hw = FastDiv(hw); A.div_w = FastDiv(d->w); A.div_rs = FastDiv(rs); A.div_s = FastDiv(d->s);
+    A.div_hw = FastDiv(hw); A.div_w = FastDiv(d->w); A.div_k = FastDiv(d->k); A.div_s = FastDiv(d->s);
     A.div_sh = FastDiv(d->stride_h); A.div_sw = FastDiv(d->stride_w);
     A.kpq = d->k * pq; A.pq = pq;
-    // weights viewed as [c][(k, rs)]: offset = c*RS + k*C*RS + rs
+    // weights viewed as [c][(tap, ko)] with the same tap-major k as A: offset = c*RS + tap + ko*C*RS
     SplitDense B;
     B.p = w; B.rows = d->c; B.cols = d->k * rs;
     B.row_div = FastDiv(1u << 30); B.row_hi = 0; B.row_lo = rs;
-    B.col_div = FastDiv(rs); B.col_hi = d->c * rs; B.col_lo = 1;
+    B.col_div = FastDiv(d->k); B.col_hi = 1; B.col_lo = d->c * rs;
     Epilogue e{};
     e.out = dx; e.bias = nullptr; e.alpha = alpha; e.beta = beta;
     e.row_div = FastDiv(hw); e.row_hi = d->c * hw; e.row_lo = 1; e.col_stride = hw;
     const int M = d->n * hw;
-    return contract<DyGather, SplitDense, false, true>(A, B, e, M, d->c, d->k * rs, static_cast<size_t>(M) * d->c, 0,
+    // B is walked along its rows (channels, 36-byte stride) by neighbouring threads: along k it would be a
+    // stride of a whole filter (C*R*S floats)
+    return contract<DyGather, SplitDense, false, false>(A, B, e, M, d->c, d->k * rs, static_cast<size_t>(M) * d->c, 0,
                                                        algo_mode, workspace, workspace_bytes, as_stream(stream));
 }
 

@@ -129,26 +129,13 @@ struct Gather {
         }
     }
     __device__ __forceinline__ void fetch(const Op& op, int k0, int kend, int t) {
-        if (KC) {
-            typename Op::Col c[4];
+        if constexpr (KC) {
             const int kk = k0 + (t & 7) * 4;
+            const auto c = op.cols4(kk, kend);
 #pragma unroll
-            for (int e = 0; e < 4; ++e) { c[e] = op.col(kk + e); c[e].valid = c[e].valid && (kk + e) < kend; }
-#pragma unroll
-            for (int j = 0; j < PASSES; ++j)
-#pragma unroll
-                for (int e = 0; e < 4; ++e) v[j * 4 + e] = op.load(rows[j], c[e]);
+            for (int j = 0; j < PASSES; ++j) op.load4(rows[j], c, kk, &v[j * 4]);
         } else {
-            int kk = k0 + (t / ROWS) * KRUN;
-            typename Op::Col c = op.col(kk);
-#pragma unroll
-            for (int e = 0; e < KRUN; ++e) {
-                typename Op::Col ce = c;
-                ce.valid = ce.valid && kk < kend;
-                v[e] = op.load(rows[0], ce);
-                ++kk;
-                if (e + 1 < KRUN) op.next_col(c, kk);
-            }
+            op.template load_run<KRUN>(rows[0], k0 + (t / ROWS) * KRUN, kend, v);
         }
     }
     __device__ __forceinline__ void stash(char* hi_tile, char* lo_tile, int t) const {
