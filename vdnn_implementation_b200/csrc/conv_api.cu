@@ -75,6 +75,65 @@ __global__ void __launch_bounds__(256) pack_weights_tap_major(int K, int C, int 
     }
 }
 
+// wp[(tap*C + c)*K + ko] = w[(ko*C + c)*RS + tap]: tap outermost, output filters innermost (what the data
+// gradient's reduction over (tap, ko) wants to read for one input channel).
+__global__ void __launch_bounds__(256) pack_weights_tap_major_transposed(int K, int C, int RS, const float* __restrict__ w,
+                                                                         float* __restrict__ wp) {
+    const size_t total = static_cast<size_t>(K) * C * RS;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int ko = static_cast<int>(i % K);
+        const size_t t = i / K;
+        const int c = static_cast<int>(t % C), tap = static_cast<int>(t / C);
+        wp[i] = w[(static_cast<size_t>(ko) * C + c) * RS + tap];
+    }
+}
+
+// Data gradient for layers with very few input channels (the first layer: C = 3).  As a contraction it has
+// N = C columns, which would leave a 128 x 64 tensor-core tile almost empty; here one thread owns one input pixel
+// and all its channels, the filter bank sits in shared memory, and dy is read with unit stride across a warp.
+constexpr int SMALL_C_MAX = 4;
+__global__ void __launch_bounds__(256) dgrad_small_c_kernel(int N, int C, int H, int W, int K, int R, int S, int P, int Q,
+                                                            int pad_h, int pad_w, float alpha, float beta,
+                                                            const float* __restrict__ w, const float* __restrict__ dy,
+                                                            float* __restrict__ dx) {
+    extern __shared__ float w_s[];                       // [K][C][R*S], as stored
+    const int wcount = K * C * R * S;
+    for (int i = threadIdx.x; i < wcount; i += blockDim.x) w_s[i] = w[i];
+    __syncthreads();
+    const int hw = H * W, pq = P * Q, rs = R * S;
+    const long long total = static_cast<long long>(N) * hw;
+    for (long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total;
+         idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int n = static_cast<int>(idx / hw), rem = static_cast<int>(idx - static_cast<long long>(n) * hw);
+        const int h = rem / W, x = rem - h * W;
+        float acc[SMALL_C_MAX] = {0.f, 0.f, 0.f, 0.f};
+        const float* dyn = dy + static_cast<size_t>(n) * K * pq;
+        for (int r = 0; r < R; ++r) {
+            const int p = h + pad_h - r;
+            if (p < 0 || p >= P) continue;
+            for (int s = 0; s < S; ++s) {
+                const int q = x + pad_w - s;
+                if (q < 0 || q >= Q) continue;
+                const float* dp = dyn + p * Q + q;
+                const float* wp = w_s + r * S + s;
+                for (int k = 0; k < K; ++k) {
+                    const float g = __ldg(dp + static_cast<size_t>(k) * pq);
+#pragma unroll
+                    for (int c = 0; c < SMALL_C_MAX; ++c)
+                        if (c < C) acc[c] = fmaf(g, wp[(k * C + c) * rs], acc[c]);
+                }
+            }
+        }
+        for (int c = 0; c < C; ++c) {
+            float* o = dx + (static_cast<size_t>(n) * C + c) * hw + rem;
+            float v = alpha * acc[c];
+            if (beta != 0.0f) v = fmaf(beta, *o, v);
+            *o = v;
+        }
+    }
+}
+
 size_t packed_weight_bytes(const vdnn_conv_desc* d) {
     return (static_cast<size_t>(d->k) * d->c * d->r * d->s * sizeof(float) + 255) / 256 * 256;
 }
@@ -210,7 +269,7 @@ size_t vdnn_conv_workspace_bytes(int op, int algo_mode, const vdnn_conv_desc* d)
     }
     const SplitPlan plan = plan_split(M, N, K);
     size_t bytes = plan.splits > 1 ? static_cast<size_t>(plan.splits) * out * sizeof(float) : 0;
-    if (op == VDNN_CONV_FWD) bytes += packed_weight_bytes(d);      // tap-major copy of the filter bank
+    if (op == VDNN_CONV_FWD || op == VDNN_CONV_BWD_DATA) bytes += packed_weight_bytes(d);      // tap-major copy of the filter bank
     return bytes;
 }
 
@@ -250,6 +309,18 @@ int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, cons
     if (!w || !dy || !dx || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
     if (!fits_int32(d, P, Q)) return VDNN_ERR_UNSUPPORTED;
     const int rs = d->r * d->s, hw = d->h * d->w, pq = P * Q;
+    if (d->c <= SMALL_C_MAX && d->stride_h == 1 && d->stride_w == 1 &&
+        static_cast<size_t>(d->k) * d->c * rs * sizeof(float) <= 48 * 1024) {
+        const size_t smem = static_cast<size_t>(d->k) * d->c * rs * sizeof(float);
+        const long long total = static_cast<long long>(d->n) * hw;
+        long long blocks = (total + 255) / 256;
+        const long long cap = static_cast<long long>(sm_count()) * 8;
+        if (blocks > cap) blocks = cap;
+        dgrad_small_c_kernel<<<static_cast<int>(blocks), 256, smem, as_stream(stream)>>>(
+            d->n, d->c, d->h, d->w, d->k, d->r, d->s, P, Q, d->pad_h, d->pad_w, alpha, beta, w, dy, dx);
+        VDNN_LAUNCHED();
+        return VDNN_OK;
+    }
     DyGather A;
     A.dy = dy; A.K = d->k; A.P = P; A.Q = Q; A.R = d->r; A.S = d->s;
     A.pad_h = d->pad_h; A.pad_w = d->pad_w; A.stride_h = d->stride_h; A.stride_w = d->stride_w;
@@ -257,19 +328,32 @@ int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, cons
     A.div_hw = FastDiv(hw); A.div_w = FastDiv(d->w); A.div_k = FastDiv(d->k); A.div_s = FastDiv(d->s);
     A.div_sh = FastDiv(d->stride_h); A.div_sw = FastDiv(d->stride_w);
     A.kpq = d->k * pq; A.pq = pq;
-    // weights viewed as [c][(tap, ko)] with the same tap-major k as A: offset = c*RS + tap + ko*C*RS
-    SplitDense B;
-    B.p = w; B.rows = d->c; B.cols = d->k * rs;
-    B.row_div = FastDiv(1u << 30); B.row_hi = 0; B.row_lo = rs;
-    B.col_div = FastDiv(d->k); B.col_hi = 1; B.col_lo = d->c * rs;
     Epilogue e{};
     e.out = dx; e.bias = nullptr; e.alpha = alpha; e.beta = beta;
     e.row_div = FastDiv(hw); e.row_hi = d->c * hw; e.row_lo = 1; e.col_stride = hw;
     const int M = d->n * hw;
-    // B is walked along its rows (channels, 36-byte stride) by neighbouring threads: along k it would be a
-    // stride of a whole filter (C*R*S floats)
+    cudaStream_t s = as_stream(stream);
+    SplitDense B;
+    B.p = w; B.rows = d->c; B.cols = d->k * rs;
+    B.row_div = FastDiv(1u << 30); B.row_hi = 0;
+    B.col_div = FastDiv(d->k);
+    if (algo_mode == VDNN_ALGO_PERF_OPT) {
+        // workspace variant: a copy of the weights laid out [tap][c][ko], so that the reduction index (tap, ko)
+        // is contiguous for a channel and is read with 16-byte loads
+        const size_t pack = packed_weight_bytes(d);
+        if (!workspace || workspace_bytes < pack) return VDNN_ERR_WORKSPACE;
+        float* wp = static_cast<float*>(workspace);
+        pack_weights_tap_major_transposed<<<stream_blocks(static_cast<size_t>(d->k) * d->c * rs), 256, 0, s>>>(d->k, d->c, rs, w, wp);
+        VDNN_LAUNCHED();
+        B.p = wp; B.row_lo = d->k; B.col_hi = d->c * d->k; B.col_lo = 1;
+        return contract<DyGather, SplitDense, false, true>(A, B, e, M, d->c, d->k * rs, static_cast<size_t>(M) * d->c, 0, algo_mode,
+                                                           static_cast<char*>(workspace) + pack, workspace_bytes - pack, s);
+    }
+    // zero-workspace variant: the KCRS weights viewed as [c][(tap, ko)]: offset = c*RS + tap + ko*C*RS.  B is walked
+    // along its rows (channels, 36-byte stride) by neighbouring threads: along k it would be a whole filter apart.
+    B.row_lo = rs; B.col_hi = 1; B.col_lo = d->c * rs;
     return contract<DyGather, SplitDense, false, false>(A, B, e, M, d->c, d->k * rs, static_cast<size_t>(M) * d->c, 0,
-                                                       algo_mode, workspace, workspace_bytes, as_stream(stream));
+                                                        algo_mode, workspace, workspace_bytes, s);
 }
 
 int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* x, const float* dy,

@@ -4,17 +4,17 @@
 // with fp32 accumulation in tensor memory (TMEM).
 //
 // One CTA computes a 128 x BN tile of D (BN = 64 or 128) over a K range in steps of 32:
-//   warps 0-7  producers: gather the 128 x 32 A tile and BN x 32 B tile straight from the NCHW /
+//   warps 0-15 producers: gather the 128 x 32 A tile and BN x 32 B tile straight from the NCHW /
 //              KCRS tensors (gemm_operands.cuh), split every value into hi / lo, and store both
 //              into shared memory in the K-major, 128-byte-swizzled layout tcgen05.mma reads;
 //              they also collect the per-stage sums from TMEM (tcgen05.ld) and run the epilogue:
 //              alpha / beta / bias / split-K handling, coalesced stores.
-//   warp 8     allocates TMEM; one elected lane issues tcgen05.mma (3 per 8-wide k slice, 12 per
+//   warp 16    allocates TMEM; one elected lane issues tcgen05.mma (3 per 8-wide k slice, 12 per
 //              stage) into one of two TMEM accumulator buffers and tcgen05.commit to hand the stage
 //              back and to publish that buffer.  The producers add each finished buffer into fp32
 //              registers (round-to-nearest adds), so no accumulation chain inside the tensor core
 //              is longer than one stage.
-// Stages are handed over with mbarriers (full: 256 producer arrivals, empty: one commit).  Every
+// Stages are handed over with mbarriers (full: one arrival per producer thread, empty: one commit).  Every
 // wait is bounded: on expiry the thread records an error code in g_tc_error, stops waiting, and
 // the CTA still runs its common exit path (barrier, TMEM release).
 #pragma once
@@ -24,7 +24,12 @@
 namespace vdnn {
 namespace tc {
 
-constexpr int BM = 128, BK = 32, PRODUCERS = 256, THREADS = PRODUCERS + 32;
+#ifndef VDNN_TC_PRODUCERS
+#define VDNN_TC_PRODUCERS 512
+#endif
+constexpr int BM = 128, BK = 32, PRODUCERS = VDNN_TC_PRODUCERS, THREADS = PRODUCERS + 32;
+constexpr int PRODUCER_WARPS = PRODUCERS / 32;      // 8 or 16; the MMA warp comes after them
+static_assert(PRODUCERS == 256 || PRODUCERS == 512, "producer mappings are written for 256 or 512 threads");
 constexpr int A_TILE_BYTES = BM * BK * 4;              // 16 KB, one per hi / lo
 constexpr unsigned long long SPIN_CYCLES = 4000000000ull;   // ~2 s at 1.9 GHz
 constexpr unsigned SPIN_TRIES = 1u << 26;
@@ -114,8 +119,10 @@ __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
 //               32 / (256 / ROWS) consecutive k: a warp reads 32 consecutive rows of one k.
 template <class Op, bool KC, int ROWS>
 struct Gather {
-    static constexpr int PASSES = ROWS / 32;                 // KC
-    static constexpr int KRUN = BK / (PRODUCERS / ROWS);     // !KC: 16 (ROWS = 128) or 8 (ROWS = 64)
+    static constexpr int ROWS_PER_PASS = PRODUCERS / 8;      // KC: 8 threads cover one 128-byte row
+    static constexpr int PASSES = ROWS / ROWS_PER_PASS;
+    static constexpr int KRUN = BK / (PRODUCERS / ROWS);     // !KC: consecutive k per thread (4 .. 16)
+    static_assert(PASSES >= 1 && KRUN >= 4, "tile too small for the producer count");
     static constexpr int COUNT = KC ? PASSES * 4 : KRUN;
     typename Op::Row rows[KC ? PASSES : 1];
     float v[COUNT];
@@ -123,7 +130,7 @@ struct Gather {
     __device__ __forceinline__ void init(const Op& op, int row0, int t) {
         if (KC) {
 #pragma unroll
-            for (int j = 0; j < PASSES; ++j) rows[j] = op.row(row0 + (t >> 3) + 32 * j);
+            for (int j = 0; j < PASSES; ++j) rows[j] = op.row(row0 + (t >> 3) + ROWS_PER_PASS * j);
         } else {
             rows[0] = op.row(row0 + t % ROWS);
         }
@@ -145,7 +152,7 @@ struct Gather {
                 float4 h, l;
                 split_tf32(v[j * 4 + 0], h.x, l.x); split_tf32(v[j * 4 + 1], h.y, l.y);
                 split_tf32(v[j * 4 + 2], h.z, l.z); split_tf32(v[j * 4 + 3], h.w, l.w);
-                const uint32_t o = swz((t >> 3) + 32 * j, t & 7);
+                const uint32_t o = swz((t >> 3) + ROWS_PER_PASS * j, t & 7);
                 *reinterpret_cast<float4*>(hi_tile + o) = h;
                 *reinterpret_cast<float4*>(lo_tile + o) = l;
             }
@@ -195,7 +202,7 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
     // buffer (a chain of 12 MMAs) while the previous block's buffer is added into fp32 registers.
     // Keeping the in-TMEM chains short matters for accuracy: the tensor core truncates when it adds
     // into its accumulator, and over thousands of chained MMAs that bias reaches 1e-5 relative.
-    if (warp == 8) {
+    if (warp == PRODUCER_WARPS) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -204,14 +211,14 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp < 8) {
+    if (warp < PRODUCER_WARPS) {
         // ------------------------------------------------------------------ producers
         Gather<OpA, AKC, BM> ga;
         Gather<OpB, BKC, BN> gb;
         ga.init(opa, m0, t);
         gb.init(opb, n0, t);
-        // this thread owns row (warp & 3) * 32 + lane of the tile and half of its columns
-        constexpr int NACC = BN / 2;
+        // this thread owns row (warp & 3) * 32 + lane of the tile and a slice of its columns
+        constexpr int NACC = BN / (PRODUCER_WARPS / 4);
         const int col_beg = (warp >> 2) * NACC;
         const uint32_t tmem_mine = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(col_beg);
         float acc[NACC];
@@ -298,7 +305,7 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 8) {
+    if (warp == PRODUCER_WARPS) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
     }

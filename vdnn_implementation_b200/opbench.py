@@ -28,18 +28,42 @@ def timeit(fn, reps):
     return a.elapsed_time(b) / reps
 
 
+def elementwise(ops, n, args):
+    """ReLU and 2x2/s2 max-pool, forward and backward, on the first VGG16 activation shape (64 x 224 x 224 per image).
+    GB/s = algorithmic bytes (each tensor the layer must read or write, once) / time."""
+    c, h = 64, 224
+    count = n * c * h * h
+    x = torch.randn(n, c, h, h, device="cuda")
+    y = torch.empty_like(x)
+    dy = torch.randn_like(x)
+    dx = torch.empty_like(x)
+    yp = torch.empty(n, c, h // 2, h // 2, device="cuda")
+    dyp = torch.randn_like(yp)
+    cases = [
+        ("relu_fwd", lambda: ops.relu_fwd(count, x, y), 8.0 * count),
+        ("relu_bwd", lambda: ops.relu_bwd(count, y, dy, x, dx), 12.0 * count),
+        ("maxpool_fwd", lambda: ops.maxpool_fwd(n, c, h, h, (2, 2), (2, 2), x, yp), 4.0 * (count + count / 4)),
+        ("maxpool_bwd", lambda: ops.maxpool_bwd(n, c, h, h, (2, 2), (2, 2), yp, dyp, x, dx), 4.0 * (2 * count + count / 4)),
+    ]
+    for name, fn, nbytes in cases:
+        ms = timeit(fn, args.reps)
+        print(f"{name:12s} {count} elements  {ms:7.3f} ms  {nbytes / ms / 1e6:7.0f} GB/s", flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--engine", default="tcgen05", choices=["ffma", "tcgen05"])
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--layer", type=int, default=-1, help="index into the VGG16 shape list; -1 = all")
-    ap.add_argument("--op", default="all", choices=["all", "fwd", "dgrad", "wgrad"])
+    ap.add_argument("--op", default="all", choices=["all", "fwd", "dgrad", "wgrad", "elementwise"])
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--algo", type=int, default=1, help="0 MEMORY_OPT, 1 PERF_OPT")
     args = ap.parse_args()
     ops = v.ops
     ops.set_engine({"ffma": v.ENGINE_FFMA, "tcgen05": v.ENGINE_TCGEN05}[args.engine])
     n = args.batch
+    if args.op == "elementwise":
+        return elementwise(ops, n, args)
     total = {"fwd": 0.0, "dgrad": 0.0, "wgrad": 0.0}
     flops = 0.0
     for idx, (c, k, h) in enumerate(SHAPES):
