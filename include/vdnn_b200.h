@@ -106,7 +106,7 @@ int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, co
  *
  * Same result as vdnn_conv_bwd_filter with VDNN_ALGO_PERF_OPT (fixed-order, deterministic split-K
  * sums), but the per-split partial sums live in a scratch array that is part of the library image
- * (a file-scope __device__ array of VDNN_STATIC_SCRATCH_BYTES = 24 MiB, resident on every GPU that
+ * (a file-scope __device__ array of VDNN_STATIC_SCRATCH_BYTES = 16 MiB, resident on every GPU that
  * loads the library until the process exits) instead of caller-provided workspace.  It is meant for
  * hosts that fix their device-memory budget at start-up and must not allocate afterwards -- a
  * plugin loaded into a process whose allocator it cannot reach, or a steady-state loop that must
@@ -121,7 +121,7 @@ int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, co
  *   - All calls on a device share the one array, which keeps whatever the last call left in it.
  *     Every element a call reads was written by that same call, so nothing has to be cleared; but
  *     two calls that overlap on the GPU (different streams without ordering) race on it. */
-#define VDNN_STATIC_SCRATCH_BYTES (24u << 20)
+#define VDNN_STATIC_SCRATCH_BYTES (16u << 20)
 int vdnn_conv_bwd_filter_static(const vdnn_conv_desc* d, float alpha, const float* x, const float* dy,
                                 float beta, float* dw, void* stream);
 

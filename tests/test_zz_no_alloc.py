@@ -4,7 +4,7 @@ Some hosts of this library cannot allocate device memory once they are running: 
 is fixed at start-up, or they sit inside a process whose allocator they cannot reach, or an
 allocation's implicit device-wide synchronisation is not acceptable in their steady-state loop.
 They have no buffer to pass as `workspace`, so this entry point keeps the split-K partial sums in a
-24 MiB array that is part of the library image.  The file is named so that pytest collects it last.
+16 MiB array that is part of the library image.  The file is named so that pytest collects it last.
 """
 import numpy as np
 import pytest
@@ -51,7 +51,7 @@ def test_static_scratch_matches_workspace_entry_point_twice(vdnn):
 
 def test_static_scratch_refuses_what_does_not_fit(vdnn):
     ops = vdnn.ops
-    # 512 -> 512 channels at 14x14: few output tiles, many splits, 27 MiB of partial sums, beyond the 24 MiB array
+    # 512 -> 512 channels at 14x14: few output tiles, many splits, 18 MiB of partial sums, beyond the 16 MiB array
     d = ops.conv_desc(8, 512, 14, 14, 512, 3, 3, (1, 1), (1, 1))
     assert ops.conv_workspace_bytes(2, 1, d) > ops.STATIC_SCRATCH_BYTES
     x = torch.zeros(8, 512, 14, 14, device="cuda")

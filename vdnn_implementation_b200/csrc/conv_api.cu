@@ -15,16 +15,18 @@ int g_engine = VDNN_ENGINE_AUTO;
 
 struct SplitPlan { int splits; int k_chunk; };
 
-// Split K so that roughly two waves of 128x128 tiles exist, keeping at least 64 k per split.
+// Split K so that the grid is as close to two full waves of 128x128 tiles as it can get without exceeding them
+// (a third, nearly empty wave would cost as much as a full one), keeping at least 64 k per split.
 SplitPlan plan_split(int M, int N, int K) {
     const long tiles = static_cast<long>(ceil_div(M, 128)) * ceil_div(N, 128);
     const int sms = sm_count();
     int splits = 1;
     if (tiles < sms) {
-        splits = static_cast<int>(ceil_div<long>(2L * sms, tiles));
+        splits = static_cast<int>((2L * sms) / tiles);
         const int max_by_k = K / 64 > 0 ? K / 64 : 1;
         if (splits > max_by_k) splits = max_by_k;
         if (splits > 1024) splits = 1024;
+        if (splits < 1) splits = 1;
     }
     int k_chunk = ceil_div(ceil_div(K, splits), 32) * 32;      // multiple of both engines' k tile
     if (k_chunk < 32) k_chunk = 32;
@@ -58,34 +60,6 @@ __global__ void __launch_bounds__(256) reduce_partials_kernel(size_t n, int spli
         float v = alpha * acc;
         if (beta != 0.0f) v = fmaf(beta, out[i], v);
         out[i] = v;
-    }
-}
-
-// wp[(tap*K + ko)*C + c] = w[(ko*C + c)*RS + tap]: the filter bank with the tap outermost, so that for one tap
-// the channels of an output filter are contiguous (what a tap-major reduction wants to read).
-__global__ void __launch_bounds__(256) pack_weights_tap_major(int K, int C, int RS, const float* __restrict__ w,
-                                                              float* __restrict__ wp) {
-    const size_t total = static_cast<size_t>(K) * C * RS;
-    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int c = static_cast<int>(i % C);
-        const size_t t = i / C;
-        const int ko = static_cast<int>(t % K), tap = static_cast<int>(t / K);
-        wp[i] = w[(static_cast<size_t>(ko) * C + c) * RS + tap];
-    }
-}
-
-// wp[(tap*C + c)*K + ko] = w[(ko*C + c)*RS + tap]: tap outermost, output filters innermost (what the data
-// gradient's reduction over (tap, ko) wants to read for one input channel).
-__global__ void __launch_bounds__(256) pack_weights_tap_major_transposed(int K, int C, int RS, const float* __restrict__ w,
-                                                                         float* __restrict__ wp) {
-    const size_t total = static_cast<size_t>(K) * C * RS;
-    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int ko = static_cast<int>(i % K);
-        const size_t t = i / K;
-        const int c = static_cast<int>(t % C), tap = static_cast<int>(t / C);
-        wp[i] = w[(static_cast<size_t>(ko) * C + c) * RS + tap];
     }
 }
 
@@ -134,8 +108,11 @@ __global__ void __launch_bounds__(256) dgrad_small_c_kernel(int N, int C, int H,
     }
 }
 
-size_t packed_weight_bytes(const vdnn_conv_desc* d) {
-    return (static_cast<size_t>(d->k) * d->c * d->r * d->s * sizeof(float) + 255) / 256 * 256;
+// PERF_OPT scratch for the weight operand of forward (N = K filters) and data gradient (N = C channels): images of
+// its shared-memory tiles, split into tf32 hi / lo halves, that the kernel fetches with bulk copies.
+size_t packed_weight_bytes(const vdnn_conv_desc* d, int op) {
+    const int red = (op == VDNN_CONV_FWD ? d->c : d->k) * d->r * d->s;
+    return tc::bulk_bytes(op == VDNN_CONV_FWD ? d->k : d->c, red);
 }
 
 int stream_blocks(size_t n) {
@@ -147,9 +124,9 @@ int stream_blocks(size_t n) {
 
 template <class OpA, class OpB, bool AKC, bool BKC>
 int run_engine(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K, int splits, int k_chunk,
-               cudaStream_t stream) {
+               cudaStream_t stream, char* b_tiles = nullptr) {
     if (g_engine != VDNN_ENGINE_FFMA && tc::supported<OpA, OpB>(M, N, K)) {
-        return tc::launch<OpA, OpB, AKC, BKC>(a, b, epi, M, N, K, splits, k_chunk, stream);
+        return tc::launch<OpA, OpB, AKC, BKC>(a, b, epi, M, N, K, splits, k_chunk, stream, b_tiles);
     }
     if (g_engine == VDNN_ENGINE_TCGEN05) return VDNN_ERR_UNSUPPORTED;
     return ffma::launch<OpA, OpB, AKC, BKC>(a, b, epi, M, N, K, splits, k_chunk, stream);
@@ -159,12 +136,12 @@ int run_engine(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, in
 // dense_elems > 0 says the output is one dense block of that many floats (needed for PARTIAL).
 template <class OpA, class OpB, bool AKC, bool BKC>
 int contract(const OpA& a, const OpB& b, Epilogue epi, int M, int N, int K, size_t dense_elems, int ld_rows,
-             int algo_mode, void* ws, size_t ws_bytes, cudaStream_t stream) {
+             int algo_mode, void* ws, size_t ws_bytes, cudaStream_t stream, char* b_tiles = nullptr) {
     SplitPlan plan = plan_split(M, N, K);
     if (epi.bias) { plan.splits = 1; plan.k_chunk = ceil_div(K, 32) * 32; }
     if (plan.splits == 1) {
         epi.mode = EPI_DIRECT;
-        return run_engine<OpA, OpB, AKC, BKC>(a, b, epi, M, N, K, 1, plan.k_chunk, stream);
+        return run_engine<OpA, OpB, AKC, BKC>(a, b, epi, M, N, K, 1, plan.k_chunk, stream, b_tiles);
     }
     if (algo_mode == VDNN_ALGO_PERF_OPT && dense_elems > 0) {
         const size_t need = static_cast<size_t>(plan.splits) * dense_elems * sizeof(float);
@@ -173,7 +150,7 @@ int contract(const OpA& a, const OpB& b, Epilogue epi, int M, int N, int K, size
         part.mode = EPI_PARTIAL;
         part.out = static_cast<float*>(ws);
         part.partial_stride = dense_elems;
-        int st = run_engine<OpA, OpB, AKC, BKC>(a, b, part, M, N, K, plan.splits, plan.k_chunk, stream);
+        int st = run_engine<OpA, OpB, AKC, BKC>(a, b, part, M, N, K, plan.splits, plan.k_chunk, stream, b_tiles);
         if (st != VDNN_OK) return st;
         reduce_partials_kernel<<<stream_blocks(dense_elems), 256, 0, stream>>>(dense_elems, plan.splits, epi.alpha, epi.beta,
                                                                              static_cast<const float*>(ws), epi.out);
@@ -195,7 +172,7 @@ int contract(const OpA& a, const OpB& b, Epilogue epi, int M, int N, int K, size
         }
     }
     epi.mode = EPI_ATOMIC;
-    return run_engine<OpA, OpB, AKC, BKC>(a, b, epi, M, N, K, plan.splits, plan.k_chunk, stream);
+    return run_engine<OpA, OpB, AKC, BKC>(a, b, epi, M, N, K, plan.splits, plan.k_chunk, stream, b_tiles);
 }
 
 bool valid_desc(const vdnn_conv_desc* d, int* P, int* Q) {
@@ -269,7 +246,7 @@ size_t vdnn_conv_workspace_bytes(int op, int algo_mode, const vdnn_conv_desc* d)
     }
     const SplitPlan plan = plan_split(M, N, K);
     size_t bytes = plan.splits > 1 ? static_cast<size_t>(plan.splits) * out * sizeof(float) : 0;
-    if (op == VDNN_CONV_FWD || op == VDNN_CONV_BWD_DATA) bytes += packed_weight_bytes(d);      // tap-major copy of the filter bank
+    if (op == VDNN_CONV_FWD || op == VDNN_CONV_BWD_DATA) bytes += packed_weight_bytes(d, op);
     return bytes;
 }
 
@@ -285,17 +262,16 @@ int vdnn_conv_fwd(const vdnn_conv_desc* d, int algo_mode, float alpha, const flo
     const int M = d->n * pq;
     cudaStream_t s = as_stream(stream);
     if (algo_mode == VDNN_ALGO_PERF_OPT) {
-        // workspace variant: reduce tap-major (k = tap*C + c) against a tap-major copy of the weights
-        const size_t pack = packed_weight_bytes(d);
+        // workspace variant: reduce tap-major (k = tap*C + c: one bounds test per run of channels); the weights, read
+        // through the matching view ko*CRS + c*RS + tap, are packed once into tile images that the kernel bulk-copies
+        const size_t pack = packed_weight_bytes(d, VDNN_CONV_FWD);
         if (!workspace || workspace_bytes < pack) return VDNN_ERR_WORKSPACE;
-        float* wp = static_cast<float*>(workspace);
-        pack_weights_tap_major<<<stream_blocks(static_cast<size_t>(d->k) * crs), 256, 0, s>>>(d->k, d->c, rs, w, wp);
-        VDNN_LAUNCHED();
         XGatherPixRowsTap A; A.g = make_xgather(d, x, P, Q);
-        SplitDense B = make_dense(wp, d->k, crs, d->c, 1);          // row ko at ko*C, k = (tap, c) at tap*K*C + c
-        B.col_div = FastDiv(d->c); B.col_hi = d->k * d->c; B.col_lo = 1;
+        SplitDense B = make_dense(w, d->k, crs, crs, 1);
+        B.col_div = FastDiv(d->c); B.col_hi = 1; B.col_lo = rs;
+        char* tiles = (g_engine != VDNN_ENGINE_FFMA && (reinterpret_cast<uintptr_t>(workspace) & 127u) == 0) ? static_cast<char*>(workspace) : nullptr;
         return contract<XGatherPixRowsTap, SplitDense, false, true>(A, B, e, M, d->k, crs, static_cast<size_t>(M) * d->k, 0, algo_mode,
-                                                                    static_cast<char*>(workspace) + pack, workspace_bytes - pack, s);
+                                                                    static_cast<char*>(workspace) + pack, workspace_bytes - pack, s, tiles);
     }
     XGatherPixRows A; A.g = make_xgather(d, x, P, Q);
     SplitDense B = make_dense(w, d->k, crs, crs, 1);
@@ -337,21 +313,17 @@ int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, cons
     B.p = w; B.rows = d->c; B.cols = d->k * rs;
     B.row_div = FastDiv(1u << 30); B.row_hi = 0;
     B.col_div = FastDiv(d->k);
+    B.row_lo = rs; B.col_hi = 1; B.col_lo = d->c * rs;      // KCRS weights viewed as [c][(tap, ko)]: offset c*RS + tap + ko*C*RS
     if (algo_mode == VDNN_ALGO_PERF_OPT) {
-        // workspace variant: a copy of the weights laid out [tap][c][ko], so that the reduction index (tap, ko)
-        // is contiguous for a channel and is read with 16-byte loads
-        const size_t pack = packed_weight_bytes(d);
+        // workspace variant: that view is packed once into tile images that the kernel bulk-copies
+        const size_t pack = packed_weight_bytes(d, VDNN_CONV_BWD_DATA);
         if (!workspace || workspace_bytes < pack) return VDNN_ERR_WORKSPACE;
-        float* wp = static_cast<float*>(workspace);
-        pack_weights_tap_major_transposed<<<stream_blocks(static_cast<size_t>(d->k) * d->c * rs), 256, 0, s>>>(d->k, d->c, rs, w, wp);
-        VDNN_LAUNCHED();
-        B.p = wp; B.row_lo = d->k; B.col_hi = d->c * d->k; B.col_lo = 1;
-        return contract<DyGather, SplitDense, false, true>(A, B, e, M, d->c, d->k * rs, static_cast<size_t>(M) * d->c, 0, algo_mode,
-                                                           static_cast<char*>(workspace) + pack, workspace_bytes - pack, s);
+        char* tiles = (g_engine != VDNN_ENGINE_FFMA && (reinterpret_cast<uintptr_t>(workspace) & 127u) == 0) ? static_cast<char*>(workspace) : nullptr;
+        return contract<DyGather, SplitDense, false, false>(A, B, e, M, d->c, d->k * rs, static_cast<size_t>(M) * d->c, 0, algo_mode,
+                                                            static_cast<char*>(workspace) + pack, workspace_bytes - pack, s, tiles);
     }
-    // zero-workspace variant: the KCRS weights viewed as [c][(tap, ko)]: offset = c*RS + tap + ko*C*RS.  B is walked
-    // along its rows (channels, 36-byte stride) by neighbouring threads: along k it would be a whole filter apart.
-    B.row_lo = rs; B.col_hi = 1; B.col_lo = d->c * rs;
+    // zero-workspace variant: B is walked along its rows (channels, 36-byte stride) by neighbouring threads: along k it
+    // would be a whole filter apart.
     return contract<DyGather, SplitDense, false, false>(A, B, e, M, d->c, d->k * rs, static_cast<size_t>(M) * d->c, 0,
                                                         algo_mode, workspace, workspace_bytes, s);
 }

@@ -171,9 +171,14 @@ struct Gather {
     }
 };
 
-template <class OpA, class OpB, bool AKC, bool BKC, int BN>
+// BBULK: the B operand was packed beforehand into images of its shared-memory tiles (hi and lo halves,
+// swizzled, zero-padded; see pack_b_tiles_kernel), one image per (n tile, k block).  A producer thread then
+// fetches a stage's B tiles with a single bulk asynchronous copy (the TMA engine, no tensor map needed for a
+// contiguous image) that reports its bytes to the stage's "full" barrier; the producers only gather A.
+template <class OpA, class OpB, bool AKC, bool BKC, int BN, bool BBULK>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int K, int k_chunk) {
+gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int K, int k_chunk,
+            const char* __restrict__ b_tiles, int kblocks_total) {
     typedef Config<BN> Cfg;
     constexpr int S = Cfg::STAGES;
     extern __shared__ char smem_raw[];
@@ -216,7 +221,9 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
         Gather<OpA, AKC, BM> ga;
         Gather<OpB, BKC, BN> gb;
         ga.init(opa, m0, t);
-        gb.init(opb, n0, t);
+        if (!BBULK) gb.init(opb, n0, t);
+        const char* b_src = BBULK ? b_tiles + (static_cast<size_t>(blockIdx.y) * kblocks_total + kbeg / BK) * (2 * Cfg::B_TILE_BYTES)
+                                  : nullptr;
         // this thread owns row (warp & 3) * 32 + lane of the tile and a slice of its columns
         constexpr int NACC = BN / (PRODUCER_WARPS / 4);
         const int col_beg = (warp >> 2) * NACC;
@@ -243,7 +250,7 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         };
 
-        if (nkb > 0) { ga.fetch(opa, kbeg, kend, t); gb.fetch(opb, kbeg, kend, t); }
+        if (nkb > 0) { ga.fetch(opa, kbeg, kend, t); if (!BBULK) gb.fetch(opb, kbeg, kend, t); }
         for (int i = 0; i < nkb && alive; ++i) {
             const int s = i % S;
             const uint32_t phase = static_cast<uint32_t>(i / S) & 1u;
@@ -254,14 +261,25 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { atomicCAS(&g_tc_error, 0, 101); alive = false; break; }
             char* st = tiles + s * Cfg::STAGE_BYTES;
+            if (BBULK) {
+                // the stage is free: one thread announces the bytes and starts the copy of both B halves
+                if (t == 0) {
+                    const uint32_t bar = smem_u32(&bars[s]), dst = smem_u32(st + 2 * A_TILE_BYTES);
+                    const char* src = b_src + static_cast<size_t>(i) * (2 * Cfg::B_TILE_BYTES);
+                    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(2 * Cfg::B_TILE_BYTES) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(dst), "l"(src), "r"(2 * Cfg::B_TILE_BYTES), "r"(bar) : "memory");
+                }
+            } else {
+                gb.stash(st + 2 * A_TILE_BYTES, st + 2 * A_TILE_BYTES + Cfg::B_TILE_BYTES, t);
+            }
             ga.stash(st, st + A_TILE_BYTES, t);
-            gb.stash(st + 2 * A_TILE_BYTES, st + 2 * A_TILE_BYTES + Cfg::B_TILE_BYTES, t);
             // make the generic-proxy stores visible to the tensor core (async proxy), then publish
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(smem_u32(&bars[s]));
             if (i + 1 < nkb) {
                 ga.fetch(opa, kbeg + (i + 1) * BK, kend, t);
-                gb.fetch(opb, kbeg + (i + 1) * BK, kend, t);
+                if (!BBULK) gb.fetch(opb, kbeg + (i + 1) * BK, kend, t);
             }
         }
         if (alive && nkb >= 2) drain(nkb - 2);
@@ -314,29 +332,78 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
 template <class OpA, class OpB>
 inline bool supported(int M, int N, int K) { return M >= 1 && N >= 1 && K >= 1; }
 
-template <class OpA, class OpB, bool AKC, bool BKC, int BN>
-int launch_bn(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K, int splits, int k_chunk, cudaStream_t stream) {
+// Writes the shared-memory images of all B tiles: image (nt, kb) = [hi tile | lo tile], each BN rows of 128 bytes,
+// 16-byte chunks swizzled as the kernel's own stash() does, zero where n >= N or k >= K.
+template <class OpB, int BN>
+__global__ void __launch_bounds__(256) pack_b_tiles_kernel(const OpB opb, int N, int K, int n_tiles, int kblocks, char* __restrict__ out) {
+    typedef Config<BN> Cfg;
+    const size_t total = static_cast<size_t>(n_tiles) * kblocks * BN * 8;          // one thread per 16-byte chunk
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int chunk = static_cast<int>(i & 7);
+        const int row = static_cast<int>((i >> 3) % BN);
+        const size_t tile = (i >> 3) / BN;                                         // nt * kblocks + kb
+        const int kb = static_cast<int>(tile % kblocks), nt = static_cast<int>(tile / kblocks);
+        const typename OpB::Row r = opb.row(nt * BN + row);
+        const int kk = kb * BK + chunk * 4;
+        float4 h, l;
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = (kk + e < K) ? opb.load(r, opb.col(kk + e)) : 0.0f;
+        split_tf32(v[0], h.x, l.x); split_tf32(v[1], h.y, l.y); split_tf32(v[2], h.z, l.z); split_tf32(v[3], h.w, l.w);
+        char* img = out + tile * (2 * Cfg::B_TILE_BYTES);
+        *reinterpret_cast<float4*>(img + swz(row, chunk)) = h;
+        *reinterpret_cast<float4*>(img + Cfg::B_TILE_BYTES + swz(row, chunk)) = l;
+    }
+}
+
+inline int tile_n(int N) { return N <= 64 ? 64 : 128; }
+
+// Bytes of packed B tile images for an N x K operand.
+inline size_t bulk_bytes(int N, int K) {
+    const int bn = tile_n(N);
+    return static_cast<size_t>(ceil_div(N, bn)) * ceil_div(K, BK) * 2 * bn * BK * sizeof(float);
+}
+
+template <class OpA, class OpB, bool AKC, bool BKC, int BN, bool BBULK>
+int launch_bn(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K, int splits, int k_chunk, cudaStream_t stream,
+              char* b_tiles) {
     typedef Config<BN> Cfg;
     static bool configured[16] = {false};
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
-    auto kern = gemm_kernel<OpA, OpB, AKC, BKC, BN>;
+    auto kern = gemm_kernel<OpA, OpB, AKC, BKC, BN, BBULK>;
     if (dev < 16 && !configured[dev]) {
         VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         configured[dev] = true;
     }
     dim3 grid(ceil_div(M, BM), ceil_div(N, BN), splits);
     if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
-    kern<<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(a, b, epi, M, N, K, k_chunk);
+    const int kblocks = ceil_div(K, BK);
+    if (BBULK) {
+        const size_t chunks = static_cast<size_t>(grid.y) * kblocks * BN * 8;
+        size_t blocks = ceil_div<size_t>(chunks, 256);
+        const size_t cap = static_cast<size_t>(sm_count()) * 8;
+        if (blocks > cap) blocks = cap;
+        pack_b_tiles_kernel<OpB, BN><<<static_cast<int>(blocks), 256, 0, stream>>>(b, N, K, static_cast<int>(grid.y), kblocks, b_tiles);
+        VDNN_LAUNCHED();
+    }
+    kern<<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(a, b, epi, M, N, K, k_chunk, b_tiles, kblocks);
     VDNN_LAUNCHED();
     return VDNN_OK;
 }
 
-// k_chunk must be a multiple of 32.
+// k_chunk must be a multiple of 32.  b_tiles: nullptr, or bulk_bytes(N, K) bytes of 128-byte-aligned scratch: B is then
+// packed into tile images first and fetched by bulk copies.
 template <class OpA, class OpB, bool AKC, bool BKC>
-int launch(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K, int splits, int k_chunk, cudaStream_t stream) {
-    if (N <= 64) return launch_bn<OpA, OpB, AKC, BKC, 64>(a, b, epi, M, N, K, splits, k_chunk, stream);
-    return launch_bn<OpA, OpB, AKC, BKC, 128>(a, b, epi, M, N, K, splits, k_chunk, stream);
+int launch(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K, int splits, int k_chunk, cudaStream_t stream,
+           char* b_tiles = nullptr) {
+    if (b_tiles) {
+        if (N <= 64) return launch_bn<OpA, OpB, AKC, BKC, 64, true>(a, b, epi, M, N, K, splits, k_chunk, stream, b_tiles);
+        return launch_bn<OpA, OpB, AKC, BKC, 128, true>(a, b, epi, M, N, K, splits, k_chunk, stream, b_tiles);
+    }
+    if (N <= 64) return launch_bn<OpA, OpB, AKC, BKC, 64, false>(a, b, epi, M, N, K, splits, k_chunk, stream, nullptr);
+    return launch_bn<OpA, OpB, AKC, BKC, 128, false>(a, b, epi, M, N, K, splits, k_chunk, stream, nullptr);
 }
 
 // Reads and clears the device-side error word (synchronises the device).

@@ -57,12 +57,12 @@ def conv_bwd_filter(desc, x, dy, dw, alpha=1.0, beta=0.0, algo_mode=0, workspace
                                      workspace_bytes, _s(stream)), "conv_bwd_filter")
 
 
-STATIC_SCRATCH_BYTES = 24 << 20
+STATIC_SCRATCH_BYTES = 16 << 20
 
 
 def conv_bwd_filter_static(desc, x, dy, dw, alpha=1.0, beta=0.0, stream=0):
     """Filter gradient without caller workspace: the split-K partial sums go to the library's own
-    24 MiB device array.  For hosts that may not allocate after start-up.  Raises VdnnError
+    16 MiB device array.  For hosts that may not allocate after start-up.  Raises VdnnError
     (VDNN_ERR_SCRATCH_LIMIT) when the shape needs more than that."""
     check(lib().vdnn_conv_bwd_filter_static(C.byref(desc), alpha, _p(x), _p(dy), beta, _p(dw), _s(stream)),
           "conv_bwd_filter_static")
