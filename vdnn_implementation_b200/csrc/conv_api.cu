@@ -67,10 +67,11 @@ __global__ void __launch_bounds__(256) reduce_partials_kernel(size_t n, int spli
 // N = C columns, which would leave a 128 x 64 tensor-core tile almost empty; here one thread owns one input pixel
 // and all its channels, the filter bank sits in shared memory, and dy is read with unit stride across a warp.
 constexpr int SMALL_C_MAX = 4;
+constexpr size_t SMALL_C_SMEM_MAX = 200 * 1024;
 __global__ void __launch_bounds__(256) dgrad_small_c_kernel(int N, int C, int H, int W, int K, int R, int S, int P, int Q,
-                                                            int pad_h, int pad_w, float alpha, float beta,
-                                                            const float* __restrict__ w, const float* __restrict__ dy,
-                                                            float* __restrict__ dx) {
+                                                            int pad_h, int pad_w, int stride_h, int stride_w, float alpha,
+                                                            float beta, const float* __restrict__ w,
+                                                            const float* __restrict__ dy, float* __restrict__ dx) {
     extern __shared__ float w_s[];                       // [K][C][R*S], as stored
     const int wcount = K * C * R * S;
     for (int i = threadIdx.x; i < wcount; i += blockDim.x) w_s[i] = w[i];
@@ -83,12 +84,13 @@ __global__ void __launch_bounds__(256) dgrad_small_c_kernel(int N, int C, int H,
         const int h = rem / W, x = rem - h * W;
         float acc[SMALL_C_MAX] = {0.f, 0.f, 0.f, 0.f};
         const float* dyn = dy + static_cast<size_t>(n) * K * pq;
-        for (int r = 0; r < R; ++r) {
-            const int p = h + pad_h - r;
-            if (p < 0 || p >= P) continue;
-            for (int s = 0; s < S; ++s) {
-                const int q = x + pad_w - s;
-                if (q < 0 || q >= Q) continue;
+        // taps that connect this input pixel to an output pixel: (h + pad - r) divisible by the stride and in range
+        for (int r = (h + pad_h) % stride_h; r < R; r += stride_h) {
+            const int p = (h + pad_h - r) / stride_h;
+            if (h + pad_h - r < 0 || p >= P) continue;
+            for (int s = (x + pad_w) % stride_w; s < S; s += stride_w) {
+                const int q = (x + pad_w - s) / stride_w;
+                if (x + pad_w - s < 0 || q >= Q) continue;
                 const float* dp = dyn + p * Q + q;
                 const float* wp = w_s + r * S + s;
                 for (int k = 0; k < K; ++k) {
@@ -106,6 +108,12 @@ __global__ void __launch_bounds__(256) dgrad_small_c_kernel(int N, int C, int H,
             *o = v;
         }
     }
+}
+
+// A convolution whose filter covers the whole (unpadded) input produces one output pixel per image: it is a fully
+// connected layer, y[n][k] = sum_j w[k][j] x[n][j] with j running over (c, r, s) -- both operands contiguous in j.
+bool is_full_extent(const vdnn_conv_desc* d) {
+    return d->pad_h == 0 && d->pad_w == 0 && d->h == d->r && d->w == d->s;
 }
 
 // PERF_OPT scratch for the weight operand of forward (N = K filters) and data gradient (N = C channels): images of
@@ -238,6 +246,14 @@ size_t vdnn_conv_workspace_bytes(int op, int algo_mode, const vdnn_conv_desc* d)
     int M, N, K;
     size_t out;
     const int crs = d->c * d->r * d->s;
+    if (is_full_extent(d)) {        // runs as the corresponding FC product
+        switch (op) {
+        case VDNN_CONV_FWD: return vdnn_sgemm_workspace_bytes(algo_mode, d->k, d->n, crs);
+        case VDNN_CONV_BWD_DATA: return vdnn_sgemm_workspace_bytes(algo_mode, crs, d->n, d->k);
+        case VDNN_CONV_BWD_FILTER: return vdnn_sgemm_workspace_bytes(algo_mode, crs, d->k, d->n);
+        default: return 0;
+        }
+    }
     switch (op) {
     case VDNN_CONV_FWD: M = d->n * P * Q; N = d->k; K = crs; out = static_cast<size_t>(M) * N; break;
     case VDNN_CONV_BWD_DATA: M = d->n * d->h * d->w; N = d->c; K = d->k * d->r * d->s; out = static_cast<size_t>(M) * N; break;
@@ -256,6 +272,11 @@ int vdnn_conv_fwd(const vdnn_conv_desc* d, int algo_mode, float alpha, const flo
     if (!x || !w || !y || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
     if (!fits_int32(d, P, Q)) return VDNN_ERR_UNSUPPORTED;
     const int crs = d->c * d->r * d->s, pq = P * Q, rs = d->r * d->s;
+    if (is_full_extent(d)) {    // Y[n][k] = sum_j W[k][j] X[n][j]   (the FC forward product, layer.cu:677-685), then the bias
+        const int st = vdnn_sgemm(1, 0, d->k, d->n, crs, alpha, w, crs, x, crs, beta, y, d->k, algo_mode, workspace, workspace_bytes, stream);
+        if (st != VDNN_OK || !bias) return st;
+        return vdnn_add_bias(d->n, d->k, 1, 1.0f, bias, y, stream);
+    }
     Epilogue e{};
     e.out = y; e.bias = bias; e.alpha = alpha; e.beta = beta;
     e.row_div = FastDiv(pq); e.row_hi = d->k * pq; e.row_lo = 1; e.col_stride = pq;
@@ -285,15 +306,24 @@ int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, cons
     if (!w || !dy || !dx || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
     if (!fits_int32(d, P, Q)) return VDNN_ERR_UNSUPPORTED;
     const int rs = d->r * d->s, hw = d->h * d->w, pq = P * Q;
-    if (d->c <= SMALL_C_MAX && d->stride_h == 1 && d->stride_w == 1 &&
-        static_cast<size_t>(d->k) * d->c * rs * sizeof(float) <= 48 * 1024) {
-        const size_t smem = static_cast<size_t>(d->k) * d->c * rs * sizeof(float);
+    if (is_full_extent(d))      // dX[n][j] = sum_k W[k][j] dY[n][k]   (the FC data-gradient product, layer.cu:725-733)
+        return vdnn_sgemm(0, 0, d->c * rs, d->n, d->k, alpha, w, d->c * rs, dy, d->k, beta, dx, d->c * rs, algo_mode, workspace,
+                          workspace_bytes, stream);
+    const size_t small_smem = static_cast<size_t>(d->k) * d->c * rs * sizeof(float);
+    if (d->c <= SMALL_C_MAX && small_smem <= SMALL_C_SMEM_MAX) {
+        static bool configured[16] = {false};
+        int dev = 0;
+        VDNN_CUDA(cudaGetDevice(&dev));
+        if (dev < 16 && !configured[dev]) {
+            VDNN_CUDA(cudaFuncSetAttribute(dgrad_small_c_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMALL_C_SMEM_MAX)));
+            configured[dev] = true;
+        }
         const long long total = static_cast<long long>(d->n) * hw;
         long long blocks = (total + 255) / 256;
-        const long long cap = static_cast<long long>(sm_count()) * 8;
+        const long long cap = static_cast<long long>(sm_count()) * (small_smem > 100 * 1024 ? 1 : 2) * 2;
         if (blocks > cap) blocks = cap;
-        dgrad_small_c_kernel<<<static_cast<int>(blocks), 256, smem, as_stream(stream)>>>(
-            d->n, d->c, d->h, d->w, d->k, d->r, d->s, P, Q, d->pad_h, d->pad_w, alpha, beta, w, dy, dx);
+        dgrad_small_c_kernel<<<static_cast<int>(blocks), 256, small_smem, as_stream(stream)>>>(
+            d->n, d->c, d->h, d->w, d->k, d->r, d->s, P, Q, d->pad_h, d->pad_w, d->stride_h, d->stride_w, alpha, beta, w, dy, dx);
         VDNN_LAUNCHED();
         return VDNN_OK;
     }
@@ -334,6 +364,8 @@ int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, co
     if (!x || !dy || !dw || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
     if (!fits_int32(d, P, Q)) return VDNN_ERR_UNSUPPORTED;
     const int crs = d->c * d->r * d->s, pq = P * Q;
+    if (is_full_extent(d))      // W[k][j] = alpha * sum_n X[n][j] dY[n][k] + beta * W[k][j]   (layer.cu:736-744)
+        return vdnn_sgemm(0, 1, crs, d->k, d->n, alpha, x, crs, dy, d->k, beta, dw, crs, algo_mode, workspace, workspace_bytes, stream);
     // dy viewed as [k][(n, pq)]: offset = k*PQ + n*K*PQ + pq
     SplitDense A;
     A.p = dy; A.rows = d->k; A.cols = d->n * pq;

@@ -253,6 +253,30 @@ __global__ void __launch_bounds__(kThreads) maxpool_bwd_generic(int planes, int 
     }
 }
 
+// Overlapping windows (AlexNet's 3x3 / stride 2): one thread per window finds its first maximum once and adds dy
+// there; dx is zeroed beforehand.  An input element collects at most four contributions, in arbitrary order.
+__global__ void __launch_bounds__(kThreads) maxpool_bwd_scatter(int planes, int h, int w, int P, int Q, int wh, int ww,
+                                                                int sh, int sw, const float* __restrict__ dy,
+                                                                const float* __restrict__ x, float* __restrict__ dx) {
+    const size_t total = static_cast<size_t>(planes) * P * Q;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const int q = static_cast<int>(idx % Q);
+        const size_t t = idx / Q;
+        const int p = static_cast<int>(t % P);
+        const size_t plane = t / P;
+        const size_t origin = plane * h * w + static_cast<size_t>(p * sh) * w + q * sw;
+        float m = -INFINITY;
+        int best = 0;
+        for (int i = 0; i < wh; ++i)
+            for (int j = 0; j < ww; ++j) {
+                const float v = x[origin + i * w + j];
+                if (v > m) { m = v; best = i * w + j; }
+            }
+        atomicAdd(dx + origin + best, dy[idx]);
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) maxpool_bwd_2x2(size_t pairs, int w, int Qh, const float* __restrict__ dy,
                                                             const float* __restrict__ x, float* __restrict__ dx) {
     const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
@@ -522,6 +546,11 @@ int vdnn_maxpool_bwd(int n, int c, int h, int w, int win_h, int win_w, int strid
     if (pool_fast_2x2(h, w, win_h, win_w, stride_h, stride_w, x, dx, dy)) {
         const size_t pairs = static_cast<size_t>(planes) * P * (Q / 2);
         maxpool_bwd_2x2<<<stream_grid(pairs, 1), kThreads, 0, as_stream(stream)>>>(pairs, w, Q / 2, dy, x, dx);
+    } else if (win_h > stride_h || win_w > stride_w) {
+        VDNN_CUDA(cudaMemsetAsync(dx, 0, static_cast<size_t>(planes) * h * w * sizeof(float), as_stream(stream)));
+        const size_t total = static_cast<size_t>(planes) * P * Q;
+        maxpool_bwd_scatter<<<stream_grid(total, 1), kThreads, 0, as_stream(stream)>>>(planes, h, w, P, Q, win_h, win_w,
+                                                                                       stride_h, stride_w, dy, x, dx);
     } else {
         const size_t total = static_cast<size_t>(planes) * h * w;
         maxpool_bwd_generic<<<stream_grid(total, 1), kThreads, 0, as_stream(stream)>>>(planes, h, w, P, Q, win_h, win_w,
