@@ -430,6 +430,47 @@ __global__ void __launch_bounds__(kThreads) lrn_bwd_kernel(int n, int c, int hw,
     }
 }
 
+// Window of 5 (the AlexNet setting): one pass over the channels per position.  Channel j's scale s_j and
+// t_j = dy_j * y_j / s_j are produced once and kept in a five-entry shift register; channel i = j - 2 is finished
+// as soon as t_{i+2} exists:  dx_i = dy_i * s_i^-beta - 2*alpha*beta/n * x_i * sum_{|j-i|<=2} t_j.
+__global__ void __launch_bounds__(kThreads) lrn_bwd_win5_kernel(int n, int c, int hw, float alpha_over_n, float beta, float k,
+                                                                const float* __restrict__ x, const float* __restrict__ y,
+                                                                const float* __restrict__ dy, float* __restrict__ dx) {
+    const size_t total = static_cast<size_t>(n) * hw;
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+        const size_t in = idx / hw;
+        const size_t base = in * c * hw + (idx - in * hw);
+        float t[5] = {0.f, 0.f, 0.f, 0.f, 0.f};     // t[4] newest (channel j), t[0] = channel j - 4
+        float sc[3] = {k, k, k};                     // scales of channels j-2 (sc[0]), j-1, j
+        float xq[5] = {0.f, 0.f, 0.f, 0.f, 0.f};     // x of channels j-2 .. j+2, for the sliding sum of squares
+        // prime x window for j = 0: channels 0..2 at xq[2..4]
+        for (int m = 0; m < 3; ++m) xq[2 + m] = m < c ? x[base + static_cast<size_t>(m) * hw] : 0.0f;
+        for (int j = 0; j < c + 2; ++j) {
+            if (j < c) {
+                const float ss = xq[0] * xq[0] + xq[1] * xq[1] + xq[2] * xq[2] + xq[3] * xq[3] + xq[4] * xq[4];
+                const float sj = fmaf(alpha_over_n, ss, k);
+                const size_t o = base + static_cast<size_t>(j) * hw;
+                t[0] = t[1]; t[1] = t[2]; t[2] = t[3]; t[3] = t[4];
+                t[4] = dy[o] * y[o] / sj;
+                sc[0] = sc[1]; sc[1] = sc[2]; sc[2] = sj;
+            } else {
+                t[0] = t[1]; t[1] = t[2]; t[2] = t[3]; t[3] = t[4]; t[4] = 0.0f;
+                sc[0] = sc[1]; sc[1] = sc[2];
+            }
+            const int i = j - 2;
+            if (i >= 0) {
+                // x_i sits at xq[0] (the window is centred on j = i + 2)
+                const size_t o = base + static_cast<size_t>(i) * hw;
+                dx[o] = dy[o] * powf(sc[0], -beta) - 2.0f * alpha_over_n * beta * xq[0] * (t[0] + t[1] + t[2] + t[3] + t[4]);
+            }
+            // slide the x window to be centred on j + 1
+            xq[0] = xq[1]; xq[1] = xq[2]; xq[2] = xq[3]; xq[3] = xq[4];
+            xq[4] = (j + 3 < c) ? x[base + static_cast<size_t>(j + 3) * hw] : 0.0f;
+        }
+    }
+}
+
 }  // namespace
 }  // namespace vdnn
 
@@ -593,8 +634,12 @@ int vdnn_lrn_fwd(int n, int c, int hw, int win, float alpha, float beta, float k
 int vdnn_lrn_bwd(int n, int c, int hw, int win, float alpha, float beta, float k, const float* x, const float* y,
                  const float* dy, float* dx, void* stream) {
     if (!x || !y || !dy || !dx || n <= 0 || c <= 0 || hw <= 0 || win <= 0 || win % 2 == 0) return VDNN_ERR_BAD_ARG;
-    lrn_bwd_kernel<<<stream_grid(static_cast<size_t>(n) * hw, 1), kThreads, 0, as_stream(stream)>>>(
-        n, c, hw, win, alpha / win, beta, k, x, y, dy, dx);
+    if (win == 5)
+        lrn_bwd_win5_kernel<<<stream_grid(static_cast<size_t>(n) * hw, 1), kThreads, 0, as_stream(stream)>>>(
+            n, c, hw, alpha / win, beta, k, x, y, dy, dx);
+    else
+        lrn_bwd_kernel<<<stream_grid(static_cast<size_t>(n) * hw, 1), kThreads, 0, as_stream(stream)>>>(
+            n, c, hw, win, alpha / win, beta, k, x, y, dy, dx);
     VDNN_LAUNCHED();
     return VDNN_OK;
 }
