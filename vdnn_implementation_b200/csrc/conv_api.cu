@@ -15,10 +15,11 @@ int g_engine = VDNN_ENGINE_AUTO;
 
 struct SplitPlan { int splits; int k_chunk; };
 
-// Split K so that the grid is as close to two full waves of 128x128 tiles as it can get without exceeding them
+// Split K so that the grid is as close to two full waves of output tiles as it can get without exceeding them
 // (a third, nearly empty wave would cost as much as a full one), keeping at least 64 k per split.
 SplitPlan plan_split(int M, int N, int K) {
-    const long tiles = static_cast<long>(ceil_div(M, 128)) * ceil_div(N, 128);
+    const int bn = g_engine == VDNN_ENGINE_FFMA ? 128 : tc::tile_n(N);
+    const long tiles = static_cast<long>(ceil_div(M, 128)) * ceil_div(N, bn);
     const int sms = sm_count();
     int splits = 1;
     if (tiles < sms) {
@@ -257,7 +258,7 @@ size_t vdnn_conv_workspace_bytes(int op, int algo_mode, const vdnn_conv_desc* d)
     switch (op) {
     case VDNN_CONV_FWD: M = d->n * P * Q; N = d->k; K = crs; out = static_cast<size_t>(M) * N; break;
     case VDNN_CONV_BWD_DATA: M = d->n * d->h * d->w; N = d->c; K = d->k * d->r * d->s; out = static_cast<size_t>(M) * N; break;
-    case VDNN_CONV_BWD_FILTER: M = d->k; N = crs; K = d->n * P * Q; out = static_cast<size_t>(M) * N; break;
+    case VDNN_CONV_BWD_FILTER: M = crs; N = d->k; K = d->n * P * Q; out = static_cast<size_t>(M) * N; break;
     default: return 0;
     }
     const SplitPlan plan = plan_split(M, N, K);
@@ -366,16 +367,19 @@ int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, co
     const int crs = d->c * d->r * d->s, pq = P * Q;
     if (is_full_extent(d))      // W[k][j] = alpha * sum_n X[n][j] dY[n][k] + beta * W[k][j]   (layer.cu:736-744)
         return vdnn_sgemm(0, 1, crs, d->k, d->n, alpha, x, crs, dy, d->k, beta, dw, crs, algo_mode, workspace, workspace_bytes, stream);
+    // D[j][k] = sum over pixels of x(j; pixel) * dy(k; pixel), written to dw[k*CRS + j]: the expensive operand, the
+    // gathered input, supplies the 128 tile rows; dy supplies up to 256 columns, so every gathered element feeds up to
+    // 256 multiply-adds and layers with few filters (K = 64) still fill the tile's rows.
+    XGatherFiltRows A; A.g = make_xgather(d, x, P, Q);
     // dy viewed as [k][(n, pq)]: offset = k*PQ + n*K*PQ + pq
-    SplitDense A;
-    A.p = dy; A.rows = d->k; A.cols = d->n * pq;
-    A.row_div = FastDiv(1u << 30); A.row_hi = 0; A.row_lo = pq;
-    A.col_div = FastDiv(pq); A.col_hi = d->k * pq; A.col_lo = 1;
-    XGatherFiltRows B; B.g = make_xgather(d, x, P, Q);
+    SplitDense B;
+    B.p = dy; B.rows = d->k; B.cols = d->n * pq;
+    B.row_div = FastDiv(1u << 30); B.row_hi = 0; B.row_lo = pq;
+    B.col_div = FastDiv(pq); B.col_hi = d->k * pq; B.col_lo = 1;
     Epilogue e{};
     e.out = dw; e.bias = nullptr; e.alpha = alpha; e.beta = beta;
-    e.row_div = FastDiv(1u << 30); e.row_hi = 0; e.row_lo = crs; e.col_stride = 1;
-    return contract<SplitDense, XGatherFiltRows, true, true>(A, B, e, d->k, crs, d->n * pq, static_cast<size_t>(d->k) * crs, 0,
+    e.row_div = FastDiv(1u << 30); e.row_hi = 0; e.row_lo = 1; e.col_stride = crs;
+    return contract<XGatherFiltRows, SplitDense, true, true>(A, B, e, crs, d->k, d->n * pq, static_cast<size_t>(d->k) * crs, 0,
                                                              algo_mode, workspace, workspace_bytes, as_stream(stream));
 }
 

@@ -3,7 +3,7 @@
 //        a*b ~= a_hi*b_hi + a_hi*b_lo + a_lo*b_hi,      x_hi = tf32(x), x_lo = x - x_hi  (exact),
 // with fp32 accumulation in tensor memory (TMEM).
 //
-// One CTA computes a 128 x BN tile of D (BN = 64 or 128) over a K range in steps of 32:
+// One CTA computes a 128 x BN tile of D (BN = 64, 128 or 256) over a K range in steps of 32:
 //   warps 0-15 producers: gather the 128 x 32 A tile and BN x 32 B tile straight from the NCHW /
 //              KCRS tensors (gemm_operands.cuh), split every value into hi / lo, and store both
 //              into shared memory in the K-major, 128-byte-swizzled layout tcgen05.mma reads;
@@ -40,7 +40,7 @@ __device__ int g_tc_error = 0;
 template <int BN> struct Config {
     static constexpr int B_TILE_BYTES = BN * BK * 4;
     static constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;
-    static constexpr int STAGES = BN == 128 ? 3 : 4;
+    static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
     // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
     static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
@@ -357,7 +357,8 @@ __global__ void __launch_bounds__(256) pack_b_tiles_kernel(const OpB opb, int N,
     }
 }
 
-inline int tile_n(int N) { return N <= 64 ? 64 : 128; }
+// Column tile: wide tiles amortise the A gather over more columns (the producers' cost per flop goes with 1/BN).
+inline int tile_n(int N) { return N <= 64 ? 64 : (N < 256 ? 128 : 256); }
 
 // Bytes of packed B tile images for an N x K operand.
 inline size_t bulk_bytes(int N, int K) {
@@ -398,12 +399,15 @@ int launch_bn(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int
 template <class OpA, class OpB, bool AKC, bool BKC>
 int launch(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K, int splits, int k_chunk, cudaStream_t stream,
            char* b_tiles = nullptr) {
+    const int bn = tile_n(N);
     if (b_tiles) {
-        if (N <= 64) return launch_bn<OpA, OpB, AKC, BKC, 64, true>(a, b, epi, M, N, K, splits, k_chunk, stream, b_tiles);
-        return launch_bn<OpA, OpB, AKC, BKC, 128, true>(a, b, epi, M, N, K, splits, k_chunk, stream, b_tiles);
+        if (bn == 64) return launch_bn<OpA, OpB, AKC, BKC, 64, true>(a, b, epi, M, N, K, splits, k_chunk, stream, b_tiles);
+        if (bn == 128) return launch_bn<OpA, OpB, AKC, BKC, 128, true>(a, b, epi, M, N, K, splits, k_chunk, stream, b_tiles);
+        return launch_bn<OpA, OpB, AKC, BKC, 256, true>(a, b, epi, M, N, K, splits, k_chunk, stream, b_tiles);
     }
-    if (N <= 64) return launch_bn<OpA, OpB, AKC, BKC, 64, false>(a, b, epi, M, N, K, splits, k_chunk, stream, nullptr);
-    return launch_bn<OpA, OpB, AKC, BKC, 128, false>(a, b, epi, M, N, K, splits, k_chunk, stream, nullptr);
+    if (bn == 64) return launch_bn<OpA, OpB, AKC, BKC, 64, false>(a, b, epi, M, N, K, splits, k_chunk, stream, nullptr);
+    if (bn == 128) return launch_bn<OpA, OpB, AKC, BKC, 128, false>(a, b, epi, M, N, K, splits, k_chunk, stream, nullptr);
+    return launch_bn<OpA, OpB, AKC, BKC, 256, false>(a, b, epi, M, N, K, splits, k_chunk, stream, nullptr);
 }
 
 // Reads and clears the device-side error word (synchronises the device).
