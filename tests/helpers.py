@@ -1,5 +1,7 @@
 import numpy as np
 
+FC_GEMM, CONV, FC_CONV, RELU, SOFTMAX, POOL, LRN = 0, 1, 2, 3, 6, 7, 9
+
 
 def rel_err(a, b):
     """Tensor-normalised error: max|a-b| / max|b|."""
@@ -10,8 +12,27 @@ def rel_err(a, b):
     return float(np.abs(a - b).max()) / denom
 
 
+def relu_knife_edges(onet, specs, eps=5e-8, live=2e-5):
+    """Count ReLU inputs the oracle holds within `eps` (tensor-normalised; an fp32 convolution output near
+    zero carries a rounding error around 1e-8 of the tensor's maximum) of zero while a gradient above
+    `live` of the largest arrives there.  The sign of such an input is decided by the last rounding of the
+    convolution below it, so two correct fp32 implementations may disagree on that mask bit, and the
+    disagreement then spreads through every gradient underneath.  Whole-network parity is only meaningful
+    on inputs where this count is zero."""
+    count = 0
+    for l, spec in enumerate(specs):
+        if tuple(spec)[0] != RELU:
+            continue
+        x = np.abs(onet.dst(l - 1).ravel())
+        dy = np.abs(onet.grad(l + 1).ravel()) if l + 1 < len(specs) else None
+        near = x < eps * x.max()
+        if dy is not None:
+            near &= dy > live * max(float(dy.max()), 1e-30)
+        count += int(near.sum())
+    return count
+
+
 # Small topologies in the reference's constructor order: (type, n, c, h, w, pad_h, pad_w, stride_h, stride_w, k, r, s)
-FC_GEMM, CONV, FC_CONV, RELU, SOFTMAX, POOL, LRN = 0, 1, 2, 3, 6, 7, 9
 
 
 def tiny_net(n=4, with_lrn=False):

@@ -4,14 +4,14 @@ loss within 1e-5, updated parameters, and the allocation / offload / prefetch tr
 import numpy as np
 import pytest
 
-from helpers import rel_err, tiny_net
+from helpers import rel_err, relu_knife_edges, tiny_net
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-4
 POLICIES = ["BASELINE", "VDNN_NONE", "VDNN_ALL", "VDNN_CONV"]
 
 
-def _run(vdnn, oracle, specs, cnn, policy, algo, batch, lr, steps=2, host_sync=False, init_mode=0):
+def _run(vdnn, oracle, specs, cnn, policy, algo, batch, lr, steps=2, host_sync=False, init_mode=0, seed0=1000):
     onet = oracle.Net(specs, lr, init_mode=init_mode)
     net = vdnn.Network(cnn, policy, algo, batch_size=batch, pool_bytes=4e9, learning_rate=lr, init_mode=init_mode,
                        capture=True, custom_layers=specs if cnn == "CUSTOM_CNN" else None, host_sync_per_layer=host_sync)
@@ -20,7 +20,7 @@ def _run(vdnn, oracle, specs, cnn, policy, algo, batch, lr, steps=2, host_sync=F
         rows = specs[-1][1] if not hasattr(specs[-1], "n") else specs[-1].n
         cols = net.output_size // rows
         for step in range(steps):
-            x = oracle.fill_normal(net.input_size, 1000 + step)
+            x = oracle.fill_normal(net.input_size, seed0 + step)
             t = oracle.fill_onehot(rows, cols, 2000 + step)
             onet.set_input(x, t)
             onet.forward()
@@ -79,7 +79,23 @@ def test_reference_topologies_small_batch(vdnn, oracle, cnn, policy):
 
 def test_vgg16_single_image(vdnn, oracle):
     specs = [s.astuple() for s in oracle.model_layers(oracle.VGG16_64, 1)]
-    _run(vdnn, oracle, specs, "VGG16_64", "VDNN_ALL", "VDNN_MEMORY_OPT_ALGO", 1, 0.01, steps=1)
+    # 13 ReLU layers over up to 3.2 M activations each: take the first input seed on which the oracle has
+    # no ReLU input within rounding of zero under a live gradient (seed 1000 has two; one is 2e-8 against
+    # a tensor maximum of 11 where the gradient is half the tensor's largest, and its mask bit depends on
+    # the summation order of the convolution below).
+    for seed0 in range(1000, 1016):
+        onet = oracle.Net(specs, 0.01, init_mode=0)
+        try:
+            onet.set_input(oracle.fill_normal(3 * 224 * 224, seed0), oracle.fill_onehot(1, 1000, 2000))
+            onet.forward()
+            onet.backward()
+            if relu_knife_edges(onet, specs) == 0:
+                break
+        finally:
+            onet.close()
+    else:
+        pytest.fail("no seed without a knife-edge ReLU input")
+    _run(vdnn, oracle, specs, "VGG16_64", "VDNN_ALL", "VDNN_MEMORY_OPT_ALGO", 1, 0.01, steps=1, seed0=seed0)
 
 
 def test_policies_agree_at_full_width(vdnn):

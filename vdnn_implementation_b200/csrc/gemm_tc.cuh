@@ -13,7 +13,7 @@
 //              stage) into one of two TMEM accumulator buffers and tcgen05.commit to hand the stage
 //              back and to publish that buffer.  The producers add each finished buffer into fp32
 //              registers (round-to-nearest adds), so no accumulation chain inside the tensor core
-//              is longer than one stage.
+//              is longer than two stages (24 MMAs).
 // Stages are handed over with mbarriers (full: one arrival per producer thread, empty: one commit).  Every
 // wait is bounded: on expiry the thread records an error code in g_tc_error, stops waiting, and
 // the CTA still runs its common exit path (barrier, TMEM release).
@@ -203,8 +203,8 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
         mbar_init(smem_u32(&bars[2 * S + 1]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // Two accumulator buffers of BN columns each: the tensor core sums one 32-wide k block into a
-    // buffer (a chain of 12 MMAs) while the previous block's buffer is added into fp32 registers.
+    // Two accumulator buffers of BN columns each: the tensor core sums two 32-wide k blocks into a
+    // buffer (a chain of 24 MMAs) while the previous pair's buffer is added into fp32 registers.
     // Keeping the in-TMEM chains short matters for accuracy: the tensor core truncates when it adds
     // into its accumulator, and over thousands of chained MMAs that bias reaches 1e-5 relative.
     if (warp == PRODUCER_WARPS) {
@@ -232,11 +232,12 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
 #pragma unroll
         for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
         bool alive = true;
+        int next_drain = 0;
 
-        // adds the finished k block `blk` from its TMEM buffer into the register accumulators
-        auto drain = [&](int blk) {
-            const int b = blk & 1;
-            bool ok = mbar_wait(smem_u32(&bars[2 * S + b]), static_cast<uint32_t>(blk >> 1) & 1u);
+        // adds the finished pair of k blocks `pair` from its TMEM buffer into the register accumulators
+        auto drain = [&](int pair) {
+            const int b = pair & 1;
+            bool ok = mbar_wait(smem_u32(&bars[2 * S + b]), static_cast<uint32_t>(pair >> 1) & 1u);
             ok = __all_sync(0xffffffffu, ok);               // tcgen05.ld is warp-collective
             if (!ok) { atomicCAS(&g_tc_error, 0, 103); alive = false; return; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -254,9 +255,9 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
         for (int i = 0; i < nkb && alive; ++i) {
             const int s = i % S;
             const uint32_t phase = static_cast<uint32_t>(i / S) & 1u;
-            // block i reuses the accumulator buffer of block i - 2: empty it first (every producer does,
-            // and the MMA of block i cannot start before all of them have arrived on full[s])
-            if (i >= 2) { drain(i - 2); if (!alive) break; }
+            // blocks i, i+1 (i even) reuse the accumulator buffer of blocks i-4, i-3: empty it first (every producer
+            // does, and the MMA of block i cannot start before all of them have arrived on full[s])
+            if (i >= 4 && !(i & 1)) { drain(next_drain++); if (!alive) break; }
             bool ok = mbar_wait(smem_u32(&bars[S + s]), phase ^ 1u);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) { atomicCAS(&g_tc_error, 0, 101); alive = false; break; }
@@ -282,8 +283,7 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
                 if (!BBULK) gb.fetch(opb, kbeg + (i + 1) * BK, kend, t);
             }
         }
-        if (alive && nkb >= 2) drain(nkb - 2);
-        if (alive && nkb >= 1) drain(nkb - 1);
+        while (alive && next_drain < (nkb + 1) / 2) drain(next_drain++);
 
         // ------------------------------------------------------------------ epilogue
         const int m = m0 + (warp & 3) * 32 + lane;
@@ -306,18 +306,20 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
             const uint32_t a_lo = a_hi + A_TILE_BYTES;
             const uint32_t b_hi = a_hi + 2 * A_TILE_BYTES;
             const uint32_t b_lo = b_hi + Cfg::B_TILE_BYTES;
-            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((i & 1) * BN);
+            // two consecutive k blocks share an accumulator buffer (a chain of 24 MMAs), then the other buffer is used
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(((i >> 1) & 1) * BN);
 #pragma unroll
             for (int ks = 0; ks < BK / 8; ++ks) {
                 // one k slice = 8 tf32 = 32 bytes inside the swizzle atom
                 const uint64_t dah = make_desc(a_hi + ks * 32), dal = make_desc(a_lo + ks * 32);
                 const uint64_t dbh = make_desc(b_hi + ks * 32), dbl = make_desc(b_lo + ks * 32);
-                mma_tf32(d_tmem, dal, dbh, Cfg::IDESC, ks != 0 ? 1u : 0u);     // small terms first
+                mma_tf32(d_tmem, dal, dbh, Cfg::IDESC, (ks != 0 || (i & 1)) ? 1u : 0u);     // small terms first
                 mma_tf32(d_tmem, dah, dbl, Cfg::IDESC, 1u);
                 mma_tf32(d_tmem, dah, dbh, Cfg::IDESC, 1u);
             }
             mma_commit(smem_u32(&bars[S + s]));             // stage s may be overwritten once these finish
-            mma_commit(smem_u32(&bars[2 * S + (i & 1)]));   // and this block's sums may be collected
+            if ((i & 1) || i == nkb - 1)
+                mma_commit(smem_u32(&bars[2 * S + ((i >> 1) & 1)]));   // and this pair's sums may be collected
         }
     }
 
