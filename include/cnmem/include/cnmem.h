@@ -65,6 +65,16 @@ cnmemStatus_t vdnnPoolFreeAfter(void* ptr, const cudaStream_t* streams, int numS
  * covers part of the returned block.  Among the free blocks that fit, the one that becomes usable
  * soonest is chosen (no pending event, else the oldest pending events), then the tightest fit. */
 cnmemStatus_t vdnnPoolMallocFor(void** ptr, size_t size, const cudaStream_t* streams, int numStreams);
+/* Same as vdnnPoolFreeAfter, for bytes whose last reader has not been enqueued yet (a copy that the
+ * host will submit later, in an order of its own choosing).  The bytes count as free, but carry a "hold"
+ * named by `token` (> 0).  vdnnPoolResolve(token, stream), called once that reader has been enqueued on
+ * `stream`, turns the hold into an ordinary pending event.  Allocations avoid held bytes while anything
+ * else fits; when only held bytes fit, the pool calls the resolver (lowest token first), which must
+ * enqueue the reader and call vdnnPoolResolve for that token before it returns. */
+typedef void (*vdnnPoolResolver_t)(void* user, unsigned long long token);
+cnmemStatus_t vdnnPoolSetResolver(vdnnPoolResolver_t resolver, void* user);
+cnmemStatus_t vdnnPoolFreeHeld(void* ptr, const cudaStream_t* streams, int numStreams, unsigned long long token);
+cnmemStatus_t vdnnPoolResolve(unsigned long long token, cudaStream_t stream);
 cnmemStatus_t vdnnPoolHighWater(size_t* peakBytes, int reset);
 /* Makes the k-th allocation from now fail with CNMEM_STATUS_OUT_OF_MEMORY (k >= 1; 0 disarms).
  * Host-side fault injection for the soft-OOM return path (layer.h:119-125). */

@@ -287,6 +287,15 @@ typedef struct {
 /* Fills timing fields only if profiling events were enabled with vdnn_network_set_profiling. */
 int vdnn_network_get_stats(vdnn_network* net, vdnn_network_stats* out);
 int vdnn_network_set_profiling(vdnn_network* net, int enabled);
+/* Order in which the offload copies of one forward pass reach the device-to-host copy engine.  The
+ * reference enqueues each copy in its own layer (layer.cu:969-977) and waits for it there
+ * (network.cu:1090-1091).  Without those waits the engine serves copies first in, first out, while
+ * backward needs the last layer's data first; so by default (forward_order = 0) only as many bytes of
+ * the first layers as the copy engine moves under the forward kernels are enqueued in their own layer,
+ * and the rest after the last layer's forward, latest layer first.  Which layers are offloaded, the
+ * bytes moved, the host-side allocation order and the pool's byte counts are the same either way.
+ * forward_order = 1 (or the environment variable VDNN_OFFLOAD_ORDER=forward) restores layer order. */
+int vdnn_network_set_offload_order(vdnn_network* net, int forward_order);
 /* Per-layer timeline of the last profiled step, in milliseconds from the step's first event:
  * out[8*l + 0..7] = forward begin, forward end, offload begin, offload end, backward begin, backward end,
  * prefetch begin, prefetch end of layer l (negative where the layer has no such event).  `out` holds

@@ -66,6 +66,19 @@ int vdnnContext::release(void* ptr, size_t bytes, int layer, int tag, std::initi
     return 0;
 }
 
+int vdnnContext::releaseHeld(void* ptr, size_t bytes, int layer, int tag, std::initializer_list<cudaStream_t> after) {
+    std::vector<cudaStream_t> st_list;
+    for (cudaStream_t s : after) if (s) st_list.push_back(s);
+    const cnmemStatus_t st = vdnnPoolFreeHeld(ptr, st_list.data(), static_cast<int>(st_list.size()),
+                                              static_cast<unsigned long long>(layer) + 1);
+    if (st != CNMEM_STATUS_SUCCESS) {
+        fprintf(stderr, "\n[pool free failed with %s]\n", cnmemGetErrorString(st));
+        return VDNN_ERR_STATE;
+    }
+    record(1, layer, tag, static_cast<int64_t>(bytes));
+    return 0;
+}
+
 int vdnnContext::upload(void* dst, const void* src_h, size_t bytes) {
     if (dry_run) return VDNN_OK;
     return cudaMemcpy(dst, src_h, bytes, cudaMemcpyHostToDevice) == cudaSuccess ? VDNN_OK : VDNN_ERR_CUDA;
@@ -424,16 +437,50 @@ int Layer::offloadSrcData(bool* _offloaded, DATATYPE** _offloadedSrcData_h) {
     handle->record(2, layerId, TAG_SRC, static_cast<int64_t>(bytes));
     handle->offload_bytes += static_cast<int64_t>(bytes);
     if (handle->dry_run) return 0;
-    cudaStream_t lane = *stream_memory;
-    cudaEvent_t ready = layerId == 0 ? handle->ev_input_ready : handle->ev_fwd_done[layerId - 1];
-    if (handle->profiling) {
+    const vdnnContext::PendingOffload p{layerId, _offloadedSrcData_h[layerId], srcData, bytes};
+    if (handle->defer_offloads && handle->eager_offload_used + static_cast<int64_t>(bytes) > handle->eager_offload_budget) {
+        handle->eager_offload_used = handle->eager_offload_budget;     // nothing later overtakes a deferred copy
+        handle->pending_offloads.push_back(p);
+        return 0;
+    }
+    handle->eager_offload_used += static_cast<int64_t>(bytes);
+    return handle->submitOffload(p);
+}
+
+int vdnnContext::submitOffload(const PendingOffload& p) {
+    vdnnContext* handle = this;
+    cudaStream_t lane = stream_d2h;
+    cudaEvent_t ready = p.layer == 0 ? ev_input_ready : ev_fwd_done[p.layer - 1];
+    if (profiling) {
         CU(cudaStreamWaitEvent(lane, ready, 0));
-        CU(cudaEventRecord(handle->pf_off_beg[layerId], lane));
+        CU(cudaEventRecord(pf_off_beg[p.layer], lane));
         ready = NULL;
     }
-    DEV(vdnn_offload(_offloadedSrcData_h[layerId], srcData, bytes, ready, NULL, lane));
-    if (handle->profiling) CU(cudaEventRecord(handle->pf_off_end[layerId], lane));
-    CU(cudaEventRecord(handle->ev_offload_done[layerId], lane));
+    DEV(vdnn_offload(p.host, p.dev, p.bytes, ready, NULL, lane));
+    if (profiling) CU(cudaEventRecord(pf_off_end[p.layer], lane));
+    CU(cudaEventRecord(ev_offload_done[p.layer], lane));
+    if (vdnnPoolResolve(static_cast<unsigned long long>(p.layer) + 1, lane) != CNMEM_STATUS_SUCCESS) return VDNN_ERR_STATE;
+    return 0;
+}
+
+int vdnnContext::flushOffloads(int layer) {
+    vdnnContext* handle = this;
+    if (layer >= 0) {
+        size_t keep = 0;
+        for (size_t i = 0; i < pending_offloads.size(); ++i) {
+            const PendingOffload p = pending_offloads[i];
+            if (p.layer > layer) { pending_offloads[keep++] = p; continue; }
+            const int st = submitOffload(p);
+            if (st != 0) return st;
+        }
+        pending_offloads.resize(keep);
+        return 0;
+    }
+    for (size_t i = pending_offloads.size(); i-- > 0;) {
+        const int st = submitOffload(pending_offloads[i]);
+        if (st != 0) return st;
+    }
+    pending_offloads.clear();
     return 0;
 }
 

@@ -49,6 +49,26 @@ struct vdnnContext {
     std::vector<vdnn_trace_event> trace;
     int64_t offload_bytes = 0, prefetch_bytes = 0, pinned_bytes = 0, workspace_bytes_max = 0;
 
+    // Offloads whose copy has not been enqueued yet.  The single device-to-host engine serves copies in
+    // the order they were enqueued, forward produces layers 0..L and backward needs them L..0; so the copies
+    // are enqueued after the last layer's forward, latest layer first: the prefetch of layer l then follows
+    // its offload closely and both PCIe directions run at the same time.  Blocks released meanwhile are held
+    // in the pool; when only held bytes fit a request, the pool has the oldest copies enqueued at once.
+    // `eager_offload_budget` bytes of the first layers (environment variable VDNN_EAGER_OFFLOAD_BYTES) are
+    // still enqueued in their own layer, for networks whose forward is long enough to hide them.
+    struct PendingOffload { int layer; void* host; const void* dev; size_t bytes; };
+    bool defer_offloads = false;
+    std::vector<PendingOffload> pending_offloads;
+    int64_t eager_offload_budget = 0, eager_offload_used = 0;
+    bool offloadPending(int layer) const {
+        for (const PendingOffload& p : pending_offloads) if (p.layer == layer) return true;
+        return false;
+    }
+    int submitOffload(const PendingOffload& p);      // enqueue the copy, record ev_offload_done, resolve the pool hold
+    // layer >= 0: everything pending up to that layer, in forward order (a held block is needed);
+    // layer < 0: everything, latest layer first (end of forward)
+    int flushOffloads(int layer);
+
     // data parallelism
     int dp_rank = 0, dp_world = 1;
     void* nccl_comm = nullptr;
@@ -61,6 +81,8 @@ struct vdnnContext {
     int alloc(void** ptr, size_t bytes, int layer, int tag, bool isDynamic, std::initializer_list<cudaStream_t> streams);
     // Returns the block to the pool; its bytes stay fenced until the work enqueued so far on `after` is done.
     int release(void* ptr, size_t bytes, int layer, int tag, std::initializer_list<cudaStream_t> after);
+    // Same for srcData whose offload copy is still pending: fenced on `after` now, held until the copy is enqueued.
+    int releaseHeld(void* ptr, size_t bytes, int layer, int tag, std::initializer_list<cudaStream_t> after);
     int upload(void* dst, const void* src_h, size_t bytes);        // synchronous H2D (initialisation)
 };
 typedef vdnnContext* vdnnHandle_t;

@@ -10,6 +10,7 @@
 #include "network.h"
 
 #include <math.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include "dp_nccl.h"
@@ -63,7 +64,7 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
     stream_compute = stream_memory = NULL;
     customLayers = cfg.custom_layers; numCustomLayers = cfg.num_custom_layers;
     externalInput = false; forwardDone = false; stepCounter = 0;
-    stage_h = NULL; loss_d = NULL; loss_h = NULL; ev_loss = NULL; ev_step_end = NULL;
+    stage_h = NULL; loss_h = NULL; ev_loss = NULL; ev_step_end = NULL;
     launchesAtStepStart = launchesLastStep = 0;
     n_in = c_in = h_in = w_in = n_out = c_out = h_out = w_out = 0;
     for (int i = 0; i < DEFAULT_NUM_LAYER; i++) {
@@ -138,6 +139,14 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
             cudaEventCreateWithFlags(&ev_step_end, cudaEventDisableTiming) != cudaSuccess)
             state = VDNN_ERR_CUDA;
         if (state != VDNN_OK) return;
+        // Offload copies go out in the order backward needs them unless the reference's per-layer
+        // synchronisation is asked for (then each copy is enqueued, and waited for, in its own layer).
+        const char* order = getenv("VDNN_OFFLOAD_ORDER");
+        ctx.defer_offloads = !ctx.host_sync_per_layer && !(order && strcmp(order, "forward") == 0);
+        if (const char* eager = getenv("VDNN_EAGER_OFFLOAD_BYTES")) ctx.eager_offload_budget = strtoll(eager, NULL, 10);
+        vdnnPoolSetResolver([](void* user, unsigned long long token) {
+            static_cast<vdnnContext*>(user)->flushOffloads(static_cast<int>(token) - 1);
+        }, &ctx);
     }
     ctx.weights_pending.assign(DEFAULT_NUM_LAYER, 0);
 
@@ -155,8 +164,7 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
     if (!dry_run) {
         const size_t stage = sizeof(float) * (static_cast<size_t>(getInputSize()) + getOutputSize());
         if (cudaMallocHost(reinterpret_cast<void**>(&stage_h), stage) != cudaSuccess ||
-            cudaMallocHost(reinterpret_cast<void**>(&loss_h), 2 * sizeof(double)) != cudaSuccess ||
-            cudaMalloc(reinterpret_cast<void**>(&loss_d), 2 * sizeof(double)) != cudaSuccess)
+            cudaMallocHost(reinterpret_cast<void**>(&loss_h), 2 * sizeof(double)) != cudaSuccess)
             state = VDNN_ERR_CUDA;
     }
     if (ctx.capture) { capDst.resize(numLayers); capGrad.resize(numLayers); }
@@ -185,7 +193,6 @@ Network::~Network() {
     if (ev_step_end) cudaEventDestroy(ev_step_end);
     if (stage_h) cudaFreeHost(stage_h);
     if (loss_h) cudaFreeHost(loss_h);
-    if (loss_d) cudaFree(loss_d);
     if (stream_compute) cudaStreamDestroy(stream_compute);
     if (stream_memory) cudaStreamDestroy(stream_memory);
     if (ctx.stream_h2d) cudaStreamDestroy(ctx.stream_h2d);
@@ -478,6 +485,7 @@ int Network::forwardPropagation(bool isDynamic) {
         if (!ctx.dry_run) NET_CU(cudaEventRecord(ctx.ev_input_ready, stream_compute));
     }
     if (ctx.profiling) NET_CU(cudaEventRecord(ctx.pf_step_beg, stream_compute));
+    ctx.eager_offload_used = 0;
 
     for (int l = 0; l < numLayers; l++) {
         layer[l]->copySrcData(l == 0 ? inputData : layer[l - 1]->DstData());
@@ -495,18 +503,23 @@ int Network::forwardPropagation(bool isDynamic) {
             }
             /* Release srcData of this layer (network.cu:1094-1095); the block stays fenced until the
                copy and the kernels that read it have finished */
-            if (l != 0 && isOffload[l])
-                NET_TRY(ctx.release(layer[l]->SrcData(), sizeof(DATATYPE) * layer[l]->SrcDataSize(), l, TAG_SRC,
-                                    {stream_memory, stream_compute}));
+            if (l != 0 && isOffload[l]) {
+                if (ctx.offloadPending(l))
+                    NET_TRY(ctx.releaseHeld(layer[l]->SrcData(), sizeof(DATATYPE) * layer[l]->SrcDataSize(), l, TAG_SRC,
+                                            {stream_compute}));
+                else
+                    NET_TRY(ctx.release(layer[l]->SrcData(), sizeof(DATATYPE) * layer[l]->SrcDataSize(), l, TAG_SRC,
+                                        {stream_memory, stream_compute}));
+            }
         }
         if (ctx.capture) NET_TRY(captureTensor(capDst[l], layer[l]->DstData(), layer[l]->DstDataSize()));
         ctx.record(4, l, TAG_NONE, 0);
         memoryLine("Fwd", l, layer[l]->FwdWorkSpaceSize());
     }
+    if (!ctx.dry_run) NET_TRY(ctx.flushOffloads(-1));
     if (!ctx.dry_run && externalInput) {
         NET_TRY(vdnn_loss(n_out, c_out * h_out * w_out, (const float*)layer[numLayers - 1]->DstData(),
-                          (const float*)labelData, loss_d, stream_compute));
-        NET_CU(cudaMemcpyAsync(loss_h, loss_d, 2 * sizeof(double), cudaMemcpyDeviceToHost, stream_compute));
+                          (const float*)labelData, loss_h, stream_compute));
         NET_CU(cudaEventRecord(ev_loss, stream_compute));
     }
     forwardDone = true;
@@ -671,6 +684,12 @@ int Network::writeTensor(int l, int kind, const float* src_h, size_t count) {
     NET_TRY(synchronize());
     void* dst = kind == VDNN_TENSOR_WEIGHT ? layer[l]->FilterData() : layer[l]->BiasData();
     NET_CU(cudaMemcpy(dst, src_h, count * sizeof(float), cudaMemcpyHostToDevice));
+    return VDNN_OK;
+}
+
+int Network::setOffloadOrder(bool forwardOrder) {
+    if (state != VDNN_OK) return state;
+    ctx.defer_offloads = !forwardOrder && !ctx.host_sync_per_layer && !ctx.dry_run;
     return VDNN_OK;
 }
 

@@ -59,6 +59,7 @@ public:
     int             writeTensor(int layerId, int kind, const float* src_h, size_t count);
     int             getStats(vdnn_network_stats* out);
     int             setProfiling(bool enabled);
+    int             setOffloadOrder(bool forwardOrder);
     int             timeline(float* out);
     int             enableDataParallel(int rank, int world, const char* unique_id128);
     int             weightChecksum(uint64_t* out);
@@ -107,7 +108,6 @@ private:
     bool                forwardDone;
     uint64_t            stepCounter;
     float*              stage_h;               // pinned staging for generated input / labels
-    double*             loss_d;
     double*             loss_h;
     cudaEvent_t         ev_loss;
     cudaEvent_t         ev_step_end;

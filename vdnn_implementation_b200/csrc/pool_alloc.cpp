@@ -16,9 +16,12 @@ constexpr size_t kGranularity = 512;   // cnmem rounds every request up to 512 b
 
 struct Block { size_t size; bool free; };
 struct Fence { size_t begin, end; cudaEvent_t event; unsigned long long seq; cudaStream_t stream; };
+// Bytes whose last reader the host has not enqueued yet (vdnnPoolFreeHeld).
+struct Hold { size_t begin, end; unsigned long long token; };
+constexpr unsigned long long kHeldRank = 1ull << 62;   // held bytes rank behind every pending event
 
 struct Pool {
-    std::mutex mu;
+    std::recursive_mutex mu;            // the resolver re-enters through vdnnPoolResolve
     bool ready = false;
     bool is_virtual = false;
     int device = 0;
@@ -26,6 +29,9 @@ struct Pool {
     size_t capacity = 0, used = 0, peak = 0;
     std::map<size_t, Block> blocks;     // offset -> block
     std::vector<Fence> fences;
+    std::vector<Hold> holds;
+    vdnnPoolResolver_t resolver = nullptr;
+    void* resolver_user = nullptr;
     int fail_countdown = 0;
     unsigned long long next_seq = 1;
     std::vector<cudaEvent_t> spare_events;   // recycled fence events
@@ -48,7 +54,23 @@ unsigned long long range_readiness_locked(size_t begin, size_t end, const cudaSt
     unsigned long long youngest = 0;
     for (const Fence& f : g_pool.fences)
         if (f.begin < end && begin < f.end && f.seq > youngest && !is_consumer(f.stream, consumers, n)) youngest = f.seq;
+    for (const Hold& h : g_pool.holds)
+        if (h.begin < end && begin < h.end && kHeldRank + h.token > youngest) youngest = kHeldRank + h.token;
     return youngest;
+}
+
+// Has the host enqueue the readers that still hold bytes of [begin, end), lowest token first.
+cnmemStatus_t resolve_holds_locked(size_t begin, size_t end) {
+    for (;;) {
+        unsigned long long lowest = 0;
+        for (const Hold& h : g_pool.holds)
+            if (h.begin < end && begin < h.end && (lowest == 0 || h.token < lowest)) lowest = h.token;
+        if (lowest == 0) return CNMEM_STATUS_SUCCESS;
+        if (!g_pool.resolver) return CNMEM_STATUS_INVALID_ARGUMENT;
+        const size_t before = g_pool.holds.size();
+        g_pool.resolver(g_pool.resolver_user, lowest);
+        if (g_pool.holds.size() >= before) return CNMEM_STATUS_UNKNOWN_ERROR;   // the resolver did not resolve
+    }
 }
 
 // Best fit.  With consumer streams given, the block whose bytes those streams can use soonest wins even
@@ -66,21 +88,44 @@ cnmemStatus_t alloc_locked(void** ptr, size_t size, size_t* off_out, size_t* len
     const size_t need = round_up(size);
     auto best = g_pool.blocks.end();
     unsigned long long best_ready = 0;
-    const bool rank = num_consumers > 0 && !g_pool.fences.empty();
+    size_t best_at = 0;
+    const bool rank = (num_consumers > 0 && !g_pool.fences.empty()) || !g_pool.holds.empty();
+    // A candidate is a start offset inside a free block: the block's own start, or the edge of a pending
+    // event's (or hold's) byte range inside it -- after a long-lived copy has been queued on the first bytes
+    // of a large coalesced block, the bytes behind it are still usable at once.
+    auto consider = [&](std::map<size_t, Block>::iterator it, size_t at) {
+        const unsigned long long ready = rank ? range_readiness_locked(at, at + need, consumers, num_consumers) : 0;
+        const bool better = best == g_pool.blocks.end() || ready < best_ready ||
+            (ready == best_ready && ((at == it->first) > (best_at == best->first) ||
+                                     ((at == it->first) == (best_at == best->first) && it->second.size < best->second.size)));
+        if (better) { best = it; best_ready = ready; best_at = at; }
+    };
     for (auto it = g_pool.blocks.begin(); it != g_pool.blocks.end(); ++it) {
         if (!it->second.free || it->second.size < need) continue;
-        // only the first `need` bytes of the block would be handed out
-        const unsigned long long ready = rank ? range_readiness_locked(it->first, it->first + need, consumers, num_consumers) : 0;
-        if (best == g_pool.blocks.end() || ready < best_ready ||
-            (ready == best_ready && it->second.size < best->second.size)) {
-            best = it;
-            best_ready = ready;
+        const size_t lo = it->first, hi = it->first + it->second.size - need;   // admissible starts: [lo, hi]
+        consider(it, lo);
+        if (!rank || (best == it && best_ready == 0)) continue;
+        for (const Fence& f : g_pool.fences) {
+            if (f.end > lo && f.end <= hi) consider(it, f.end);
+            if (f.begin > lo && f.begin <= hi) consider(it, f.begin);
+        }
+        for (const Hold& h : g_pool.holds) {
+            if (h.end > lo && h.end <= hi) consider(it, h.end);
+            if (h.begin > lo && h.begin <= hi) consider(it, h.begin);
         }
     }
     if (best == g_pool.blocks.end()) return CNMEM_STATUS_OUT_OF_MEMORY;
-    const size_t off = best->first, rest = best->second.size - need;
-    best->second.size = need;
-    best->second.free = false;
+    size_t off = best->first;
+    const size_t total = best->second.size;
+    if (best_at > off) {                       // keep the bytes in front as a free block of their own
+        best->second.size = best_at - off;
+        g_pool.blocks[best_at] = Block{need, false};
+        off = best_at;
+    } else {
+        best->second.size = need;
+        best->second.free = false;
+    }
+    const size_t rest = (best->first + total) - (off + need);
     if (rest) g_pool.blocks[off + need] = Block{rest, true};
     g_pool.used += need;
     if (g_pool.used > g_pool.peak) g_pool.peak = g_pool.used;
@@ -136,7 +181,7 @@ extern "C" {
 
 cnmemStatus_t cnmemInit(int numDevices, const cnmemDevice_t* devices, unsigned) {
     if (numDevices != 1 || !devices) return CNMEM_STATUS_INVALID_ARGUMENT;
-    std::lock_guard<std::mutex> lock(g_pool.mu);
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     if (g_pool.ready) return CNMEM_STATUS_INVALID_ARGUMENT;
     size_t size = devices[0].size;
     if (const char* cap = std::getenv("VDNN_POOL_BYTES")) {
@@ -156,36 +201,42 @@ cnmemStatus_t cnmemInit(int numDevices, const cnmemDevice_t* devices, unsigned) 
     g_pool.blocks.clear();
     g_pool.blocks[0] = Block{size, true};
     g_pool.fences.clear();
+    g_pool.holds.clear();
     g_pool.fail_countdown = 0;
     g_pool.ready = true;
     return CNMEM_STATUS_SUCCESS;
 }
 
 cnmemStatus_t cnmemFinalize(void) {
-    std::lock_guard<std::mutex> lock(g_pool.mu);
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
     if (!g_pool.is_virtual) destroy_events_locked();
     cudaError_t e = g_pool.is_virtual ? cudaSuccess : cudaFree(g_pool.base);
     g_pool.base = nullptr;
     g_pool.blocks.clear();
     g_pool.fences.clear();
+    g_pool.holds.clear();
+    g_pool.resolver = nullptr;
     g_pool.capacity = g_pool.used = 0;
     g_pool.ready = false;
     return e == cudaSuccess ? CNMEM_STATUS_SUCCESS : CNMEM_STATUS_CUDA_ERROR;
 }
 
 cnmemStatus_t cnmemMalloc(void** ptr, size_t size, cudaStream_t) {
-    std::lock_guard<std::mutex> lock(g_pool.mu);
-    return alloc_locked(ptr, size, nullptr, nullptr);
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
+    size_t off = 0, len = 0;
+    const cnmemStatus_t st = alloc_locked(ptr, size, &off, &len);
+    if (st != CNMEM_STATUS_SUCCESS || size == 0 || g_pool.holds.empty()) return st;
+    return resolve_holds_locked(off, off + len);
 }
 
 cnmemStatus_t cnmemFree(void* ptr, cudaStream_t) {
-    std::lock_guard<std::mutex> lock(g_pool.mu);
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     return free_locked(ptr, nullptr, nullptr);
 }
 
 cnmemStatus_t cnmemMemGetInfo(size_t* freeMem, size_t* totalMem, cudaStream_t) {
-    std::lock_guard<std::mutex> lock(g_pool.mu);
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
     if (!freeMem || !totalMem) return CNMEM_STATUS_INVALID_ARGUMENT;
     *totalMem = g_pool.capacity;
@@ -194,7 +245,7 @@ cnmemStatus_t cnmemMemGetInfo(size_t* freeMem, size_t* totalMem, cudaStream_t) {
 }
 
 cnmemStatus_t cnmemPrintMemoryState(FILE* file, cudaStream_t) {
-    std::lock_guard<std::mutex> lock(g_pool.mu);
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
     if (!file) return CNMEM_STATUS_INVALID_ARGUMENT;
     std::fprintf(file, "pool device=%d capacity=%zu used=%zu peak=%zu blocks=%zu\n", g_pool.device,
@@ -219,7 +270,7 @@ const char* cnmemGetErrorString(cnmemStatus_t status) {
 }
 
 cnmemStatus_t vdnnPoolFreeAfter(void* ptr, const cudaStream_t* streams, int numStreams) {
-    std::lock_guard<std::mutex> lock(g_pool.mu);
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     size_t off = 0, len = 0;
     cnmemStatus_t st = free_locked(ptr, &off, &len);
     if (st != CNMEM_STATUS_SUCCESS || !ptr || g_pool.is_virtual) return st;
@@ -237,21 +288,67 @@ cnmemStatus_t vdnnPoolFreeAfter(void* ptr, const cudaStream_t* streams, int numS
 }
 
 cnmemStatus_t vdnnPoolMallocFor(void** ptr, size_t size, const cudaStream_t* streams, int numStreams) {
-    std::lock_guard<std::mutex> lock(g_pool.mu);
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     size_t off = 0, len = 0;
     if (!g_pool.is_virtual && g_pool.ready) drop_finished_fences_locked();
     cnmemStatus_t st = alloc_locked(ptr, size, &off, &len, streams, g_pool.is_virtual ? 0 : numStreams);
     if (st != CNMEM_STATUS_SUCCESS || size == 0) return st;
     if (g_pool.is_virtual) return CNMEM_STATUS_SUCCESS;
+    if (!g_pool.holds.empty()) {
+        st = resolve_holds_locked(off, off + len);
+        if (st != CNMEM_STATUS_SUCCESS) return st;
+    }
+    static const bool debug = std::getenv("VDNN_DEBUG_POOL") != nullptr;
     for (const Fence& f : g_pool.fences)
         if (f.begin < off + len && off < f.end)
-            for (int s = 0; s < numStreams; ++s)
-                if (streams[s] != f.stream && cudaStreamWaitEvent(streams[s], f.event, 0) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
+            for (int s = 0; s < numStreams; ++s) {
+                if (streams[s] == f.stream) continue;
+                if (debug) std::fprintf(stderr, "[pool] %zu bytes at %zu for stream %p wait for event %llu of stream %p on [%zu, %zu); %zu events pending\n",
+                                        len, off, (void*)streams[s], f.seq, (void*)f.stream, f.begin, f.end, g_pool.fences.size());
+                if (cudaStreamWaitEvent(streams[s], f.event, 0) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
+            }
+    return CNMEM_STATUS_SUCCESS;
+}
+
+cnmemStatus_t vdnnPoolSetResolver(vdnnPoolResolver_t resolver, void* user) {
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
+    g_pool.resolver = resolver;
+    g_pool.resolver_user = user;
+    return CNMEM_STATUS_SUCCESS;
+}
+
+cnmemStatus_t vdnnPoolFreeHeld(void* ptr, const cudaStream_t* streams, int numStreams, unsigned long long token) {
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
+    if (token == 0 || token >= kHeldRank) return CNMEM_STATUS_INVALID_ARGUMENT;
+    if (!ptr || !g_pool.ready || g_pool.is_virtual) return vdnnPoolFreeAfter(ptr, streams, numStreams);
+    const size_t off = static_cast<char*>(ptr) - g_pool.base;
+    auto it = g_pool.blocks.find(off);
+    if (it == g_pool.blocks.end() || it->second.free) return CNMEM_STATUS_INVALID_ARGUMENT;
+    const size_t len = it->second.size;
+    const cnmemStatus_t st = vdnnPoolFreeAfter(ptr, streams, numStreams);
+    if (st == CNMEM_STATUS_SUCCESS) g_pool.holds.push_back(Hold{off, off + len, token});
+    return st;
+}
+
+cnmemStatus_t vdnnPoolResolve(unsigned long long token, cudaStream_t stream) {
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
+    if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
+    size_t keep = 0;
+    for (size_t i = 0; i < g_pool.holds.size(); ++i) {
+        const Hold h = g_pool.holds[i];
+        if (h.token != token) { g_pool.holds[keep++] = h; continue; }
+        cudaEvent_t ev = nullptr;
+        if (!g_pool.spare_events.empty()) { ev = g_pool.spare_events.back(); g_pool.spare_events.pop_back(); }
+        else if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
+        if (cudaEventRecord(ev, stream) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
+        g_pool.fences.push_back(Fence{h.begin, h.end, ev, g_pool.next_seq++, stream});
+    }
+    g_pool.holds.resize(keep);
     return CNMEM_STATUS_SUCCESS;
 }
 
 cnmemStatus_t vdnnPoolHighWater(size_t* peakBytes, int reset) {
-    std::lock_guard<std::mutex> lock(g_pool.mu);
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
     if (peakBytes) *peakBytes = g_pool.peak;
     if (reset) g_pool.peak = g_pool.used;
@@ -259,13 +356,13 @@ cnmemStatus_t vdnnPoolHighWater(size_t* peakBytes, int reset) {
 }
 
 cnmemStatus_t vdnnPoolFailAfter(int k) {
-    std::lock_guard<std::mutex> lock(g_pool.mu);
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     g_pool.fail_countdown = k > 0 ? k : 0;
     return CNMEM_STATUS_SUCCESS;
 }
 
 cnmemStatus_t vdnnPoolInitVirtual(size_t size) {
-    std::lock_guard<std::mutex> lock(g_pool.mu);
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     if (g_pool.ready) return CNMEM_STATUS_INVALID_ARGUMENT;
     size = size / kGranularity * kGranularity;
     if (size == 0) return CNMEM_STATUS_INVALID_ARGUMENT;
@@ -277,13 +374,14 @@ cnmemStatus_t vdnnPoolInitVirtual(size_t size) {
     g_pool.blocks.clear();
     g_pool.blocks[0] = Block{size, true};
     g_pool.fences.clear();
+    g_pool.holds.clear();
     g_pool.fail_countdown = 0;
     g_pool.ready = true;
     return CNMEM_STATUS_SUCCESS;
 }
 
 int vdnnPoolIsInitialized(void) {
-    std::lock_guard<std::mutex> lock(g_pool.mu);
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     return g_pool.ready ? 1 : 0;
 }
 

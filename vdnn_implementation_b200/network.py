@@ -136,6 +136,11 @@ class Network:
     def set_profiling(self, enabled=True):
         check(lib().vdnn_network_set_profiling(self._h, int(enabled)), "set_profiling")
 
+    def set_offload_order(self, forward_order=False):
+        """False (default): offload copies reach the copy engine in the order backward needs them;
+        True: in layer order, as the reference enqueues them."""
+        check(lib().vdnn_network_set_offload_order(self._h, int(forward_order)), "set_offload_order")
+
     def timeline(self):
         """(num_layers, 8) array of ms since step start: fwd beg/end, offload beg/end, bwd beg/end, prefetch beg/end."""
         out = np.empty(8 * self.num_layers, np.float32)
