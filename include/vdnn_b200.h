@@ -283,6 +283,8 @@ typedef struct {
     double contraction_flops;     /* algorithmic FLOPs of those CONV / FC layers: 2*M*N*K each for forward,
                                      data gradient and filter gradient                             */
     double elementwise_bytes;     /* algorithmic bytes of the bandwidth-bound layers, forward + backward */
+    int64_t forced_offloads;      /* offload copies of the last forward that had to be enqueued early because
+                                     only their (held) bytes fitted an allocation: see vdnn_network_set_offload_order */
 } vdnn_network_stats;
 /* Fills timing fields only if profiling events were enabled with vdnn_network_set_profiling. */
 int vdnn_network_get_stats(vdnn_network* net, vdnn_network_stats* out);

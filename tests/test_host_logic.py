@@ -98,6 +98,51 @@ def test_pool_allocator_bookkeeping(vdnn):
         assert L.cnmemFinalize() == 0
 
 
+def test_pool_held_bytes_are_avoided_then_resolved_oldest_first(vdnn):
+    """Bytes released with vdnnPoolFreeHeld (their last reader is not enqueued yet) count as free, are
+    passed over while anything else fits -- also by placing a request behind them inside a coalesced free
+    block -- and are claimed through the resolver, lowest token first, when nothing else fits."""
+    L = C.CDLL(vdnn.lib_path())
+    L.vdnnPoolInitVirtual.argtypes = [C.c_size_t]
+    L.cnmemMalloc.argtypes = [C.POINTER(C.c_void_p), C.c_size_t, C.c_void_p]
+    L.cnmemFree.argtypes = [C.c_void_p, C.c_void_p]
+    L.cnmemMemGetInfo.argtypes = [C.POINTER(C.c_size_t), C.POINTER(C.c_size_t), C.c_void_p]
+    L.vdnnPoolFreeHeld.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_ulonglong]
+    L.vdnnPoolResolve.argtypes = [C.c_ulonglong, C.c_void_p]
+    RESOLVER = C.CFUNCTYPE(None, C.c_void_p, C.c_ulonglong)
+    L.vdnnPoolSetResolver.argtypes = [RESOLVER, C.c_void_p]
+    L.vdnnPoolMallocFor.argtypes = [C.POINTER(C.c_void_p), C.c_size_t, C.c_void_p, C.c_int]
+    K = 256 << 10
+    asked = []
+
+    def resolve(user, token):
+        asked.append(token)
+        assert L.vdnnPoolResolve(token, None) == 0
+
+    cb = RESOLVER(resolve)
+    assert L.vdnnPoolInitVirtual(4 * K) == 0
+    try:
+        assert L.vdnnPoolSetResolver(cb, None) == 0
+        a, b, c, d, e = (C.c_void_p() for _ in range(5))
+        for p in (a, b, c):
+            assert L.cnmemMalloc(C.byref(p), K, None) == 0
+        free, total = C.c_size_t(), C.c_size_t()
+        assert L.vdnnPoolFreeHeld(b, None, 0, 2) == 0 and L.vdnnPoolFreeHeld(a, None, 0, 1) == 0
+        L.cnmemMemGetInfo(C.byref(free), C.byref(total), None)
+        assert total.value - free.value == K                       # held bytes are free bytes
+        assert L.cnmemFree(c, None) == 0                            # [a b c tail] is one free block now; a and b held
+        assert L.vdnnPoolMallocFor(C.byref(d), K, None, 0) == 0
+        assert d.value == c.value and asked == []                   # placed behind the held bytes, nobody asked
+        assert L.vdnnPoolMallocFor(C.byref(e), K, None, 0) == 0
+        assert e.value == c.value + K and asked == []
+        assert L.vdnnPoolMallocFor(C.byref(c), 2 * K, None, 0) == 0 # only the held bytes are left
+        assert c.value == a.value and asked == [1, 2]
+        assert L.vdnnPoolMallocFor(C.byref(b), 512, None, 0) == 4   # OUT_OF_MEMORY: the pool is full
+        L.vdnnPoolSetResolver(RESOLVER(0), None)
+    finally:
+        assert L.cnmemFinalize() == 0
+
+
 MODELS = [("ALEXNET", 128), ("ALEXNET_LRN", 128), ("OVERFEAT", 128), ("VGG16_64", 64), ("VGG16_128", 128)]
 
 

@@ -163,3 +163,58 @@ def test_offload_bytes_and_overlap_are_reported(vdnn, oracle):
         assert st["kernel_launches"] > 37
     finally:
         net.close()
+
+
+def _alexnet_steps(vdnn, pool_bytes, forward_order, steps=2, batch=32):
+    net = vdnn.Network("ALEXNET", "VDNN_ALL", "VDNN_PERF_OPT_ALGO", batch_size=batch, pool_bytes=pool_bytes, learning_rate=1e-4)
+    try:
+        net.set_offload_order(forward_order)
+        forced = 0
+        for step in range(steps):
+            net.seed_input(1000 + step, 2000 + step)
+            net.forwardPropagation()
+            forced += net.stats()["forced_offloads"]
+            net.backwardPropagation()
+        net.synchronize()
+        return ([net.weights(l) for l in (0, 6, 13, 17)], [net.bias(l) for l in (0, 17)], net.loss(), net.trace(),
+                net.stats()["pool_peak_bytes"], forced)
+    finally:
+        net.close()
+
+
+def test_offload_order_is_not_observable(vdnn):
+    """Offload copies enqueued in the order backward needs them (the default) or in layer order (the
+    reference's): same host-side trace (allocations, releases, offloads, prefetches with the pool's byte
+    count after each), same peak, same step to rounding."""
+    by_need = _alexnet_steps(vdnn, 6e9, False)
+    in_order = _alexnet_steps(vdnn, 6e9, True)
+    assert by_need[3] == in_order[3] and by_need[4] == in_order[4]
+    assert by_need[5] == 0 and in_order[5] == 0
+    assert abs(by_need[2][0] - in_order[2][0]) < 1e-6 and abs(by_need[2][1] - in_order[2][1]) < 1e-5 * abs(in_order[2][1])
+    for a, b in zip(by_need[0], in_order[0]):
+        assert rel_err(a, b) < 1e-5
+    for a, b in zip(by_need[1], in_order[1]):        # bias gradients are summed with atomics
+        assert rel_err(a, b) < 1e-4
+    assert vdnn.ops.engine_status() == 0
+
+
+def test_held_blocks_are_given_back_under_pool_pressure(vdnn):
+    """A pool barely larger than the policy's peak: forward can only go on by reusing the bytes of tensors whose
+    offload copy is still held back, so the pool has those copies enqueued early (oldest first).  Same step as in a
+    roomy pool."""
+    dry = vdnn.Network("ALEXNET", "VDNN_ALL", "VDNN_PERF_OPT_ALGO", batch_size=32, device=-1, pool_bytes=6e9)
+    try:
+        dry.step()
+        dry.step()
+        peak = dry.stats()["pool_peak_bytes"]
+    finally:
+        dry.close()
+    tight = _alexnet_steps(vdnn, int(peak * 1.15), False)
+    roomy = _alexnet_steps(vdnn, 6e9, False)
+    assert tight[5] > 0 and roomy[5] == 0
+    assert tight[3] == roomy[3] and tight[4] == roomy[4] == peak
+    for a, b in zip(tight[0], roomy[0]):
+        assert rel_err(a, b) < 1e-5
+    for a, b in zip(tight[1], roomy[1]):
+        assert rel_err(a, b) < 1e-4
+    assert vdnn.ops.engine_status() == 0

@@ -57,7 +57,7 @@ class NetworkStats(C.Structure):
                 ("workspace_bytes_max", C.c_int64), ("grad_buffer_bytes", C.c_int64), ("step_ms", C.c_float),
                 ("offload_ms", C.c_float), ("prefetch_ms", C.c_float), ("copy_overlap_ms", C.c_float),
                 ("kernel_launches", C.c_int), ("contraction_ms", C.c_float), ("elementwise_ms", C.c_float),
-                ("contraction_flops", C.c_double), ("elementwise_bytes", C.c_double)]
+                ("contraction_flops", C.c_double), ("elementwise_bytes", C.c_double), ("forced_offloads", C.c_int64)]
 
     def asdict(self):
         return {f: getattr(self, f) for f, _ in self._fields_}

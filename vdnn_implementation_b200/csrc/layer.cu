@@ -470,6 +470,7 @@ int vdnnContext::flushOffloads(int layer) {
         for (size_t i = 0; i < pending_offloads.size(); ++i) {
             const PendingOffload p = pending_offloads[i];
             if (p.layer > layer) { pending_offloads[keep++] = p; continue; }
+            ++forced_offloads;
             const int st = submitOffload(p);
             if (st != 0) return st;
         }

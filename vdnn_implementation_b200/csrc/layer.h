@@ -59,7 +59,7 @@ struct vdnnContext {
     struct PendingOffload { int layer; void* host; const void* dev; size_t bytes; };
     bool defer_offloads = false;
     std::vector<PendingOffload> pending_offloads;
-    int64_t eager_offload_budget = 0, eager_offload_used = 0;
+    int64_t eager_offload_budget = 0, eager_offload_used = 0, forced_offloads = 0;
     bool offloadPending(int layer) const {
         for (const PendingOffload& p : pending_offloads) if (p.layer == layer) return true;
         return false;

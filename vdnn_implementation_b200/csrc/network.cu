@@ -486,6 +486,7 @@ int Network::forwardPropagation(bool isDynamic) {
     }
     if (ctx.profiling) NET_CU(cudaEventRecord(ctx.pf_step_beg, stream_compute));
     ctx.eager_offload_used = 0;
+    ctx.forced_offloads = 0;
 
     for (int l = 0; l < numLayers; l++) {
         layer[l]->copySrcData(l == 0 ? inputData : layer[l - 1]->DstData());
@@ -724,6 +725,7 @@ int Network::getStats(vdnn_network_stats* out) {
     out->prefetch_bytes = ctx.prefetch_bytes;
     out->workspace_bytes_max = ctx.workspace_bytes_max;
     out->kernel_launches = static_cast<int>(launchesLastStep);
+    out->forced_offloads = ctx.forced_offloads;
     for (int l = 0; l < numLayers; ++l)
         if (layer[l]->GradFilter()) out->grad_buffer_bytes += static_cast<int64_t>(sizeof(float)) * (tensorSize(l, VDNN_TENSOR_WEIGHT) + tensorSize(l, VDNN_TENSOR_BIAS));
     for (int l = 0; l < numLayers; ++l) {

@@ -90,9 +90,11 @@ cnmemStatus_t alloc_locked(void** ptr, size_t size, size_t* off_out, size_t* len
     unsigned long long best_ready = 0;
     size_t best_at = 0;
     const bool rank = (num_consumers > 0 && !g_pool.fences.empty()) || !g_pool.holds.empty();
-    // A candidate is a start offset inside a free block: the block's own start, or the edge of a pending
-    // event's (or hold's) byte range inside it -- after a long-lived copy has been queued on the first bytes
-    // of a large coalesced block, the bytes behind it are still usable at once.
+    // A candidate is a start offset inside a free block: the block's own start, or -- while at least a
+    // quarter of the pool stays free, because cutting a block in the middle fragments it -- the edge of a
+    // pending event's (or hold's) byte range inside it: after a long-lived copy has been queued on the first
+    // bytes of a large coalesced block, the bytes behind it are still usable at once.
+    const bool roomy = g_pool.used + need <= g_pool.capacity && (g_pool.capacity - g_pool.used - need) >= g_pool.capacity / 4;
     auto consider = [&](std::map<size_t, Block>::iterator it, size_t at) {
         const unsigned long long ready = rank ? range_readiness_locked(at, at + need, consumers, num_consumers) : 0;
         const bool better = best == g_pool.blocks.end() || ready < best_ready ||
@@ -104,7 +106,7 @@ cnmemStatus_t alloc_locked(void** ptr, size_t size, size_t* off_out, size_t* len
         if (!it->second.free || it->second.size < need) continue;
         const size_t lo = it->first, hi = it->first + it->second.size - need;   // admissible starts: [lo, hi]
         consider(it, lo);
-        if (!rank || (best == it && best_ready == 0)) continue;
+        if (!rank || !roomy || (best == it && best_ready == 0)) continue;
         for (const Fence& f : g_pool.fences) {
             if (f.end > lo && f.end <= hi) consider(it, f.end);
             if (f.begin > lo && f.begin <= hi) consider(it, f.begin);
@@ -293,11 +295,11 @@ cnmemStatus_t vdnnPoolMallocFor(void** ptr, size_t size, const cudaStream_t* str
     if (!g_pool.is_virtual && g_pool.ready) drop_finished_fences_locked();
     cnmemStatus_t st = alloc_locked(ptr, size, &off, &len, streams, g_pool.is_virtual ? 0 : numStreams);
     if (st != CNMEM_STATUS_SUCCESS || size == 0) return st;
-    if (g_pool.is_virtual) return CNMEM_STATUS_SUCCESS;
     if (!g_pool.holds.empty()) {
         st = resolve_holds_locked(off, off + len);
         if (st != CNMEM_STATUS_SUCCESS) return st;
     }
+    if (g_pool.is_virtual) return CNMEM_STATUS_SUCCESS;
     static const bool debug = std::getenv("VDNN_DEBUG_POOL") != nullptr;
     for (const Fence& f : g_pool.fences)
         if (f.begin < off + len && off < f.end)
@@ -320,7 +322,7 @@ cnmemStatus_t vdnnPoolSetResolver(vdnnPoolResolver_t resolver, void* user) {
 cnmemStatus_t vdnnPoolFreeHeld(void* ptr, const cudaStream_t* streams, int numStreams, unsigned long long token) {
     std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     if (token == 0 || token >= kHeldRank) return CNMEM_STATUS_INVALID_ARGUMENT;
-    if (!ptr || !g_pool.ready || g_pool.is_virtual) return vdnnPoolFreeAfter(ptr, streams, numStreams);
+    if (!ptr || !g_pool.ready) return vdnnPoolFreeAfter(ptr, streams, numStreams);
     const size_t off = static_cast<char*>(ptr) - g_pool.base;
     auto it = g_pool.blocks.find(off);
     if (it == g_pool.blocks.end() || it->second.free) return CNMEM_STATUS_INVALID_ARGUMENT;
@@ -337,6 +339,7 @@ cnmemStatus_t vdnnPoolResolve(unsigned long long token, cudaStream_t stream) {
     for (size_t i = 0; i < g_pool.holds.size(); ++i) {
         const Hold h = g_pool.holds[i];
         if (h.token != token) { g_pool.holds[keep++] = h; continue; }
+        if (g_pool.is_virtual) continue;           // bookkeeping only: the hold just goes away
         cudaEvent_t ev = nullptr;
         if (!g_pool.spare_events.empty()) { ev = g_pool.spare_events.back(); g_pool.spare_events.pop_back(); }
         else if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
