@@ -26,7 +26,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 MODELS = {"ALEXNET": (128, 227), "ALEXNET_LRN": (128, 227), "OVERFEAT": (128, 231), "VGG16_64": (64, 224),
-          "VGG16_128": (128, 224)}
+          "VGG16_128": (128, 224), "VGG16_256": (256, 224)}
 
 
 def parse():

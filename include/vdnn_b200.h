@@ -144,6 +144,15 @@ int vdnn_relu_fwd(size_t count, const float* x, float* y, void* stream);
  * for signature parity and not read. */
 int vdnn_relu_bwd(size_t count, const float* y, const float* dy, const float* x, float* dx,
                   void* stream);
+/* cudnnActivationForward / Backward with the descriptor's mode made an argument (layer.cu:355-385, 774-811):
+ * RELU as above; TANH y = tanh(x), dx = dy (1 - y^2); SIGMOID y = 1 / (1 + exp(-x)), dx = dy y (1 - y).
+ * No model of the reference uses TANH or SIGMOID; its Layer class accepts them (vdnn.h:28-29). */
+#define VDNN_ACT_RELU 0
+#define VDNN_ACT_TANH 1
+#define VDNN_ACT_SIGMOID 2
+int vdnn_activation_fwd(int mode, size_t count, const float* x, float* y, void* stream);
+int vdnn_activation_bwd(int mode, size_t count, const float* y, const float* dy, const float* x, float* dx,
+                        void* stream);
 /* cudnnPoolingForward, MAX, NOT_PROPAGATE_NAN, pad 0 (layer.cu:875-882, 417-428). */
 int vdnn_maxpool_fwd(int n, int c, int h, int w, int win_h, int win_w, int stride_h, int stride_w,
                      const float* x, float* y, void* stream);

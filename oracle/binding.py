@@ -172,6 +172,21 @@ def relu_fwd(x):
     return y
 
 
+def act_fwd(mode, x):
+    """mode 1 tanh, 2 sigmoid."""
+    x = _f32(x)
+    y = np.empty_like(x)
+    lib().orc_act_fwd(C.c_int(mode), C.c_size_t(x.size), _p(x), _p(y))
+    return y
+
+
+def act_bwd(mode, y, dy):
+    y, dy = _f32(y), _f32(dy)
+    dx = np.empty_like(y)
+    lib().orc_act_bwd(C.c_int(mode), C.c_size_t(y.size), _p(y), _p(dy), _p(dx))
+    return dx
+
+
 def relu_bwd(y, dy, x):
     y, dy, x = _f32(y), _f32(dy), _f32(x)
     dx = np.empty_like(x)

@@ -312,6 +312,23 @@ void orc_relu_bwd(size_t n, const float* y, const float* dy, const float* x, flo
     for (size_t i = 0; i < n; ++i) dx[i] = (x[i] > 0.0f) ? dy[i] : 0.0f;
 }
 
+/* tanh / sigmoid as cudnnActivationForward / Backward define them: the backward reads y only. */
+void orc_act_fwd(int mode, size_t n, const float* x, float* y) {
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; ++i) {
+        const double v = x[i];
+        y[i] = (float)(mode == 1 ? tanh(v) : 1.0 / (1.0 + exp(-v)));
+    }
+}
+
+void orc_act_bwd(int mode, size_t n, const float* y, const float* dy, float* dx) {
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; ++i) {
+        const double a = y[i], d = dy[i];
+        dx[i] = (float)(mode == 1 ? d * (1.0 - a * a) : d * a * (1.0 - a));
+    }
+}
+
 /* ------------------------------------------------------------------------- */
 /* Max pooling, pad 0, NOT_PROPAGATE_NAN (layer.cu:417-428).  Backward routes  */
 /* dy to the first window element (row-major scan) equal to the window max.    */
@@ -647,6 +664,8 @@ void orc_net_forward(orc_net* net) {
             orc_add_bias(s->n, s->k, 1, net->b[l], dst);
             break;
         case ORC_RELU: orc_relu_fwd(src_size(s), src, dst); break;
+        case ORC_TANH: orc_act_fwd(1, src_size(s), src, dst); break;
+        case ORC_SIGMOID: orc_act_fwd(2, src_size(s), src, dst); break;
         case ORC_POOL:
             orc_maxpool_fwd(s->n, s->c, s->h, s->w, s->r, s->s, s->stride_h, s->stride_w, src, dst);
             break;
@@ -687,6 +706,8 @@ void orc_net_backward(orc_net* net) {
             orc_conv_bwd_bias(s->n, s->k, 1, nlr, dy, 1.0f, net->b[l]);
             break;
         case ORC_RELU: orc_relu_bwd(src_size(s), dst, dy, src, dx); break;
+        case ORC_TANH: orc_act_bwd(1, src_size(s), dst, dy, dx); break;
+        case ORC_SIGMOID: orc_act_bwd(2, src_size(s), dst, dy, dx); break;
         case ORC_POOL:
             orc_maxpool_bwd(s->n, s->c, s->h, s->w, s->r, s->s, s->stride_h, s->stride_w, dst, dy, src, dx);
             break;

@@ -78,6 +78,9 @@ void orc_sgemm(int transa, int transb, int m, int n, int k, float alpha, const f
                const float* B, int ldb, float beta, float* C, int ldc);
 void orc_relu_fwd(size_t n, const float* x, float* y);                       /* layer.cu:774-781 */
 void orc_relu_bwd(size_t n, const float* y, const float* dy, const float* x, float* dx); /* 802-811 */
+/* the other two activation modes the reference's Layer accepts (layer.cu:361-368); mode 1 tanh, 2 sigmoid */
+void orc_act_fwd(int mode, size_t n, const float* x, float* y);
+void orc_act_bwd(int mode, size_t n, const float* y, const float* dy, float* dx);
 void orc_maxpool_fwd(int n, int c, int h, int w, int win_h, int win_w, int stride_h, int stride_w,
                      const float* x, float* y);                              /* layer.cu:875-882 */
 void orc_maxpool_bwd(int n, int c, int h, int w, int win_h, int win_w, int stride_h, int stride_w,

@@ -143,7 +143,8 @@ def test_pool_held_bytes_are_avoided_then_resolved_oldest_first(vdnn):
         assert L.cnmemFinalize() == 0
 
 
-MODELS = [("ALEXNET", 128), ("ALEXNET_LRN", 128), ("OVERFEAT", 128), ("VGG16_64", 64), ("VGG16_128", 128)]
+MODELS = [("ALEXNET", 128), ("ALEXNET_LRN", 128), ("OVERFEAT", 128), ("VGG16_64", 64), ("VGG16_128", 128),
+          ("VGG16_256", 256)]      # 822 M-element tensors: byte counts beyond 2^31 (the reference's int sizes wrap there)
 
 
 @pytest.mark.parametrize("model,batch", MODELS)
@@ -152,7 +153,7 @@ def test_network_schedule_equals_reference_schedule(vdnn, oracle, model, batch, 
     """Event-for-event: every pool allocation and release, every offload and prefetch, and the pool
     usage after each of them, over two iterations."""
     for fix in (True, False):
-        net = vdnn.Network(model, policy, vdnn.VDNN_MEMORY_OPT_ALGO, device=-1, pool_bytes=40e9, fix_input_leak=fix)
+        net = vdnn.Network(model, policy, vdnn.VDNN_MEMORY_OPT_ALGO, device=-1, pool_bytes=170e9, fix_input_leak=fix)
         try:
             specs = [s.astuple() for s in net.layer_specs()]
             assert specs == [s.astuple() for s in oracle.model_layers(getattr(oracle, model), batch)]

@@ -189,6 +189,30 @@ POOL_CASES = [  # n, c, h, w, win, stride
 ]
 
 
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("count", [1, 5, 4096, 3 * 55 * 55 + 3])
+def test_tanh_sigmoid(vdnn, oracle, mode, count):
+    """The two activation modes besides ReLU that the reference's Layer accepts (layer.cu:361-368)."""
+    ops = vdnn.ops
+    rng = np.random.default_rng(100 * mode + count)
+    x = (4.0 * rng.standard_normal(count)).astype(np.float32)
+    x[0] = 0.0
+    xd = dev(x)
+    yd = torch.empty_like(xd)
+    ops.activation_fwd(mode, count, xd, yd)
+    y = host(yd)
+    assert np.abs(y - oracle.act_fwd(mode, x)).max() < 3e-7          # values are in [-1, 1]: a few ulp
+    dy = rng.standard_normal(count, dtype=np.float32)
+    dxd = torch.empty_like(xd)
+    ops.activation_bwd(mode, count, yd, dev(dy), xd, dxd)
+    assert rel_err(host(dxd), oracle.act_bwd(mode, y, dy)) < 1e-6
+    # mode 0 is the ReLU entry point
+    ops.activation_fwd(0, count, xd, yd)
+    assert np.array_equal(host(yd), oracle.relu_fwd(x))
+    with pytest.raises(vdnn.VdnnError):
+        ops.activation_fwd(3, count, xd, yd)
+
+
 @pytest.mark.parametrize("case", POOL_CASES)
 @pytest.mark.parametrize("ties", [False, True])
 def test_maxpool(vdnn, oracle, case, ties):

@@ -59,6 +59,17 @@ def test_tiny_network_all_policies(vdnn, oracle, policy, algo):
         assert st["pool_peak_bytes"] == summ.peak_bytes
 
 
+def test_tanh_and_sigmoid_layers(vdnn, oracle):
+    # the activation types besides RELU that the Layer class takes (vdnn.h:28-29); no stock model uses them
+    TANH, SIGMOID = 4, 5
+    specs = tiny_net(4)
+    relus = [i for i, s in enumerate(specs) if s[0] == 3]
+    specs[relus[0]] = (TANH,) + tuple(specs[relus[0]][1:])
+    specs[relus[1]] = (SIGMOID,) + tuple(specs[relus[1]][1:])
+    assert [s[0] for s in specs].count(TANH) == 1 and [s[0] for s in specs].count(SIGMOID) == 1
+    _run(vdnn, oracle, specs, "CUSTOM_CNN", "VDNN_ALL", "VDNN_MEMORY_OPT_ALGO", 4, 0.05)
+
+
 def test_reference_schedule_mode_gives_same_numbers(vdnn, oracle):
     # host synchronisation after every layer, as the reference does, instead of event ordering
     _run(vdnn, oracle, tiny_net(4), "CUSTOM_CNN", "VDNN_ALL", "VDNN_MEMORY_OPT_ALGO", 4, 0.05, host_sync=True)

@@ -68,6 +68,18 @@ def test_maxpool_tie_goes_to_first_element(oracle):
     assert np.array_equal(dx[0, 0], expect)
 
 
+def test_tanh_sigmoid_against_numpy(oracle):
+    rng = np.random.default_rng(5)
+    x = (3.0 * rng.standard_normal(1000)).astype(np.float32)
+    dy = rng.standard_normal(1000).astype(np.float32)
+    t = oracle.act_fwd(1, x)
+    s = oracle.act_fwd(2, x)
+    assert np.allclose(t, np.tanh(x.astype(np.float64)), atol=1e-7)
+    assert np.allclose(s, 1.0 / (1.0 + np.exp(-x.astype(np.float64))), atol=1e-7)
+    assert np.allclose(oracle.act_bwd(1, t, dy), dy * (1.0 - t.astype(np.float64) ** 2), atol=1e-6)
+    assert np.allclose(oracle.act_bwd(2, s, dy), dy * s.astype(np.float64) * (1.0 - s), atol=1e-6)
+
+
 def test_relu_softmax_lrn_sub(oracle):
     rng = np.random.default_rng(5)
     x = rng.standard_normal((4, 1000), dtype=np.float32) * 3

@@ -93,6 +93,8 @@ SIGNATURES = {
     "vdnn_fill": (_I, [_Z, _F, _P, _P]),
     "vdnn_relu_fwd": (_I, [_Z, _P, _P, _P]),
     "vdnn_relu_bwd": (_I, [_Z, _P, _P, _P, _P, _P]),
+    "vdnn_activation_fwd": (_I, [_I, _Z, _P, _P, _P]),
+    "vdnn_activation_bwd": (_I, [_I, _Z, _P, _P, _P, _P, _P]),
     "vdnn_maxpool_fwd": (_I, [_I] * 8 + [_P, _P, _P]),
     "vdnn_maxpool_bwd": (_I, [_I] * 8 + [_P, _P, _P, _P, _P]),
     "vdnn_softmax_fwd": (_I, [_I, _I, _P, _P, _P]),

@@ -96,6 +96,46 @@ __global__ void __launch_bounds__(kThreads) relu_bwd_kernel(size_t n4, size_t n,
         dx[j] = x[j] > 0.0f ? dy[j] : 0.0f;
 }
 
+// ---------------------------------------------------------------- tanh / sigmoid (mode as in vdnn_b200.h)
+template <int MODE> __device__ __forceinline__ float act1(float x) {
+    return MODE == VDNN_ACT_TANH ? tanhf(x) : 1.0f / (1.0f + expf(-x));
+}
+template <int MODE> __device__ __forceinline__ float dact1(float y, float dy) {
+    return MODE == VDNN_ACT_TANH ? dy * (1.0f - y * y) : dy * y * (1.0f - y);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads) act_fwd_kernel(size_t n4, size_t n, const float* __restrict__ x,
+                                                           float* __restrict__ y) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    const size_t first = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const float4* x4 = reinterpret_cast<const float4*>(x);
+    float4* y4 = reinterpret_cast<float4*>(y);
+    for (size_t i = first; i < n4; i += stride) {
+        float4 v = __ldcs(x4 + i);
+        v.x = act1<MODE>(v.x); v.y = act1<MODE>(v.y); v.z = act1<MODE>(v.z); v.w = act1<MODE>(v.w);
+        y4[i] = v;
+    }
+    for (size_t j = n4 * 4 + first; j < n; j += stride) y[j] = act1<MODE>(x[j]);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads) act_bwd_kernel(size_t n4, size_t n, const float* __restrict__ y,
+                                                           const float* __restrict__ dy, float* __restrict__ dx) {
+    const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+    const size_t first = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const float4* y4 = reinterpret_cast<const float4*>(y);
+    const float4* d4 = reinterpret_cast<const float4*>(dy);
+    float4* o4 = reinterpret_cast<float4*>(dx);
+    for (size_t i = first; i < n4; i += stride) {
+        const float4 a = __ldcs(y4 + i), d = __ldcs(d4 + i);
+        float4 o;
+        o.x = dact1<MODE>(a.x, d.x); o.y = dact1<MODE>(a.y, d.y); o.z = dact1<MODE>(a.z, d.z); o.w = dact1<MODE>(a.w, d.w);
+        o4[i] = o;
+    }
+    for (size_t j = n4 * 4 + first; j < n; j += stride) dx[j] = dact1<MODE>(y[j], dy[j]);
+}
+
 // ---------------------------------------------------------------- out = a - b, w += alpha g, fill
 __global__ void __launch_bounds__(kThreads) sub_kernel(size_t n, const float* __restrict__ a,
                                                        const float* __restrict__ b, float* __restrict__ out) {
@@ -493,6 +533,32 @@ int vdnn_relu_bwd(size_t count, const float* y, const float* dy, const float* x,
     if (count == 0) return VDNN_OK;
     const size_t n4 = (aligned16(x) && aligned16(dy) && aligned16(dx)) ? count / 4 : 0;
     relu_bwd_kernel<<<stream_grid(n4 ? n4 : count, 2), kThreads, 0, as_stream(stream)>>>(n4, count, dy, x, dx);
+    VDNN_LAUNCHED();
+    return VDNN_OK;
+}
+
+int vdnn_activation_fwd(int mode, size_t count, const float* x, float* y, void* stream) {
+    if (mode == VDNN_ACT_RELU) return vdnn_relu_fwd(count, x, y, stream);
+    if (mode != VDNN_ACT_TANH && mode != VDNN_ACT_SIGMOID) return VDNN_ERR_UNSUPPORTED;
+    if (!x || !y) return VDNN_ERR_BAD_ARG;
+    if (count == 0) return VDNN_OK;
+    const size_t n4 = (aligned16(x) && aligned16(y)) ? count / 4 : 0;
+    const int grid = stream_grid(n4 ? n4 : count, 1);
+    if (mode == VDNN_ACT_TANH) act_fwd_kernel<VDNN_ACT_TANH><<<grid, kThreads, 0, as_stream(stream)>>>(n4, count, x, y);
+    else act_fwd_kernel<VDNN_ACT_SIGMOID><<<grid, kThreads, 0, as_stream(stream)>>>(n4, count, x, y);
+    VDNN_LAUNCHED();
+    return VDNN_OK;
+}
+
+int vdnn_activation_bwd(int mode, size_t count, const float* y, const float* dy, const float* x, float* dx, void* stream) {
+    if (mode == VDNN_ACT_RELU) return vdnn_relu_bwd(count, y, dy, x, dx, stream);
+    if (mode != VDNN_ACT_TANH && mode != VDNN_ACT_SIGMOID) return VDNN_ERR_UNSUPPORTED;
+    if (!y || !dy || !dx) return VDNN_ERR_BAD_ARG;
+    if (count == 0) return VDNN_OK;
+    const size_t n4 = (aligned16(y) && aligned16(dy) && aligned16(dx)) ? count / 4 : 0;
+    const int grid = stream_grid(n4 ? n4 : count, 1);
+    if (mode == VDNN_ACT_TANH) act_bwd_kernel<VDNN_ACT_TANH><<<grid, kThreads, 0, as_stream(stream)>>>(n4, count, y, dy, dx);
+    else act_bwd_kernel<VDNN_ACT_SIGMOID><<<grid, kThreads, 0, as_stream(stream)>>>(n4, count, y, dy, dx);
     VDNN_LAUNCHED();
     return VDNN_OK;
 }

@@ -212,11 +212,11 @@ int Layer::forward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, void* workS
     switch (layerType) {
     case FC_GEMM: return fullyConnectedForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
     case CONV: case FC_CONV: return convolutionForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
-    case RELU: return activationForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
+    case RELU: case TANH: case SIGMOID: return activationForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
     case SOFTMAX: return softmaxForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
     case POOL: return poolingForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
     case LRN: return lrnForward(_offloaded, _offloadedSrcData_h, workSpace, isDynamic);
-    default: return VDNN_ERR_UNSUPPORTED;        // TANH, SIGMOID, CONCATENATE: used by no model
+    default: return VDNN_ERR_UNSUPPORTED;        // CONCATENATE: used by no model
     }
 }
 
@@ -225,7 +225,7 @@ int Layer::backward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, v
     switch (layerType) {
     case FC_GEMM: return fullyConnectedBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
     case CONV: case FC_CONV: return convolutionBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
-    case RELU: return activationBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
+    case RELU: case TANH: case SIGMOID: return activationBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
     case SOFTMAX: return softmaxBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
     case POOL: return poolingBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
     case LRN: return lrnBackward(_layer_id_to_prefetch, _prefetchedSrcData_h, _srcDataToPrefetch, _prefetch_bytes, workSpace, isDynamic);
@@ -349,11 +349,12 @@ int Layer::fullyConnectedBackward(int _layer_id_to_prefetch, DATATYPE* _prefetch
     return handle->release(oneVec, sizeof(DATATYPE) * n_out, layerId, TAG_ONES, {});
 }
 
-/* ------------------------------------------------------------------ ReLU (layer.cu:766-814) */
+/* ------------------------------------------------------------------ ReLU / tanh / sigmoid (layer.cu:355-385, 766-814) */
 
 int Layer::activationForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, void*, bool isDynamic) {
     FWD_PROLOGUE();
-    DEV(vdnn_relu_fwd(static_cast<size_t>(SrcDataSize()), (const float*)srcData, (float*)dstData, *stream_compute));
+    const int mode = layerType == TANH ? VDNN_ACT_TANH : (layerType == SIGMOID ? VDNN_ACT_SIGMOID : VDNN_ACT_RELU);
+    DEV(vdnn_activation_fwd(mode, static_cast<size_t>(SrcDataSize()), (const float*)srcData, (float*)dstData, *stream_compute));
     if (_offloaded[layerId]) { const int o = offloadSrcData(_offloaded, _offloadedSrcData_h); if (o != 0) return o; }
     MARK(ev_fwd_done);
     return 0;
@@ -362,8 +363,9 @@ int Layer::activationForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, v
 int Layer::activationBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, void* _srcDataToPrefetch,
                               unsigned long _prefetch_bytes, void*, bool isDynamic) {
     BWD_PROLOGUE();
-    DEV(vdnn_relu_bwd(static_cast<size_t>(SrcDataSize()), (const float*)dstData, (const float*)diffData,
-                      (const float*)srcData, (float*)gradData, *stream_compute));
+    const int mode = layerType == TANH ? VDNN_ACT_TANH : (layerType == SIGMOID ? VDNN_ACT_SIGMOID : VDNN_ACT_RELU);
+    DEV(vdnn_activation_bwd(mode, static_cast<size_t>(SrcDataSize()), (const float*)dstData, (const float*)diffData,
+                            (const float*)srcData, (float*)gradData, *stream_compute));
     MARK(ev_bwd_done);
     return 0;
 }

@@ -386,11 +386,13 @@ void Network::setVdnnType(vdnn_t newVdnnType) {
     }
 }
 
-int Network::findMaxDxDySize() {            // network.cu:1010-1023 (bytes)
+// network.cu:1010-1023 (bytes).  The reference returns an int, which wraps for VGG16_256 (822 M elements
+// x 4 bytes) and makes its BASELINE allocation fail; the byte count is kept in 64 bits here.
+size_t Network::findMaxDxDySize() {
     int ret = 0;
     for (int i = 0; i < numLayers; i++) ret = std::max(ret, layer[i]->SrcDataSize());
     ret = std::max(ret, layer[numLayers - 1]->DstDataSize());
-    return ret * static_cast<int>(sizeof(DATATYPE));
+    return static_cast<size_t>(ret) * sizeof(DATATYPE);
 }
 
 int Network::findMaxWorkSpaceSize() {       // network.cu:1025-1040: the maximum is kept in an int
@@ -736,7 +738,7 @@ int Network::getStats(vdnn_network_stats* out) {
             // forward, data gradient and filter gradient are each one M x N x K contraction
             out->contraction_flops += 3.0 * 2.0 * dst * (static_cast<double>(L->FilterDataSize()) / L->OutputC());
             break;
-        case RELU: out->elementwise_bytes += 4.0 * (2.0 * src + 3.0 * src); break;      // fwd r+w, bwd x,dy -> dx
+        case RELU: case TANH: case SIGMOID: out->elementwise_bytes += 4.0 * (2.0 * src + 3.0 * src); break;   // fwd r+w, bwd x (or y),dy -> dx
         case POOL: out->elementwise_bytes += 4.0 * ((src + dst) + (2.0 * src + dst)); break;
         case LRN: out->elementwise_bytes += 4.0 * (2.0 * src + 4.0 * src); break;
         case SOFTMAX: out->elementwise_bytes += 4.0 * (2.0 * src + 3.0 * src); break;

@@ -27,7 +27,7 @@ public:
     void            setVdnnType(vdnn_t newVdnnType);
 
     /* Find max dx, dy, workspace size */
-    int             findMaxDxDySize();
+    size_t          findMaxDxDySize();
     int             findMaxWorkSpaceSize();
 
     /* Computation for training network */

@@ -90,6 +90,17 @@ def relu_bwd(count, y, dy, x, dx, stream=0):
     check(lib().vdnn_relu_bwd(count, _p(y), _p(dy), _p(x), _p(dx), _s(stream)), "relu_bwd")
 
 
+ACT_RELU, ACT_TANH, ACT_SIGMOID = 0, 1, 2
+
+
+def activation_fwd(mode, count, x, y, stream=0):
+    check(lib().vdnn_activation_fwd(mode, count, _p(x), _p(y), _s(stream)), "activation_fwd")
+
+
+def activation_bwd(mode, count, y, dy, x, dx, stream=0):
+    check(lib().vdnn_activation_bwd(mode, count, _p(y), _p(dy), _p(x), _p(dx), _s(stream)), "activation_bwd")
+
+
 def maxpool_fwd(n, c, h, w, win, stride, x, y, stream=0):
     check(lib().vdnn_maxpool_fwd(n, c, h, w, win[0], win[1], stride[0], stride[1], _p(x), _p(y), _s(stream)), "maxpool_fwd")
 
