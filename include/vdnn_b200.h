@@ -298,6 +298,16 @@ typedef struct {
 /* Fills timing fields only if profiling events were enabled with vdnn_network_set_profiling. */
 int vdnn_network_get_stats(vdnn_network* net, vdnn_network_stats* out);
 int vdnn_network_set_profiling(vdnn_network* net, int enabled);
+/* VDNN_DYNAMIC_ALGO (network.cu:946-1008, layer.cu:1091-1147): the constructor ignores the given policy and
+ * settles on the first of VDNN_NONE, VDNN_CONV, VDNN_ALL that trains within the pool with the workspace-using
+ * algorithms; failing all three it keeps VDNN_ALL and picks, per convolution and operation, the workspace-using
+ * algorithm where the iteration still fits.  A model that does not fit under VDNN_ALL with zero workspace is
+ * refused (VDNN_ERR_OUT_OF_MEMORY; the reference asserts).  Candidates are tried by replaying their allocation
+ * schedule against a bookkeeping-only pool of the same capacity, not by running them.
+ * vdnn_network_selected reports the outcome: *algo_mode is VDNN_DYNAMIC_ALGO (2) when the choice is per layer,
+ * and vdnn_network_layer_algos then gives VDNN_ALGO_* for forward, data gradient, filter gradient of a layer. */
+int vdnn_network_selected(vdnn_network* net, int* vdnn_type, int* algo_mode);
+int vdnn_network_layer_algos(vdnn_network* net, int layer, int* out3);
 /* Order in which the offload copies of one forward pass reach the device-to-host copy engine.  The
  * reference enqueues each copy in its own layer (layer.cu:969-977) and waits for it there
  * (network.cu:1090-1091).  Without those waits the engine serves copies first in, first out, while

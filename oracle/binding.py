@@ -285,6 +285,26 @@ def policy_trace(specs, vdnn_type, ws=None, iterations=1, fix_input_leak=False, 
     return events, summ
 
 
+def dynamic_choice(specs, capacity, ws_perf, fix_input_leak=True):
+    """VDNN_DYNAMIC_ALGO as network.cu:946-1008 orders it, decided on the simulated peak of two iterations:
+    VDNN_ALL + MEMORY_OPT must fit (else None); then the first of VDNN_NONE, VDNN_CONV, VDNN_ALL that fits
+    with the workspace-using algorithms (`ws_perf`: per layer, bytes for forward / data gradient / filter
+    gradient); else (VDNN_ALL, "per layer").  Peak bytes ignore fragmentation, so a pool within a few large
+    tensors of a peak can be judged differently by a real allocator."""
+    BASELINE, VDNN_NONE, VDNN_ALL, VDNN_CONV = 0, 1, 2, 3
+    zero = [[0, 0, 0] for _ in specs]
+
+    def fits(policy, ws):
+        return policy_trace(specs, policy, ws=ws, iterations=2, fix_input_leak=fix_input_leak)[1].peak_bytes <= capacity
+
+    if not fits(VDNN_ALL, zero):
+        return None
+    for policy in (VDNN_NONE, VDNN_CONV, VDNN_ALL):
+        if fits(policy, ws_perf):
+            return policy, 1
+    return VDNN_ALL, 2
+
+
 class Net:
     """Whole-network CPU training step (forward, backward with fused SGD)."""
 

@@ -203,11 +203,78 @@ def test_pool_too_small_is_reported_not_fatal(vdnn):
     net.close()
 
 
+def _perf_workspaces(vdnn, specs):
+    L = vdnn.lib()
+    ws = []
+    for s in specs:
+        if s[0] in (1, 2):
+            d = vdnn.ConvDesc(s[1], s[2], s[3], s[4], s[9], s[10], s[11], s[5], s[6], s[7], s[8])
+            ws.append([L.vdnn_conv_workspace_bytes(op, 1, C.byref(d)) for op in range(3)])
+        else:
+            ws.append([0, 0, 0])
+    return ws
+
+
+@pytest.mark.parametrize("pool_gb,expect", [(40, (1, 1)), (13.5, (3, 1)), (10.5, (2, 1)), (5, None)])
+def test_dynamic_algo_picks_the_first_policy_that_fits(vdnn, oracle, pool_gb, expect):
+    """VDNN_DYNAMIC_ALGO (network.cu:946-1008): NONE, then CONV, then ALL with the workspace-using algorithms;
+    a model that does not even fit under VDNN_ALL with zero workspace is refused.  Pool sizes are chosen away
+    from the boundaries (peaks 15.4 / 11.2 / 8.9 GB), where peak bytes and a real allocator agree."""
+    specs = [s.astuple() for s in oracle.model_layers(oracle.VGG16_128, 128)]
+    assert oracle.dynamic_choice(specs, pool_gb * 1e9, _perf_workspaces(vdnn, specs)) == expect
+    if expect is None:
+        with pytest.raises(vdnn.VdnnError) as e:
+            vdnn.Network("VGG16_128", "BASELINE", "VDNN_DYNAMIC_ALGO", device=-1, pool_bytes=pool_gb * 1e9)
+        assert e.value.status == -5
+        return
+    net = vdnn.Network("VGG16_128", "BASELINE", "VDNN_DYNAMIC_ALGO", device=-1, pool_bytes=pool_gb * 1e9)   # the given policy is ignored
+    try:
+        assert net.selected() == expect
+        net.step()
+        net.step()
+        ev, summ = oracle.policy_trace(specs, expect[0], ws=_perf_workspaces(vdnn, specs), iterations=2, fix_input_leak=True)
+        assert net.trace() == ev and net.stats()["pool_peak_bytes"] == summ.peak_bytes
+    finally:
+        net.close()
+
+
+def workspace_heavy_net(n=2):
+    """Two 3x3 convolutions on 7x7 maps with many channels: their packed-weight workspaces (8.3 and 4.2 MB)
+    dwarf the activations, so the pool size decides which operations may use them."""
+    return [(2, n, 256, 7, 7, 1, 1, 1, 1, 256, 3, 3), (3, n, 256, 7, 7, 0, 0, 0, 0, 0, 0, 0),
+            (2, n, 256, 7, 7, 1, 1, 1, 1, 128, 3, 3), (3, n, 128, 7, 7, 0, 0, 0, 0, 0, 0, 0),
+            (0, n, 128 * 49, 1, 1, 0, 0, 0, 0, 10, 1, 1), (6, n, 10, 1, 1, 0, 0, 0, 0, 0, 0, 0)]
+
+
+def test_dynamic_algo_per_layer(vdnn, oracle):
+    """Step 5 of the dynamic mode (layer.cu:1091-1147): under VDNN_ALL every convolution operation gets the
+    workspace-using algorithm only where the iteration still fits the pool."""
+    specs = workspace_heavy_net()
+    ws = _perf_workspaces(vdnn, specs)
+    assert ws[0][0] > 8e6 and ws[2][0] > 4e6
+    picks = {}
+    for pool in (3_500_000, 4_496_896, 8_611_840, 16_000_000):
+        assert (oracle.dynamic_choice(specs, pool, ws) is None) == (pool == 3_500_000)
+        try:
+            net = vdnn.Network("CUSTOM_CNN", "VDNN_NONE", "VDNN_DYNAMIC_ALGO", device=-1, pool_bytes=pool, custom_layers=specs)
+        except vdnn.VdnnError as e:
+            picks[pool] = e.status
+            continue
+        try:
+            picks[pool] = (net.selected(), net.layer_algos(0), net.layer_algos(2))
+            net.step()
+            net.step()            # what was chosen does train within the pool
+        finally:
+            net.close()
+    assert picks[3_500_000] == -5                                         # not even VDNN_ALL with zero workspace
+    assert picks[4_496_896] == ((2, 2), (0, 0, 1), (0, 0, 1))             # VDNN_ALL, no room for any workspace
+    assert picks[8_611_840] == ((2, 2), (0, 0, 1), (1, 1, 1))             # room for the second layer's 4.2 MB
+    assert picks[16_000_000] == ((1, 1), (1, 1, 1), (1, 1, 1))            # everything fits without offloading
+
+
 def test_unsupported_modes_are_refused(vdnn):
     with pytest.raises(vdnn.VdnnError):
         vdnn.Network("GOOGLENET", "BASELINE", "VDNN_MEMORY_OPT_ALGO", device=-1)
-    with pytest.raises(vdnn.VdnnError):
-        vdnn.Network("ALEXNET", "BASELINE", "VDNN_DYNAMIC_ALGO", device=-1)
     with pytest.raises(vdnn.VdnnError):
         vdnn.Network("CUSTOM_CNN", "BASELINE", "VDNN_MEMORY_OPT_ALGO", device=-1)
 

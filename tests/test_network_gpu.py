@@ -11,11 +11,14 @@ TOL = 1e-4
 POLICIES = ["BASELINE", "VDNN_NONE", "VDNN_ALL", "VDNN_CONV"]
 
 
-def _run(vdnn, oracle, specs, cnn, policy, algo, batch, lr, steps=2, host_sync=False, init_mode=0, seed0=1000):
+def _run(vdnn, oracle, specs, cnn, policy, algo, batch, lr, steps=2, host_sync=False, init_mode=0, seed0=1000, pool_bytes=4e9,
+         expect_selected=None):
     onet = oracle.Net(specs, lr, init_mode=init_mode)
-    net = vdnn.Network(cnn, policy, algo, batch_size=batch, pool_bytes=4e9, learning_rate=lr, init_mode=init_mode,
+    net = vdnn.Network(cnn, policy, algo, batch_size=batch, pool_bytes=pool_bytes, learning_rate=lr, init_mode=init_mode,
                        capture=True, custom_layers=specs if cnn == "CUSTOM_CNN" else None, host_sync_per_layer=host_sync)
     try:
+        if expect_selected is not None:
+            assert net.selected() == expect_selected
         assert [s.astuple() for s in net.layer_specs()] == [tuple(s) if not hasattr(s, "astuple") else s.astuple() for s in specs]
         rows = specs[-1][1] if not hasattr(specs[-1], "n") else specs[-1].n
         cols = net.output_size // rows
@@ -68,6 +71,16 @@ def test_tanh_and_sigmoid_layers(vdnn, oracle):
     specs[relus[1]] = (SIGMOID,) + tuple(specs[relus[1]][1:])
     assert [s[0] for s in specs].count(TANH) == 1 and [s[0] for s in specs].count(SIGMOID) == 1
     _run(vdnn, oracle, specs, "CUSTOM_CNN", "VDNN_ALL", "VDNN_MEMORY_OPT_ALGO", 4, 0.05)
+
+
+def test_dynamic_algo_trains_with_mixed_algorithms(vdnn, oracle):
+    """VDNN_DYNAMIC_ALGO on a pool that leaves room for the second convolution's workspace only: VDNN_ALL is kept,
+    layer 0 runs its zero-workspace kernels, layer 2 the workspace-using ones, and the step equals the oracle's."""
+    from test_host_logic import workspace_heavy_net
+    specs = workspace_heavy_net()
+    _run(vdnn, oracle, specs, "CUSTOM_CNN", "BASELINE", "VDNN_DYNAMIC_ALGO", 2, 0.01, pool_bytes=8_611_840, expect_selected=(2, 2))
+    # and with room for everything the first candidate (VDNN_NONE, workspace-using algorithms) is taken
+    _run(vdnn, oracle, specs, "CUSTOM_CNN", "BASELINE", "VDNN_DYNAMIC_ALGO", 2, 0.01, pool_bytes=64e6, expect_selected=(1, 1))
 
 
 def test_reference_schedule_mode_gives_same_numbers(vdnn, oracle):

@@ -42,7 +42,7 @@ int vdnnContext::alloc(void** ptr, size_t bytes, int layer, int tag, bool isDyna
     const cnmemStatus_t st = vdnnPoolMallocFor(ptr, bytes, s.data(), dry_run ? 0 : static_cast<int>(s.size()));
     if (st == CNMEM_STATUS_OUT_OF_MEMORY) {
         if (isDynamic) return -1;                       // soft failure (layer.h:119-125)
-        fprintf(stderr, "\n[pool exhausted: %zu bytes for layer %d, tag %d]\n", bytes, layer, tag);
+        if (!quiet) fprintf(stderr, "\n[pool exhausted: %zu bytes for layer %d, tag %d]\n", bytes, layer, tag);
         return VDNN_ERR_OUT_OF_MEMORY;
     }
     if (st != CNMEM_STATUS_SUCCESS) {
@@ -107,6 +107,7 @@ Layer::Layer(vdnn_t _vdnnMode, vdnnAlgoMode_t _vdnnAlgoMode, Layer_t _layerType,
       stream_compute(_stream_compute), stream_memory(_stream_memory), handle(*_handle),
       srcData(NULL), filterData(NULL), biasData(NULL), dstData(NULL), diffData(NULL), gradData(NULL),
       gradFilter(NULL), gradBias(NULL) {
+    opMode[0] = opMode[1] = opMode[2] = VDNN_ALGO_MEMORY_OPT;
     switch (layerType) {
     case FC_GEMM:
         if (!(h_in == 1 && w_in == 1 && r == 1 && s == 1)) { fprintf(stderr, "Invalid dimensions!\n"); return; }
@@ -120,10 +121,9 @@ Layer::Layer(vdnn_t _vdnnMode, vdnnAlgoMode_t _vdnnAlgoMode, Layer_t _layerType,
         c_out = k;
         if (initializeConvolutionFilterAndBias() != 0) return;
         // algorithm choice + workspace query (layer.cu:256-294)
-        const int mode = vdnnAlgoMode == VDNN_PERF_OPT_ALGO ? VDNN_ALGO_PERF_OPT : VDNN_ALGO_MEMORY_OPT;
-        fwdWorkSpaceSize = vdnn_conv_workspace_bytes(VDNN_CONV_FWD, mode, &d);
-        bwdDataWorkSpaceSize = vdnn_conv_workspace_bytes(VDNN_CONV_BWD_DATA, mode, &d);
-        bwdFilterWorkSpaceSize = vdnn_conv_workspace_bytes(VDNN_CONV_BWD_FILTER, mode, &d);
+        const bool perf = vdnnAlgoMode == VDNN_PERF_OPT_ALGO;
+        const bool use[3] = {perf, perf, perf};
+        setOpAlgos(use);
     } break;
     case POOL:
         if (vdnn_pool_out_dims(h_in, w_in, r, s, stride_h, stride_w, &h_out, &w_out) != VDNN_OK) {
@@ -247,11 +247,20 @@ int Layer::backward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, v
     if (handle->profiling) CU(cudaEventRecord(handle->pf_bwd_beg[layerId], *stream_compute));
 #define MARK(ev) CU(cudaEventRecord(handle->ev[layerId], *stream_compute))
 
+void Layer::setOpAlgos(const bool use[3]) {
+    for (int op = 0; op < 3; ++op) opMode[op] = use[op] ? VDNN_ALGO_PERF_OPT : VDNN_ALGO_MEMORY_OPT;
+    if (layerType != CONV && layerType != FC_CONV) return;
+    const vdnn_conv_desc d = convDesc();
+    fwdWorkSpaceSize = vdnn_conv_workspace_bytes(VDNN_CONV_FWD, opMode[0], &d);
+    bwdDataWorkSpaceSize = vdnn_conv_workspace_bytes(VDNN_CONV_BWD_DATA, opMode[1], &d);
+    bwdFilterWorkSpaceSize = vdnn_conv_workspace_bytes(VDNN_CONV_BWD_FILTER, opMode[2], &d);
+}
+
 /* ------------------------------------------------------------------ CONV (layer.cu:539-665) */
 
 int Layer::convolutionForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, void* workSpace, bool isDynamic) {
     void* curWorkSpace = NULL;
-    const int mode = vdnnAlgoMode == VDNN_PERF_OPT_ALGO ? VDNN_ALGO_PERF_OPT : VDNN_ALGO_MEMORY_OPT;
+    const int mode = opMode[0];
     if (workSpace != NULL) curWorkSpace = workSpace;
     else if (fwdWorkSpaceSize > 0) {
         const int a = handle->alloc(&curWorkSpace, fwdWorkSpaceSize, layerId, TAG_WS, isDynamic, {*stream_compute});
@@ -272,7 +281,6 @@ int Layer::convolutionForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, 
 int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, void* _srcDataToPrefetch,
                                unsigned long _prefetch_bytes, void* workSpace, bool isDynamic) {
     void* curWorkSpace = NULL;
-    const int mode = vdnnAlgoMode == VDNN_PERF_OPT_ALGO ? VDNN_ALGO_PERF_OPT : VDNN_ALGO_MEMORY_OPT;
     const float lr = handle->learning_rate * -1.0f;
     const bool staged = gradFilter != NULL;
     BWD_PROLOGUE();
@@ -284,7 +292,7 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
         if (a != 0) return a;
     }
     // data gradient with the weights as they were in forward
-    DEV(vdnn_conv_bwd_data(&d, mode, 1.0f, (const float*)filterData, (const float*)diffData, 0.0f, (float*)gradData,
+    DEV(vdnn_conv_bwd_data(&d, opMode[1], 1.0f, (const float*)filterData, (const float*)diffData, 0.0f, (float*)gradData,
                            curWorkSpace, bwdDataWorkSpaceSize, *stream_compute));
     if (workSpace == NULL && bwdDataWorkSpaceSize > 0) {
         MARK(ev_bwd_done);
@@ -300,7 +308,7 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
         const int a = handle->alloc(&curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, isDynamic, {*stream_compute});
         if (a != 0) return a;
     }
-    DEV(vdnn_conv_bwd_filter(&d, mode, staged ? 1.0f : lr, (const float*)srcData, (const float*)diffData,
+    DEV(vdnn_conv_bwd_filter(&d, opMode[2], staged ? 1.0f : lr, (const float*)srcData, (const float*)diffData,
                              staged ? 0.0f : 1.0f, staged ? gradFilter : (float*)filterData, curWorkSpace,
                              bwdFilterWorkSpaceSize, *stream_compute));
     MARK(ev_bwd_done);

@@ -33,6 +33,7 @@ struct vdnnContext {
     bool capture = false;
     bool profiling = false;
     bool fix_input_leak = true;
+    bool quiet = false;                // trial networks: no message when the pool is exhausted
 
     // streams and per-layer events (index = layer id)
     cudaStream_t stream_compute = nullptr, stream_d2h = nullptr, stream_h2d = nullptr, stream_comm = nullptr;
@@ -174,6 +175,10 @@ public:
     float*  GradFilter()             { return gradFilter; }
     float*  GradBias()               { return gradBias;   }
 
+    /* VDNN_DYNAMIC_ALGO (layer.cu:1091-1147): per operation, the workspace-using algorithm when `use[op]`
+       is set, else the zero-workspace one; op = 0 forward, 1 data gradient, 2 filter gradient. */
+    void    setOpAlgos(const bool use[3]);
+    void    opAlgos(int out[3]) const { out[0] = opMode[0]; out[1] = opMode[1]; out[2] = opMode[2]; }
     void    printDstData();
     void    printFilterData();
 
@@ -192,6 +197,7 @@ private:
     int n_out, c_out, h_out, w_out;
 
     size_t fwdWorkSpaceSize, bwdDataWorkSpaceSize, bwdFilterWorkSpaceSize;
+    int    opMode[3];          // VDNN_ALGO_MEMORY_OPT / VDNN_ALGO_PERF_OPT per operation
 
     cudaStream_t* stream_compute;
     cudaStream_t* stream_memory;

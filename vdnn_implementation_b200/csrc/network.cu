@@ -53,6 +53,90 @@ Network::Network(CNN_t _cnnType, vdnn_t _vdnnType, vdnnAlgoMode_t _algoMode, int
 
 Network::Network(const vdnn_network_config& cfg, bool dry_run) { init(cfg, dry_run); }
 
+Network::Network(const vdnn_network_config& cfg, bool dry_run, const std::vector<unsigned char>& ops) {
+    layerOps = ops;
+    ctx.quiet = true;
+    init(cfg, dry_run);
+}
+
+/* ------------------------------------------------------------------ VDNN_DYNAMIC_ALGO (network.cu:946-1008) */
+
+// The reference finds out whether a (policy, algorithm mode) pair fits by running a training iteration
+// with soft allocation failures and rebuilding the whole network for the next candidate.  What decides is
+// the pool's bookkeeping in host order, so the same question is answered here by replaying two iterations of
+// the candidate against a bookkeeping-only pool of the same capacity: no kernel runs and nothing is allocated.
+bool Network::trainable(const vdnn_network_config& cfg, vdnn_t type, vdnnAlgoMode_t algo,
+                        const std::vector<unsigned char>* ops) {
+    vdnn_network_config c = cfg;
+    c.vdnn_type = type; c.algo_mode = algo; c.device = -1; c.verbose = 0; c.capture = 0;
+    static const std::vector<unsigned char> none;
+    Network trial(c, true, ops ? *ops : none);
+    if (trial.status() != VDNN_OK) return false;
+    trial.context().trace_enabled = false;
+    for (int it = 0; it < 2; ++it)
+        if (trial.forwardPropagation(true) != 0 || trial.backwardPropagation(true) != 0) return false;
+    return true;
+}
+
+int Network::vdnnDynamicAlgo(const vdnn_network_config& cfg) {
+    const bool say = cfg.verbose != 0;
+    if (say) printf("\n1. Test VDNN_ALL and VDNN_MEMORY_OPT_ALGO\n");
+    if (!trainable(cfg, VDNN_ALL, VDNN_MEMORY_OPT_ALGO, NULL)) {
+        fprintf(stderr, "This CNN model cannot be trained\n");
+        return VDNN_ERR_OUT_OF_MEMORY;
+    }
+    static const struct { vdnn_t type; const char* name; } order[3] = {
+        {VDNN_NONE, "VDNN_NONE"}, {VDNN_CONV, "VDNN_CONV"}, {VDNN_ALL, "VDNN_ALL"}};
+    for (int i = 0; i < 3; ++i) {
+        if (say) printf("\n%d. Test %s and VDNN_PERF_OPT_ALGO\n", i + 2, order[i].name);
+        if (trainable(cfg, order[i].type, VDNN_PERF_OPT_ALGO, NULL)) {
+            if (say) printf("%s and VDNN_PERF_OPT_ALGO Passed!\n", order[i].name);
+            vdnnType = order[i].type;
+            algoMode = VDNN_PERF_OPT_ALGO;
+            return VDNN_OK;
+        }
+    }
+    // Per layer and operation under VDNN_ALL (layer.cu:1091-1147 tries each layer's algorithms from the fastest
+    // down until the workspace can be had): starting from zero workspace everywhere, which step 1 showed to
+    // fit, an operation moves to its workspace-using algorithm when the whole iteration still fits with it.
+    if (say) printf("\n5. Dynamic Algorithm with VDNN_ALL\n");
+    vdnn_network_config c = cfg;
+    c.vdnn_type = VDNN_ALL; c.algo_mode = VDNN_MEMORY_OPT_ALGO; c.device = -1; c.verbose = 0; c.capture = 0;
+    std::vector<unsigned char> ops;
+    {
+        Network shape(c, true, ops);
+        if (shape.status() != VDNN_OK) return shape.status();
+        ops.assign(shape.numLayers_(), 0);
+        for (int l = 0; l < shape.numLayers_(); ++l) {
+            const Layer_t t = shape.layerArray()[l]->LayerType();
+            if (t != CONV && t != FC_CONV) ops[l] = 0x80;            // not a convolution: nothing to choose
+        }
+    }
+    for (size_t l = 0; l < ops.size(); ++l) {
+        if (ops[l] & 0x80) { ops[l] = 0; continue; }
+        for (int op = 0; op < 3; ++op) {
+            ops[l] |= static_cast<unsigned char>(1u << op);
+            if (!trainable(cfg, VDNN_ALL, VDNN_MEMORY_OPT_ALGO, &ops)) ops[l] &= static_cast<unsigned char>(~(1u << op));
+        }
+    }
+    vdnnType = VDNN_ALL;
+    algoMode = VDNN_MEMORY_OPT_ALGO;
+    dynamicPerLayer = true;
+    layerOps = ops;
+    return VDNN_OK;
+}
+
+void Network::selected(int* vdnn_type, int* algo) const {
+    if (vdnn_type) *vdnn_type = vdnnType;
+    if (algo) *algo = dynamicPerLayer ? VDNN_DYNAMIC_ALGO : algoMode;
+}
+
+int Network::layerAlgos(int layerId, int out3[3]) const {
+    if (layerId < 0 || layerId >= numLayers || !out3) return VDNN_ERR_BAD_ARG;
+    layer[layerId]->opAlgos(out3);
+    return VDNN_OK;
+}
+
 void Network::init(const vdnn_network_config& cfg, bool dry_run) {
     cnnType = static_cast<CNN_t>(cfg.cnn_type);
     vdnnType = static_cast<vdnn_t>(cfg.vdnn_type);
@@ -80,15 +164,16 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
     ctx.capture = cfg.capture != 0;
     ctx.fix_input_leak = cfg.fix_input_leak != 0;
 
-    if (algoMode == VDNN_DYNAMIC_ALGO) {
-        fprintf(stderr, "VDNN_DYNAMIC_ALGO is not implemented by this build; use VDNN_MEMORY_OPT_ALGO or VDNN_PERF_OPT_ALGO\n");
-        state = VDNN_ERR_UNSUPPORTED;
-        return;
-    }
     if (vdnnPoolIsInitialized()) {
         fprintf(stderr, "a Network already owns the device pool of this process\n");
         state = VDNN_ERR_STATE;
         return;
+    }
+
+    dynamicPerLayer = false;
+    if (algoMode == VDNN_DYNAMIC_ALGO) {          // the given policy is ignored, as network.cu:60-78 does
+        const int st = vdnnDynamicAlgo(cfg);
+        if (st != VDNN_OK) { state = st; return; }
     }
 
     const size_t pool = cfg.pool_bytes ? cfg.pool_bytes : static_cast<size_t>(24e9);
@@ -152,6 +237,12 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
 
     setLayers(cnnType);
     if (state != VDNN_OK) return;
+    for (size_t l = 0; l < layerOps.size() && static_cast<int>(l) < numLayers; ++l) {
+        const Layer_t t = layer[l]->LayerType();
+        if (t != CONV && t != FC_CONV) continue;
+        const bool use[3] = {(layerOps[l] & 1) != 0, (layerOps[l] & 2) != 0, (layerOps[l] & 4) != 0};
+        layer[l]->setOpAlgos(use);
+    }
     setVdnnType(vdnnType);
     if (state != VDNN_OK) return;
 

@@ -13,6 +13,8 @@ class Network {
 public:
     Network(CNN_t _cnnType, vdnn_t _vdnnType, vdnnAlgoMode_t _algoMode, int _batchSize = DEFAULT_BATCH_SIZE);
     explicit Network(const vdnn_network_config& cfg, bool dry_run = false);
+    // trial networks of the dynamic mode: per layer, bit `op` set = workspace-using algorithm for that operation
+    Network(const vdnn_network_config& cfg, bool dry_run, const std::vector<unsigned char>& layerOps);
     ~Network();
 
     /* Setup */
@@ -58,6 +60,10 @@ public:
     int             readTensor(int layerId, int kind, float* dst_h, size_t count);
     int             writeTensor(int layerId, int kind, const float* src_h, size_t count);
     int             getStats(vdnn_network_stats* out);
+    /* VDNN_DYNAMIC_ALGO (network.cu:946-1008): what the constructor settled on.  algo is VDNN_DYNAMIC_ALGO when
+       the algorithms were chosen per layer and operation (see layerAlgos), else the mode all layers share. */
+    void            selected(int* vdnn_type, int* algo) const;
+    int             layerAlgos(int layerId, int out3[3]) const;
     int             setProfiling(bool enabled);
     int             setOffloadOrder(bool forwardOrder);
     int             timeline(float* out);
@@ -66,6 +72,9 @@ public:
 
 private:
     void            init(const vdnn_network_config& cfg, bool dry_run);
+    int             vdnnDynamicAlgo(const vdnn_network_config& cfg);
+    static bool     trainable(const vdnn_network_config& cfg, vdnn_t type, vdnnAlgoMode_t algo,
+                              const std::vector<unsigned char>* layerOps);
     void            addLayer(Layer_t type, vdnnAlgoMode_t algo, int n, int c, int h, int w, int pad, int stride, int k, int r);
     void            convRelu(int pad, int stride, int k, int r, bool forceMemOpt = false);
     void            fcRelu(int k);
@@ -76,6 +85,8 @@ private:
     CNN_t               cnnType;
     vdnn_t              vdnnType;
     vdnnAlgoMode_t      algoMode;
+    bool                dynamicPerLayer;
+    std::vector<unsigned char> layerOps;       // set by the dynamic mode (empty: every layer follows algoMode)
     vdnnContext         ctx;
     vdnnHandle_t        handle;
     cudaStream_t        stream_compute;

@@ -86,6 +86,9 @@ int vdnn_network_trace_reset(vdnn_network* net) { NET(net); net->impl->context()
 int vdnn_network_get_stats(vdnn_network* net, vdnn_network_stats* out) { NET(net); return net->impl->getStats(out); }
 int vdnn_network_set_profiling(vdnn_network* net, int enabled) { NET(net); return net->impl->setProfiling(enabled != 0); }
 
+int vdnn_network_selected(vdnn_network* net, int* vdnn_type, int* algo_mode) { NET(net); net->impl->selected(vdnn_type, algo_mode); return VDNN_OK; }
+int vdnn_network_layer_algos(vdnn_network* net, int layer, int* out3) { NET(net); return net->impl->layerAlgos(layer, out3); }
+
 int vdnn_network_set_offload_order(vdnn_network* net, int forward_order) { NET(net); return net->impl->setOffloadOrder(forward_order != 0); }
 
 int vdnn_network_timeline(vdnn_network* net, float* out) { NET(net); return net->impl->timeline(out); }

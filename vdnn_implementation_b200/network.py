@@ -136,6 +136,18 @@ class Network:
     def set_profiling(self, enabled=True):
         check(lib().vdnn_network_set_profiling(self._h, int(enabled)), "set_profiling")
 
+    def selected(self):
+        """(vdnn_type, algo_mode) the constructor settled on; algo_mode 2 (VDNN_DYNAMIC_ALGO) = chosen per layer."""
+        t, a = C.c_int(), C.c_int()
+        check(lib().vdnn_network_selected(self._h, C.byref(t), C.byref(a)), "selected")
+        return t.value, a.value
+
+    def layer_algos(self, layer):
+        """VDNN_ALGO_MEMORY_OPT (0) / VDNN_ALGO_PERF_OPT (1) for forward, data gradient, filter gradient."""
+        out = (C.c_int * 3)()
+        check(lib().vdnn_network_layer_algos(self._h, layer, out), "layer_algos")
+        return tuple(out)
+
     def set_offload_order(self, forward_order=False):
         """False (default): offload copies reach the copy engine in the order backward needs them;
         True: in layer order, as the reference enqueues them."""
