@@ -75,6 +75,10 @@ typedef void (*vdnnPoolResolver_t)(void* user, unsigned long long token);
 cnmemStatus_t vdnnPoolSetResolver(vdnnPoolResolver_t resolver, void* user);
 cnmemStatus_t vdnnPoolFreeHeld(void* ptr, const cudaStream_t* streams, int numStreams, unsigned long long token);
 cnmemStatus_t vdnnPoolResolve(unsigned long long token, cudaStream_t stream);
+/* packed != 0: allocations take the tightest-fitting free block from its start, whatever events are pending on it
+ * (the streams still wait for them): the placement of plain cnmemMalloc, and of the bookkeeping-only pool, so a
+ * schedule that was replayed there fits here too.  Default 0: placement by pending events as described above. */
+cnmemStatus_t vdnnPoolSetPacked(int packed);
 cnmemStatus_t vdnnPoolHighWater(size_t* peakBytes, int reset);
 /* Makes the k-th allocation from now fail with CNMEM_STATUS_OUT_OF_MEMORY (k >= 1; 0 disarms).
  * Host-side fault injection for the soft-OOM return path (layer.h:119-125). */

@@ -267,8 +267,8 @@ def test_dynamic_algo_per_layer(vdnn, oracle):
         finally:
             net.close()
     assert picks[3_500_000] == -5                                         # not even VDNN_ALL with zero workspace
-    assert picks[4_496_896] == ((2, 2), (0, 0, 1), (0, 0, 1))             # VDNN_ALL, no room for any workspace
-    assert picks[8_611_840] == ((2, 2), (0, 0, 1), (1, 1, 1))             # room for the second layer's 4.2 MB
+    assert picks[4_496_896] == ((2, 2), (0, 0, 0), (0, 0, 0))             # VDNN_ALL, no room for any workspace
+    assert picks[8_611_840] == ((2, 2), (0, 0, 1), (1, 1, 1))             # room for the second layer's 4.2 MB (and 0.3 MB of dy tiles)
     assert picks[16_000_000] == ((1, 1), (1, 1, 1), (1, 1, 1))            # everything fits without offloading
 
 

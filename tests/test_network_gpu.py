@@ -189,8 +189,8 @@ def test_offload_bytes_and_overlap_are_reported(vdnn, oracle):
         net.close()
 
 
-def _alexnet_steps(vdnn, pool_bytes, forward_order, steps=2, batch=32):
-    net = vdnn.Network("ALEXNET", "VDNN_ALL", "VDNN_PERF_OPT_ALGO", batch_size=batch, pool_bytes=pool_bytes, learning_rate=1e-4)
+def _steps(vdnn, pool_bytes, forward_order, model="ALEXNET", batch=32, layers=(0, 6, 13, 17), steps=2):
+    net = vdnn.Network(model, "VDNN_ALL", "VDNN_PERF_OPT_ALGO", batch_size=batch, pool_bytes=pool_bytes, learning_rate=1e-4)
     try:
         net.set_offload_order(forward_order)
         forced = 0
@@ -200,7 +200,7 @@ def _alexnet_steps(vdnn, pool_bytes, forward_order, steps=2, batch=32):
             forced += net.stats()["forced_offloads"]
             net.backwardPropagation()
         net.synchronize()
-        return ([net.weights(l) for l in (0, 6, 13, 17)], [net.bias(l) for l in (0, 17)], net.loss(), net.trace(),
+        return ([net.weights(l) for l in layers], [net.bias(l) for l in (layers[0], layers[-1])], net.loss(), net.trace(),
                 net.stats()["pool_peak_bytes"], forced)
     finally:
         net.close()
@@ -210,8 +210,8 @@ def test_offload_order_is_not_observable(vdnn):
     """Offload copies enqueued in the order backward needs them (the default) or in layer order (the
     reference's): same host-side trace (allocations, releases, offloads, prefetches with the pool's byte
     count after each), same peak, same step to rounding."""
-    by_need = _alexnet_steps(vdnn, 6e9, False)
-    in_order = _alexnet_steps(vdnn, 6e9, True)
+    by_need = _steps(vdnn, 6e9, False)
+    in_order = _steps(vdnn, 6e9, True)
     assert by_need[3] == in_order[3] and by_need[4] == in_order[4]
     assert by_need[5] == 0 and in_order[5] == 0
     assert abs(by_need[2][0] - in_order[2][0]) < 1e-6 and abs(by_need[2][1] - in_order[2][1]) < 1e-5 * abs(in_order[2][1])
@@ -223,22 +223,26 @@ def test_offload_order_is_not_observable(vdnn):
 
 
 def test_held_blocks_are_given_back_under_pool_pressure(vdnn):
-    """A pool barely larger than the policy's peak: forward can only go on by reusing the bytes of tensors whose
-    offload copy is still held back, so the pool has those copies enqueued early (oldest first).  Same step as in a
-    roomy pool."""
-    dry = vdnn.Network("ALEXNET", "VDNN_ALL", "VDNN_PERF_OPT_ALGO", batch_size=32, device=-1, pool_bytes=6e9)
+    """VGG16 at batch 32 in a pool of 1.45 x the policy's peak: enough room for placement by pending events, but less
+    than forward needs if nothing is reused, so forward can only go on by taking the bytes of tensors whose offload
+    copy is still held back, and the pool has those copies enqueued early (oldest first).  Same step as in a roomy
+    pool, and as in a pool so tight (1.15 x peak) that the driver packs it and sends the copies in layer order."""
+    vgg = dict(model="VGG16_64", batch=32, layers=(0, 5, 31, 35))
+    dry = vdnn.Network("VGG16_64", "VDNN_ALL", "VDNN_PERF_OPT_ALGO", batch_size=32, device=-1, pool_bytes=20e9)
     try:
         dry.step()
         dry.step()
         peak = dry.stats()["pool_peak_bytes"]
     finally:
         dry.close()
-    tight = _alexnet_steps(vdnn, int(peak * 1.15), False)
-    roomy = _alexnet_steps(vdnn, 6e9, False)
-    assert tight[5] > 0 and roomy[5] == 0
-    assert tight[3] == roomy[3] and tight[4] == roomy[4] == peak
-    for a, b in zip(tight[0], roomy[0]):
-        assert rel_err(a, b) < 1e-5
-    for a, b in zip(tight[1], roomy[1]):
-        assert rel_err(a, b) < 1e-4
+    pressed = _steps(vdnn, int(peak * 1.45), False, **vgg)
+    roomy = _steps(vdnn, 12e9, False, **vgg)
+    packed = _steps(vdnn, int(peak * 1.15), False, **vgg)
+    assert pressed[5] > 0 and roomy[5] == 0 and packed[5] == 0
+    for other in (pressed, packed):
+        assert other[3] == roomy[3] and other[4] == roomy[4] == peak
+        for a, b in zip(other[0], roomy[0]):
+            assert rel_err(a, b) < 1e-5
+        for a, b in zip(other[1], roomy[1]):
+            assert rel_err(a, b) < 1e-4
     assert vdnn.ops.engine_status() == 0

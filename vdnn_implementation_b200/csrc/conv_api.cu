@@ -124,6 +124,13 @@ size_t packed_weight_bytes(const vdnn_conv_desc* d, int op) {
     return tc::bulk_bytes(op == VDNN_CONV_FWD ? d->k : d->c, red);
 }
 
+// PERF_OPT scratch for the dy operand of the filter gradient (N = K filters as tile columns, reduction over the
+// N*P*Q pixels): the same tile images.  Only where dy fills at least 128 columns: with fewer, the columns are the
+// small part of the producers' work and the images (twice the bytes of dy) would not pay for themselves.
+size_t packed_dy_bytes(const vdnn_conv_desc* d, int P, int Q) {
+    return d->k >= 128 ? tc::bulk_bytes(d->k, d->n * P * Q) : 0;
+}
+
 int stream_blocks(size_t n) {
     size_t want = ceil_div<size_t>(n, 256);
     const size_t cap = static_cast<size_t>(sm_count()) * 8;
@@ -264,6 +271,7 @@ size_t vdnn_conv_workspace_bytes(int op, int algo_mode, const vdnn_conv_desc* d)
     const SplitPlan plan = plan_split(M, N, K);
     size_t bytes = plan.splits > 1 ? static_cast<size_t>(plan.splits) * out * sizeof(float) : 0;
     if (op == VDNN_CONV_FWD || op == VDNN_CONV_BWD_DATA) bytes += packed_weight_bytes(d, op);
+    else bytes += packed_dy_bytes(d, P, Q);
     return bytes;
 }
 
@@ -379,6 +387,17 @@ int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, co
     Epilogue e{};
     e.out = dw; e.bias = nullptr; e.alpha = alpha; e.beta = beta;
     e.row_div = FastDiv(1u << 30); e.row_hi = 0; e.row_lo = 1; e.col_stride = crs;
+    if (algo_mode == VDNN_ALGO_PERF_OPT) {
+        // workspace variant: dy, which every row tile of the gathered input needs again, is split into tf32 halves and
+        // laid out as tile images once; the kernel's producers then gather x only
+        const size_t pack = packed_dy_bytes(d, P, Q);
+        if (pack && (!workspace || workspace_bytes < pack)) return VDNN_ERR_WORKSPACE;
+        char* tiles = (pack && g_engine != VDNN_ENGINE_FFMA && (reinterpret_cast<uintptr_t>(workspace) & 127u) == 0)
+                          ? static_cast<char*>(workspace) : nullptr;
+        return contract<XGatherFiltRows, SplitDense, true, true>(A, B, e, crs, d->k, d->n * pq, static_cast<size_t>(d->k) * crs, 0,
+                                                                 algo_mode, static_cast<char*>(workspace) + pack,
+                                                                 workspace_bytes - pack, as_stream(stream), tiles);
+    }
     return contract<XGatherFiltRows, SplitDense, true, true>(A, B, e, crs, d->k, d->n * pq, static_cast<size_t>(d->k) * crs, 0,
                                                              algo_mode, workspace, workspace_bytes, as_stream(stream));
 }

@@ -336,7 +336,8 @@ inline bool supported(int M, int N, int K) { return M >= 1 && N >= 1 && K >= 1; 
 
 // Writes the shared-memory images of all B tiles: image (nt, kb) = [hi tile | lo tile], each BN rows of 128 bytes,
 // 16-byte chunks swizzled as the kernel's own stash() does, zero where n >= N or k >= K.
-template <class OpB, int BN>
+// BKC: the operand is contiguous along k (a run of 4 k is one 16-byte load where aligned).
+template <class OpB, int BN, bool BKC>
 __global__ void __launch_bounds__(256) pack_b_tiles_kernel(const OpB opb, int N, int K, int n_tiles, int kblocks, char* __restrict__ out) {
     typedef Config<BN> Cfg;
     const size_t total = static_cast<size_t>(n_tiles) * kblocks * BN * 8;          // one thread per 16-byte chunk
@@ -350,8 +351,13 @@ __global__ void __launch_bounds__(256) pack_b_tiles_kernel(const OpB opb, int N,
         const int kk = kb * BK + chunk * 4;
         float4 h, l;
         float v[4];
+        if constexpr (BKC) {
+            if (kk < K) opb.load4(r, opb.cols4(kk, K), kk, v);
+            else v[0] = v[1] = v[2] = v[3] = 0.0f;
+        } else {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) v[e] = (kk + e < K) ? opb.load(r, opb.col(kk + e)) : 0.0f;
+            for (int e = 0; e < 4; ++e) v[e] = (kk + e < K) ? opb.load(r, opb.col(kk + e)) : 0.0f;
+        }
         split_tf32(v[0], h.x, l.x); split_tf32(v[1], h.y, l.y); split_tf32(v[2], h.z, l.z); split_tf32(v[3], h.w, l.w);
         char* img = out + tile * (2 * Cfg::B_TILE_BYTES);
         *reinterpret_cast<float4*>(img + swz(row, chunk)) = h;
@@ -388,7 +394,7 @@ int launch_bn(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int
         size_t blocks = ceil_div<size_t>(chunks, 256);
         const size_t cap = static_cast<size_t>(sm_count()) * 8;
         if (blocks > cap) blocks = cap;
-        pack_b_tiles_kernel<OpB, BN><<<static_cast<int>(blocks), 256, 0, stream>>>(b, N, K, static_cast<int>(grid.y), kblocks, b_tiles);
+        pack_b_tiles_kernel<OpB, BN, BKC><<<static_cast<int>(blocks), 256, 0, stream>>>(b, N, K, static_cast<int>(grid.y), kblocks, b_tiles);
         VDNN_LAUNCHED();
     }
     kern<<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(a, b, epi, M, N, K, k_chunk, b_tiles, kblocks);

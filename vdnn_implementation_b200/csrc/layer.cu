@@ -3,6 +3,8 @@
 // through the C ABI, and device memory is ordered with events instead of host synchronisation.
 #include "layer.h"
 
+#include <algorithm>
+
 #include <math.h>
 #include <string.h>
 
@@ -457,6 +459,17 @@ int Layer::offloadSrcData(bool* _offloaded, DATATYPE** _offloadedSrcData_h) {
     return handle->submitOffload(p);
 }
 
+cudaEvent_t vdnnContext::chunkEvent(int layer, size_t piece) {
+    if (ev_offload_chunk.size() <= static_cast<size_t>(layer)) ev_offload_chunk.resize(layer + 1);
+    std::vector<cudaEvent_t>& v = ev_offload_chunk[layer];
+    while (v.size() <= piece) {
+        cudaEvent_t e = nullptr;
+        if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        v.push_back(e);
+    }
+    return v[piece];
+}
+
 int vdnnContext::submitOffload(const PendingOffload& p) {
     vdnnContext* handle = this;
     cudaStream_t lane = stream_d2h;
@@ -466,7 +479,13 @@ int vdnnContext::submitOffload(const PendingOffload& p) {
         CU(cudaEventRecord(pf_off_beg[p.layer], lane));
         ready = NULL;
     }
-    DEV(vdnn_offload(p.host, p.dev, p.bytes, ready, NULL, lane));
+    for (size_t off = 0, piece = 0; off < p.bytes; off += copy_chunk_bytes, ++piece) {
+        const size_t len = std::min(copy_chunk_bytes, p.bytes - off);
+        cudaEvent_t done = chunkEvent(p.layer, piece);
+        if (!done) return VDNN_ERR_CUDA;
+        DEV(vdnn_offload(static_cast<char*>(p.host) + off, static_cast<const char*>(p.dev) + off, len,
+                         off == 0 ? ready : NULL, done, lane));
+    }
     if (profiling) CU(cudaEventRecord(pf_off_end[p.layer], lane));
     CU(cudaEventRecord(ev_offload_done[p.layer], lane));
     if (vdnnPoolResolve(static_cast<unsigned long long>(p.layer) + 1, lane) != CNMEM_STATUS_SUCCESS) return VDNN_ERR_STATE;
@@ -501,13 +520,20 @@ int Layer::prefetchPreviousSrcData(int _layer_id_to_prefetch, DATATYPE* _prefetc
     handle->record(3, _layer_id_to_prefetch, TAG_SRC, static_cast<int64_t>(_prefetch_bytes));
     handle->prefetch_bytes += static_cast<int64_t>(_prefetch_bytes);
     if (handle->dry_run) return 0;
-    cudaEvent_t ready = handle->ev_offload_done[_layer_id_to_prefetch];
-    if (handle->profiling) {
-        CU(cudaStreamWaitEvent(handle->stream_h2d, ready, 0));
-        CU(cudaEventRecord(handle->pf_pre_beg[_layer_id_to_prefetch], handle->stream_h2d));
-        ready = NULL;
+    // piece by piece behind the pieces of the offload (the same split: submitOffload)
+    const size_t chunk = handle->copy_chunk_bytes;
+    for (size_t off = 0, piece = 0; off < _prefetch_bytes; off += chunk, ++piece) {
+        const size_t len = std::min(chunk, static_cast<size_t>(_prefetch_bytes) - off);
+        cudaEvent_t ready = handle->chunkEvent(_layer_id_to_prefetch, piece);
+        if (!ready) return VDNN_ERR_CUDA;
+        if (off == 0 && handle->profiling) {
+            CU(cudaStreamWaitEvent(handle->stream_h2d, ready, 0));
+            CU(cudaEventRecord(handle->pf_pre_beg[_layer_id_to_prefetch], handle->stream_h2d));
+            ready = NULL;
+        }
+        DEV(vdnn_prefetch(static_cast<char*>(_srcDataToPrefetch) + off, reinterpret_cast<const char*>(_prefetchedSrcData_h) + off,
+                          len, ready, NULL, handle->stream_h2d));
     }
-    DEV(vdnn_prefetch(_srcDataToPrefetch, _prefetchedSrcData_h, _prefetch_bytes, ready, NULL, handle->stream_h2d));
     if (handle->profiling) CU(cudaEventRecord(handle->pf_pre_end[_layer_id_to_prefetch], handle->stream_h2d));
     CU(cudaEventRecord(handle->ev_prefetch_done[_layer_id_to_prefetch], handle->stream_h2d));
     return 0;

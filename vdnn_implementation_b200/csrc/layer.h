@@ -61,6 +61,11 @@ struct vdnnContext {
     bool defer_offloads = false;
     std::vector<PendingOffload> pending_offloads;
     int64_t eager_offload_budget = 0, eager_offload_used = 0, forced_offloads = 0;
+    // Copies go out in pieces of this many bytes with an event after each, so that the prefetch of a tensor
+    // can start behind the first piece of its offload instead of behind the whole tensor.
+    size_t copy_chunk_bytes = static_cast<size_t>(256) << 20;
+    std::vector<std::vector<cudaEvent_t>> ev_offload_chunk;      // [layer][piece], created on demand
+    cudaEvent_t chunkEvent(int layer, size_t piece);
     bool offloadPending(int layer) const {
         for (const PendingOffload& p : pending_offloads) if (p.layer == layer) return true;
         return false;

@@ -66,7 +66,7 @@ Network::Network(const vdnn_network_config& cfg, bool dry_run, const std::vector
 // the pool's bookkeeping in host order, so the same question is answered here by replaying two iterations of
 // the candidate against a bookkeeping-only pool of the same capacity: no kernel runs and nothing is allocated.
 bool Network::trainable(const vdnn_network_config& cfg, vdnn_t type, vdnnAlgoMode_t algo,
-                        const std::vector<unsigned char>* ops) {
+                        const std::vector<unsigned char>* ops, size_t* peak) {
     vdnn_network_config c = cfg;
     c.vdnn_type = type; c.algo_mode = algo; c.device = -1; c.verbose = 0; c.capture = 0;
     static const std::vector<unsigned char> none;
@@ -75,6 +75,7 @@ bool Network::trainable(const vdnn_network_config& cfg, vdnn_t type, vdnnAlgoMod
     trial.context().trace_enabled = false;
     for (int it = 0; it < 2; ++it)
         if (trial.forwardPropagation(true) != 0 || trial.backwardPropagation(true) != 0) return false;
+    if (peak) vdnnPoolHighWater(peak, 0);
     return true;
 }
 
@@ -177,6 +178,16 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
     }
 
     const size_t pool = cfg.pool_bytes ? cfg.pool_bytes : static_cast<size_t>(24e9);
+    // How much room is there?  Placement by pending events, and offload copies held back until the end of
+    // forward, buy overlap with bytes: they need a pool well above the schedule's peak.  The peak comes from a
+    // replay on a bookkeeping-only pool; below 1.4 x peak (or when the replay does not fit) the pool is packed
+    // tightest-fit and the copies go out in layer order, which is the placement the replay was made with.
+    bool packed = false;
+    if (!dry_run && vdnnType != BASELINE) {
+        size_t peak = 0;
+        const std::vector<unsigned char>* ops = layerOps.empty() ? NULL : &layerOps;
+        packed = !trainable(cfg, vdnnType, algoMode, ops, &peak) || static_cast<double>(pool) < 1.4 * static_cast<double>(peak);
+    }
     if (dry_run) {
         if (vdnnPoolInitVirtual(pool) != CNMEM_STATUS_SUCCESS) { state = VDNN_ERR_OUT_OF_MEMORY; return; }
     } else {
@@ -227,7 +238,8 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
         // Offload copies go out in the order backward needs them unless the reference's per-layer
         // synchronisation is asked for (then each copy is enqueued, and waited for, in its own layer).
         const char* order = getenv("VDNN_OFFLOAD_ORDER");
-        ctx.defer_offloads = !ctx.host_sync_per_layer && !(order && strcmp(order, "forward") == 0);
+        ctx.defer_offloads = !packed && !ctx.host_sync_per_layer && !(order && strcmp(order, "forward") == 0);
+        vdnnPoolSetPacked(packed ? 1 : 0);
         if (const char* eager = getenv("VDNN_EAGER_OFFLOAD_BYTES")) ctx.eager_offload_budget = strtoll(eager, NULL, 10);
         vdnnPoolSetResolver([](void* user, unsigned long long token) {
             static_cast<vdnnContext*>(user)->flushOffloads(static_cast<int>(token) - 1);
@@ -278,6 +290,7 @@ Network::~Network() {
     drop(ctx.ev_weights_ready); drop(ctx.pf_fwd_beg); drop(ctx.pf_fwd_end); drop(ctx.pf_bwd_beg); drop(ctx.pf_bwd_end);
     drop(ctx.pf_off_beg); drop(ctx.pf_off_end); drop(ctx.pf_pre_beg); drop(ctx.pf_pre_end);
     if (ctx.ev_input_ready) cudaEventDestroy(ctx.ev_input_ready);
+    for (auto& v : ctx.ev_offload_chunk) drop(v);
     if (ctx.pf_step_beg) cudaEventDestroy(ctx.pf_step_beg);
     if (ctx.pf_step_end) cudaEventDestroy(ctx.pf_step_end);
     if (ev_loss) cudaEventDestroy(ev_loss);

@@ -73,8 +73,9 @@ public:
 private:
     void            init(const vdnn_network_config& cfg, bool dry_run);
     int             vdnnDynamicAlgo(const vdnn_network_config& cfg);
+    // peak: the replay's pool high-water mark (bytes), when asked for
     static bool     trainable(const vdnn_network_config& cfg, vdnn_t type, vdnnAlgoMode_t algo,
-                              const std::vector<unsigned char>* layerOps);
+                              const std::vector<unsigned char>* layerOps, size_t* peak = NULL);
     void            addLayer(Layer_t type, vdnnAlgoMode_t algo, int n, int c, int h, int w, int pad, int stride, int k, int r);
     void            convRelu(int pad, int stride, int k, int r, bool forceMemOpt = false);
     void            fcRelu(int k);

@@ -33,6 +33,7 @@ struct Pool {
     vdnnPoolResolver_t resolver = nullptr;
     void* resolver_user = nullptr;
     int fail_countdown = 0;
+    bool packed = false;                // tightest fit only (vdnnPoolSetPacked)
     unsigned long long next_seq = 1;
     std::vector<cudaEvent_t> spare_events;   // recycled fence events
 };
@@ -50,9 +51,9 @@ bool is_consumer(cudaStream_t s, const cudaStream_t* consumers, int n) {
     return false;
 }
 
-unsigned long long range_readiness_locked(size_t begin, size_t end, const cudaStream_t* consumers, int n) {
+unsigned long long range_readiness_locked(size_t begin, size_t end, const cudaStream_t* consumers, int n, bool events = true) {
     unsigned long long youngest = 0;
-    for (const Fence& f : g_pool.fences)
+    if (events) for (const Fence& f : g_pool.fences)
         if (f.begin < end && begin < f.end && f.seq > youngest && !is_consumer(f.stream, consumers, n)) youngest = f.seq;
     for (const Hold& h : g_pool.holds)
         if (h.begin < end && begin < h.end && kHeldRank + h.token > youngest) youngest = kHeldRank + h.token;
@@ -90,13 +91,14 @@ cnmemStatus_t alloc_locked(void** ptr, size_t size, size_t* off_out, size_t* len
     unsigned long long best_ready = 0;
     size_t best_at = 0;
     const bool rank = (num_consumers > 0 && !g_pool.fences.empty()) || !g_pool.holds.empty();
-    // A candidate is a start offset inside a free block: the block's own start, or -- while at least a
-    // quarter of the pool stays free, because cutting a block in the middle fragments it -- the edge of a
-    // pending event's (or hold's) byte range inside it: after a long-lived copy has been queued on the first
-    // bytes of a large coalesced block, the bytes behind it are still usable at once.
-    const bool roomy = g_pool.used + need <= g_pool.capacity && (g_pool.capacity - g_pool.used - need) >= g_pool.capacity / 4;
+    // A candidate is a start offset inside a free block: the block's own start, or the edge of a pending
+    // event's (or hold's) byte range inside it: after a long-lived copy has been queued on the first bytes of
+    // a large coalesced block, the bytes behind it are still usable at once.  Both refinements -- ranking by
+    // pending events and cutting a block in the middle -- trade packing for waiting time; a pool set to
+    // "packed" (vdnnPoolSetPacked) uses neither and places exactly like the bookkeeping-only pool.
+    const bool roomy = !g_pool.packed;
     auto consider = [&](std::map<size_t, Block>::iterator it, size_t at) {
-        const unsigned long long ready = rank ? range_readiness_locked(at, at + need, consumers, num_consumers) : 0;
+        const unsigned long long ready = rank ? range_readiness_locked(at, at + need, consumers, num_consumers, roomy) : 0;
         const bool better = best == g_pool.blocks.end() || ready < best_ready ||
             (ready == best_ready && ((at == it->first) > (best_at == best->first) ||
                                      ((at == it->first) == (best_at == best->first) && it->second.size < best->second.size)));
@@ -219,6 +221,7 @@ cnmemStatus_t cnmemFinalize(void) {
     g_pool.fences.clear();
     g_pool.holds.clear();
     g_pool.resolver = nullptr;
+    g_pool.packed = false;
     g_pool.capacity = g_pool.used = 0;
     g_pool.ready = false;
     return e == cudaSuccess ? CNMEM_STATUS_SUCCESS : CNMEM_STATUS_CUDA_ERROR;
@@ -309,6 +312,12 @@ cnmemStatus_t vdnnPoolMallocFor(void** ptr, size_t size, const cudaStream_t* str
                                         len, off, (void*)streams[s], f.seq, (void*)f.stream, f.begin, f.end, g_pool.fences.size());
                 if (cudaStreamWaitEvent(streams[s], f.event, 0) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
             }
+    return CNMEM_STATUS_SUCCESS;
+}
+
+cnmemStatus_t vdnnPoolSetPacked(int packed) {
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
+    g_pool.packed = packed != 0;
     return CNMEM_STATUS_SUCCESS;
 }
 
