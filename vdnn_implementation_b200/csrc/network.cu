@@ -172,6 +172,7 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
     }
 
     dynamicPerLayer = false;
+    packedPool = false;
     if (algoMode == VDNN_DYNAMIC_ALGO) {          // the given policy is ignored, as network.cu:60-78 does
         const int st = vdnnDynamicAlgo(cfg);
         if (st != VDNN_OK) { state = st; return; }
@@ -240,6 +241,7 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
         const char* order = getenv("VDNN_OFFLOAD_ORDER");
         ctx.defer_offloads = !packed && !ctx.host_sync_per_layer && !(order && strcmp(order, "forward") == 0);
         vdnnPoolSetPacked(packed ? 1 : 0);
+        packedPool = packed;
         if (const char* eager = getenv("VDNN_EAGER_OFFLOAD_BYTES")) ctx.eager_offload_budget = strtoll(eager, NULL, 10);
         vdnnPoolSetResolver([](void* user, unsigned long long token) {
             static_cast<vdnnContext*>(user)->flushOffloads(static_cast<int>(token) - 1);
@@ -796,7 +798,7 @@ int Network::writeTensor(int l, int kind, const float* src_h, size_t count) {
 
 int Network::setOffloadOrder(bool forwardOrder) {
     if (state != VDNN_OK) return state;
-    ctx.defer_offloads = !forwardOrder && !ctx.host_sync_per_layer && !ctx.dry_run;
+    ctx.defer_offloads = !forwardOrder && !ctx.host_sync_per_layer && !ctx.dry_run && !packedPool;
     return VDNN_OK;
 }
 

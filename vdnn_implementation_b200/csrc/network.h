@@ -87,6 +87,7 @@ private:
     vdnn_t              vdnnType;
     vdnnAlgoMode_t      algoMode;
     bool                dynamicPerLayer;
+    bool                packedPool;            // pool below 1.4 x the schedule's peak: tightest fit, copies in layer order
     std::vector<unsigned char> layerOps;       // set by the dynamic mode (empty: every layer follows algoMode)
     vdnnContext         ctx;
     vdnnHandle_t        handle;
