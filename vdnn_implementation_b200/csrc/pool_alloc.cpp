@@ -303,15 +303,10 @@ cnmemStatus_t vdnnPoolMallocFor(void** ptr, size_t size, const cudaStream_t* str
         if (st != CNMEM_STATUS_SUCCESS) return st;
     }
     if (g_pool.is_virtual) return CNMEM_STATUS_SUCCESS;
-    static const bool debug = std::getenv("VDNN_DEBUG_POOL") != nullptr;
     for (const Fence& f : g_pool.fences)
         if (f.begin < off + len && off < f.end)
-            for (int s = 0; s < numStreams; ++s) {
-                if (streams[s] == f.stream) continue;
-                if (debug) std::fprintf(stderr, "[pool] %zu bytes at %zu for stream %p wait for event %llu of stream %p on [%zu, %zu); %zu events pending\n",
-                                        len, off, (void*)streams[s], f.seq, (void*)f.stream, f.begin, f.end, g_pool.fences.size());
-                if (cudaStreamWaitEvent(streams[s], f.event, 0) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
-            }
+            for (int s = 0; s < numStreams; ++s)
+                if (streams[s] != f.stream && cudaStreamWaitEvent(streams[s], f.event, 0) != cudaSuccess) return CNMEM_STATUS_CUDA_ERROR;
     return CNMEM_STATUS_SUCCESS;
 }
 
