@@ -325,8 +325,9 @@ def run_b200(args):
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": peaks["tflops"], "unit": "TFLOP/s",
                      "frac": (achieved_tf / peaks["tflops"]) if achieved_tf else None, "traffic": contraction_bytes,
-                     "traffic_note": "DRAM bytes per step of the contraction kernels = their algorithmic bytes: one ncu capture "
-                                     "(conv 256->256 @56x56 batch 32) read 208.8 MB against 208.1 MB algorithmic, scaled to all layers",
+                     "traffic_note": "algorithmic DRAM bytes per step of the contraction kernels; ncu captures (conv 256->256 @56x56 batch 32) "
+                                     "read 107.9 MB in forward against 105.2 MB algorithmic reads (no re-reads); the filter gradient "
+                                     "reads dy as tile images of twice its bytes (322.9 MB against 205.5 MB)",
                      "kernel": "CONV/FC contraction layers (forward, data gradient, filter gradient)",
                      "peak_source": peaks["source"] + " bf16 sustained; the fp32-accurate 3xTF32 ceiling is peak/6",
                      "elementwise_gbs": elem_gbs, "hbm_peak_gbs": peaks["hbm_gbs"]},
