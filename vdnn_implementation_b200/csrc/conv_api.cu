@@ -4,6 +4,7 @@
 // and runs the selected engine.  Split results are combined either with fp32 atomics straight
 // into the output (MEMORY_OPT: no workspace) or through per-split partial tiles in the caller's
 // workspace followed by a fixed-order reduction (PERF_OPT: deterministic).
+#include <cuda_pipeline.h>
 #include "common.cuh"
 #include "gemm_ffma.cuh"
 #include "gemm_tc.cuh"
@@ -109,6 +110,125 @@ __global__ void __launch_bounds__(256) dgrad_small_c_kernel(int N, int C, int H,
             *o = v;
         }
     }
+}
+
+// The same for stride 1 (the first layer of VGG16: 3 x 3, pad 1), where every tap of every filter connects a pixel:
+// 1728 multiply-adds per pixel at C = 3, K = 64, far too many to feed from L1.  A CTA of 128 threads owns an
+// 8 x 128 tile of input pixels of one image; dy is staged through shared memory, 8 filters at a time, as the tile
+// plus its halo; every thread owns one column of the tile and keeps the R+7 staged values of a column in registers,
+// so each shared-memory load feeds up to 8 rows x R taps x C channels.  The filter bank sits in shared memory as
+// one float4 (channels 0..3) per filter and tap.
+constexpr int S1_TH = 8, S1_TW = 128, S1_KC = 8;
+template <int R, int S, int CC>
+__global__ void __launch_bounds__(S1_TW) dgrad_small_c_s1_kernel(int C, int H, int W, int K, int P, int Q, int pad_h, int pad_w,
+                                                                  float alpha, float beta, const float* __restrict__ w,
+                                                                  const float* __restrict__ dy, float* __restrict__ dx) {
+    extern __shared__ float4 s1_smem[];
+    constexpr int RS = R * S, ROWS = S1_TH + R - 1, PITCH = S1_TW + S - 1;
+    float4* w_s = s1_smem;                                            // [K][R*S]
+    float* dy_s = reinterpret_cast<float*>(s1_smem + K * RS);          // [S1_KC][ROWS][PITCH]
+    const int tx = threadIdx.x, n = blockIdx.z, h0 = blockIdx.y * S1_TH, x0 = blockIdx.x * S1_TW;
+    for (int i = tx; i < K * RS; i += S1_TW) {
+        const int k = i / RS, t = i - k * RS;
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int c = 0; c < C; ++c) v[c] = w[(k * C + c) * RS + t];
+        w_s[i] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+    float acc[S1_TH][CC];
+#pragma unroll
+    for (int i = 0; i < S1_TH; ++i)
+#pragma unroll
+        for (int c = 0; c < CC; ++c) acc[i][c] = 0.0f;
+    // tile row tr holds output row p0 + tr, tile column tc holds output column q0 + tc
+    const int p0 = h0 + pad_h - (R - 1), q0 = x0 + pad_w - (S - 1);
+    const float* dyn = dy + static_cast<size_t>(n) * K * P * Q;
+    for (int k0 = 0; k0 < K; k0 += S1_KC) {
+        const int kc = min(S1_KC, K - k0);
+        __syncthreads();                                   // the previous chunk has been consumed (first pass: w_s is complete)
+        // asynchronous 4-byte copies straight into shared memory (zero-filled outside the image): all of a chunk's
+        // loads are in flight at once.  Thread tx copies tile column tx of every row (the first S-1 threads also
+        // copy the halo columns on the right), so the column tests and offsets are computed once.
+        {
+            const int q_a = q0 + tx, col_b = S1_TW + tx, q_b = q0 + col_b;
+            const bool ok_a = static_cast<unsigned>(q_a) < static_cast<unsigned>(Q);
+            const bool has_b = col_b < PITCH, ok_b = has_b && static_cast<unsigned>(q_b) < static_cast<unsigned>(Q);
+            for (int kk = 0; kk < kc; ++kk) {
+                const float* src = dyn + static_cast<size_t>(k0 + kk) * P * Q;
+                float* dst = dy_s + kk * ROWS * PITCH;
+#pragma unroll
+                for (int tr = 0; tr < ROWS; ++tr) {
+                    const int p = p0 + tr;
+                    const bool row_ok = static_cast<unsigned>(p) < static_cast<unsigned>(P);
+                    const float* rowp = src + (row_ok ? p : 0) * Q;
+                    const bool a = row_ok && ok_a;
+                    __pipeline_memcpy_async(dst + tr * PITCH + tx, rowp + (a ? q_a : 0), sizeof(float), a ? 0 : sizeof(float));
+                    if (has_b) {
+                        const bool b2 = row_ok && ok_b;
+                        __pipeline_memcpy_async(dst + tr * PITCH + col_b, rowp + (b2 ? q_b : 0), sizeof(float), b2 ? 0 : sizeof(float));
+                    }
+                }
+            }
+        }
+        __pipeline_commit();
+        __pipeline_wait_prior(0);
+        __syncthreads();
+        for (int kk = 0; kk < kc; ++kk) {
+            const float* tile = dy_s + kk * ROWS * PITCH;
+            const float4* wk = w_s + (k0 + kk) * RS;
+#pragma unroll
+            for (int s = 0; s < S; ++s) {
+                float colv[ROWS];
+#pragma unroll
+                for (int tr = 0; tr < ROWS; ++tr) colv[tr] = tile[tr * PITCH + tx + (S - 1 - s)];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const float4 w4 = wk[r * S + s];
+                    const float wc[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+                    for (int i = 0; i < S1_TH; ++i) {
+                        const float g = colv[i + (R - 1) - r];
+#pragma unroll
+                        for (int c = 0; c < CC; ++c) acc[i][c] = fmaf(g, wc[c], acc[i][c]);
+                    }
+                }
+            }
+        }
+    }
+    const int x = x0 + tx;
+    if (x >= W) return;
+#pragma unroll
+    for (int i = 0; i < S1_TH; ++i) {
+        const int h = h0 + i;
+        if (h >= H) break;
+#pragma unroll
+        for (int c = 0; c < CC; ++c) {
+            if (c >= C) break;
+            float* o = dx + ((static_cast<size_t>(n) * C + c) * H + h) * W + x;
+            float v = alpha * acc[i][c];
+            if (beta != 0.0f) v = fmaf(beta, *o, v);
+            *o = v;
+        }
+    }
+}
+
+template <int R, int S, int CC>
+int launch_dgrad_small_c_s1(const vdnn_conv_desc* d, int P, int Q, float alpha, float beta, const float* w, const float* dy,
+                            float* dx, cudaStream_t stream) {
+    const size_t smem = static_cast<size_t>(d->k) * R * S * sizeof(float4) +
+                        static_cast<size_t>(S1_KC) * (S1_TH + R - 1) * (S1_TW + S - 1) * sizeof(float);
+    if (smem > 96 * 1024 || d->n > 65535) return VDNN_ERR_UNSUPPORTED;
+    auto kern = dgrad_small_c_s1_kernel<R, S, CC>;
+    static bool configured[16] = {false};
+    int dev = 0;
+    VDNN_CUDA(cudaGetDevice(&dev));
+    if (dev < 16 && !configured[dev]) {
+        VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+        configured[dev] = true;
+    }
+    dim3 grid(ceil_div(d->w, S1_TW), ceil_div(d->h, S1_TH), d->n);
+    kern<<<grid, S1_TW, smem, stream>>>(d->c, d->h, d->w, d->k, P, Q, d->pad_h, d->pad_w, alpha, beta, w, dy, dx);
+    VDNN_LAUNCHED();
+    return VDNN_OK;
 }
 
 // A convolution whose filter covers the whole (unpadded) input produces one output pixel per image: it is a fully
@@ -318,6 +438,11 @@ int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, cons
     if (is_full_extent(d))      // dX[n][j] = sum_k W[k][j] dY[n][k]   (the FC data-gradient product, layer.cu:725-733)
         return vdnn_sgemm(0, 0, d->c * rs, d->n, d->k, alpha, w, d->c * rs, dy, d->k, beta, dx, d->c * rs, algo_mode, workspace,
                           workspace_bytes, stream);
+    if (d->c <= SMALL_C_MAX && d->stride_h == 1 && d->stride_w == 1 && d->r == 3 && d->s == 3) {
+        const int st = d->c == 3 ? launch_dgrad_small_c_s1<3, 3, 3>(d, P, Q, alpha, beta, w, dy, dx, as_stream(stream))
+                                 : launch_dgrad_small_c_s1<3, 3, 4>(d, P, Q, alpha, beta, w, dy, dx, as_stream(stream));
+        if (st != VDNN_ERR_UNSUPPORTED) return st;
+    }
     const size_t small_smem = static_cast<size_t>(d->k) * d->c * rs * sizeof(float);
     if (d->c <= SMALL_C_MAX && small_smem <= SMALL_C_SMEM_MAX) {
         static bool configured[16] = {false};
