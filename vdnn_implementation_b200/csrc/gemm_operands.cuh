@@ -104,8 +104,13 @@ struct XGatherPixRowsT {
                 const bool ok = pc.valid && static_cast<unsigned>(ih) < static_cast<unsigned>(g.H) &&
                                 static_cast<unsigned>(iw) < static_cast<unsigned>(g.W);
                 const float* p = g.x + pc.base + f.off + ih * g.W + iw;
+                if (lim >= RUN) {                                 // every k block but the last: no test per element
 #pragma unroll
-                for (int e = 0; e < RUN; ++e) v[e] = (ok && e < lim) ? __ldg(p + e * g.hw) : 0.0f;
+                    for (int e = 0; e < RUN; ++e) v[e] = ok ? __ldg(p + e * g.hw) : 0.0f;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < RUN; ++e) v[e] = (ok && e < lim) ? __ldg(p + e * g.hw) : 0.0f;
+                }
             } else {
 #pragma unroll
                 for (int e = 0; e < RUN; ++e) v[e] = e < lim ? g.at(pc, g.filt_tap(kk0 + e)) : 0.0f;
@@ -215,8 +220,13 @@ struct DyGather {
             int pos = 0;
             const bool ok = locate(pc, f, &pos);
             const float* p = dy + pc.base + f.off + pos;
+            if (lim >= RUN) {
 #pragma unroll
-            for (int e = 0; e < RUN; ++e) v[e] = (ok && e < lim) ? __ldg(p + e * pq) : 0.0f;
+                for (int e = 0; e < RUN; ++e) v[e] = ok ? __ldg(p + e * pq) : 0.0f;
+            } else {
+#pragma unroll
+                for (int e = 0; e < RUN; ++e) v[e] = (ok && e < lim) ? __ldg(p + e * pq) : 0.0f;
+            }
         } else {
 #pragma unroll
             for (int e = 0; e < RUN; ++e) v[e] = e < lim ? load(pc, col(kk0 + e)) : 0.0f;
@@ -261,8 +271,13 @@ struct SplitDense {
         const int lim = min(kend, cols) - kk0;
         if (c0.rem + RUN <= static_cast<int>(col_div.d)) {    // the run stays inside one column segment
             const float* q = p + r.off + c0.off;
+            if (lim >= RUN) {
 #pragma unroll
-            for (int e = 0; e < RUN; ++e) v[e] = (r.valid && e < lim) ? __ldg(q + e * col_lo) : 0.0f;
+                for (int e = 0; e < RUN; ++e) v[e] = r.valid ? __ldg(q + e * col_lo) : 0.0f;
+            } else {
+#pragma unroll
+                for (int e = 0; e < RUN; ++e) v[e] = (r.valid && e < lim) ? __ldg(q + e * col_lo) : 0.0f;
+            }
         } else {
 #pragma unroll
             for (int e = 0; e < RUN; ++e) v[e] = e < lim ? load(r, col(kk0 + e)) : 0.0f;
