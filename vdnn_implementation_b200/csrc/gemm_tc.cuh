@@ -37,10 +37,16 @@ constexpr unsigned SPIN_TRIES = 1u << 26;
 // 0 = healthy; otherwise 100 + role of the first wait that expired (1 producer, 2 mma, 3 epilogue).
 __device__ int g_tc_error = 0;
 
-template <int BN> struct Config {
+// PAIRED: two CTAs of this configuration share an SM (see STAGES).
+template <int BN, bool PAIRED = false> struct Config {
     static constexpr int B_TILE_BYTES = BN * BK * 4;
     static constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;
-    static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+    // The 64-column tile with one gathered operand is bound by its producers (the tensor core needs a quarter of
+    // their time per k block), so two of its CTAs share an SM: two stages each, and the producers of one fill the
+    // issue slots the other leaves (64 -> 64 @ 224x224 forward: 1.65 -> 1.34 ms).  With both operands gathered (the
+    // filter gradient of 64-filter layers) the deeper pipeline of a single CTA was the faster one.
+    static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : (PAIRED ? 2 : 4));
+    static constexpr int CTAS_PER_SM = PAIRED ? 2 : 1;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
     // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BN, M = 128
     static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
@@ -176,10 +182,10 @@ struct Gather {
 // fetches a stage's B tiles with a single bulk asynchronous copy (the TMA engine, no tensor map needed for a
 // contiguous image) that reports its bytes to the stage's "full" barrier; the producers only gather A.
 template <class OpA, class OpB, bool AKC, bool BKC, int BN, bool BBULK>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, Config<BN, BN == 64 && !(AKC && BKC)>::CTAS_PER_SM)
 gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int K, int k_chunk,
             const char* __restrict__ b_tiles, int kblocks_total) {
-    typedef Config<BN> Cfg;
+    typedef Config<BN, BN == 64 && !(AKC && BKC)> Cfg;
     constexpr int S = Cfg::STAGES;
     extern __shared__ char smem_raw[];
     // operand tiles need 1 KB alignment (swizzle atoms); barriers and the TMEM slot follow them
@@ -377,7 +383,7 @@ inline size_t bulk_bytes(int N, int K) {
 template <class OpA, class OpB, bool AKC, bool BKC, int BN, bool BBULK>
 int launch_bn(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K, int splits, int k_chunk, cudaStream_t stream,
               char* b_tiles) {
-    typedef Config<BN> Cfg;
+    typedef Config<BN, BN == 64 && !(AKC && BKC)> Cfg;
     static bool configured[16] = {false};
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
