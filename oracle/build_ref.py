@@ -1,5 +1,5 @@
-"""Builds the reference itself, unmodified, from its sources where they lie (/root/reference), into
-oracle/_ref/ (git-ignored binaries).  TEST INFRASTRUCTURE ONLY.
+"""Builds the reference itself, unmodified, from its sources where they lie (the read-only checkout named by
+VDNN_REFERENCE_DIR), into oracle/_ref/ (git-ignored binaries).  TEST INFRASTRUCTURE ONLY.
 
   oracle/_ref/vdnn_ref      the reference's command-line program (vdnn.cu + network.cu + layer.cu)
   oracle/_ref/ref_harness   oracle/ref/ref_harness.cu linked against the reference's Layer class
@@ -18,7 +18,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-REF = "/root/reference"
+REF = os.environ.get("VDNN_REFERENCE_DIR", "/root/reference")
 OUT = os.path.join(HERE, "_ref")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
