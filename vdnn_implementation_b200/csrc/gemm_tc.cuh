@@ -62,13 +62,17 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 // Bounded wait for the phase with the given parity.  Returns false when the limit expired.
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    if (mbar_try(bar, parity)) return true;                  // the common case costs one instruction
     const unsigned long long t0 = clock64();
     for (unsigned it = 0; it < SPIN_TRIES; ++it) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
+        if (mbar_try(bar, parity)) return true;
         if ((it & 1023u) == 1023u && clock64() - t0 > SPIN_CYCLES) break;
     }
     return false;
@@ -112,7 +116,9 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-// x = hi + lo with hi representable in tf32 (10 explicit mantissa bits, round to nearest).
+// x = hi + lo with hi representable in tf32 (10 explicit mantissa bits, round to nearest, ties away from zero).
+// Two integer instructions: cvt.rna.tf32.f32 does the same in one, but on the quarter-rate conversion pipe,
+// and measured slower in the producers.
 __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
     hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
     lo = x - hi;
