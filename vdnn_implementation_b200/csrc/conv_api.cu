@@ -112,60 +112,67 @@ __global__ void __launch_bounds__(256) dgrad_small_c_kernel(int N, int C, int H,
     }
 }
 
-// The same for stride 1 (the first layer of VGG16: 3 x 3, pad 1), where every tap of every filter connects a pixel:
-// 1728 multiply-adds per pixel at C = 3, K = 64, far too many to feed from L1.  A CTA of 128 threads owns an
-// 8 x 128 tile of input pixels of one image; dy is staged through shared memory, 8 filters at a time, as the tile
-// plus its halo; every thread owns one column of the tile and keeps the R+7 staged values of a column in registers,
-// so each shared-memory load feeds up to 8 rows x R taps x C channels.  The filter bank sits in shared memory as
-// one float4 (channels 0..3) per filter and tap.
-constexpr int S1_TH = 8, S1_TW = 128, S1_KC = 8;
-template <int R, int S, int CC>
-__global__ void __launch_bounds__(S1_TW) dgrad_small_c_s1_kernel(int C, int H, int W, int K, int P, int Q, int pad_h, int pad_w,
-                                                                  float alpha, float beta, const float* __restrict__ w,
-                                                                  const float* __restrict__ dy, float* __restrict__ dx) {
+// The same with dy staged through shared memory, for filters of at most 3 taps per stride step in each direction
+// (R <= 3*stride: the first layers of VGG16, 3 x 3 / 1, and of AlexNet and OverFeat, 11 x 11 / 4).  With stride st the
+// input pixels fall into st*st phase classes ((h + pad) mod st, (x + pad) mod st); inside a class, pixel (i, j) of the
+// class, input (st*i + a - pad, st*j + b - pad), is a stride-1 correlation of dy with the sub-filter
+// w[a + st*u][b + st*v], u, v < 3 (zero where that leaves the filter):  dx = sum_{u,v} dy[i - u][j - v] * w[a+st*u][b+st*v].
+// A CTA of TW threads owns an 8 x TW tile of one class of one image; dy arrives 8 filters at a time as the tile plus
+// its halo; every thread owns one column of the tile and keeps the 10 staged values of a column in registers, so each
+// shared-memory load feeds up to 8 rows x 3 taps x C channels.  The sub-filters sit in shared memory as one float4
+// (channels 0..3) per filter and tap.
+constexpr int S1_TH = 8, S1_KC = 8;
+template <int TW, int CC>
+__global__ void __launch_bounds__(TW) dgrad_small_c_phase_kernel(int C, int H, int W, int K, int R, int S, int P, int Q, int pad_h,
+                                                                 int pad_w, int st, float alpha, float beta,
+                                                                 const float* __restrict__ w, const float* __restrict__ dy,
+                                                                 float* __restrict__ dx) {
     extern __shared__ float4 s1_smem[];
-    constexpr int RS = R * S, ROWS = S1_TH + R - 1, PITCH = S1_TW + S - 1;
-    float4* w_s = s1_smem;                                            // [K][R*S]
-    float* dy_s = reinterpret_cast<float*>(s1_smem + K * RS);          // [S1_KC][ROWS][PITCH]
-    const int tx = threadIdx.x, n = blockIdx.z, h0 = blockIdx.y * S1_TH, x0 = blockIdx.x * S1_TW;
-    for (int i = tx; i < K * RS; i += S1_TW) {
-        const int k = i / RS, t = i - k * RS;
-        float v[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int c = 0; c < C; ++c) v[c] = w[(k * C + c) * RS + t];
-        w_s[i] = make_float4(v[0], v[1], v[2], v[3]);
+    constexpr int ROWS = S1_TH + 2, PITCH = TW + 2;
+    float4* w_s = s1_smem;                                            // [K][3*3]
+    float* dy_s = reinterpret_cast<float*>(s1_smem + K * 9);           // [S1_KC][ROWS][PITCH]
+    const int tx = threadIdx.x;
+    const int cls = blockIdx.z % (st * st), n = blockIdx.z / (st * st), pa = cls / st, pb = cls - pa * st;
+    const int i0 = blockIdx.y * S1_TH, j0 = blockIdx.x * TW;          // tile origin in class coordinates
+    const int rs = R * S;
+    for (int i = tx; i < K * 9; i += TW) {
+        const int k = i / 9, t = i - k * 9, u = t / 3, v = t - u * 3;
+        const int r = pa + st * u, sx = pb + st * v;
+        float wv[4] = {0.f, 0.f, 0.f, 0.f};
+        if (r < R && sx < S)
+            for (int c = 0; c < C; ++c) wv[c] = w[(k * C + c) * rs + r * S + sx];
+        w_s[i] = make_float4(wv[0], wv[1], wv[2], wv[3]);
     }
     float acc[S1_TH][CC];
 #pragma unroll
     for (int i = 0; i < S1_TH; ++i)
 #pragma unroll
         for (int c = 0; c < CC; ++c) acc[i][c] = 0.0f;
-    // tile row tr holds output row p0 + tr, tile column tc holds output column q0 + tc
-    const int p0 = h0 + pad_h - (R - 1), q0 = x0 + pad_w - (S - 1);
+    // tile row tr holds dy row p0 + tr, tile column tc holds dy column q0 + tc
+    const int p0 = i0 - 2, q0 = j0 - 2;
     const float* dyn = dy + static_cast<size_t>(n) * K * P * Q;
+    const int q_a = q0 + tx, col_b = TW + tx, q_b = q0 + col_b;
+    const bool ok_a = static_cast<unsigned>(q_a) < static_cast<unsigned>(Q);
+    const bool has_b = col_b < PITCH, ok_b = has_b && static_cast<unsigned>(q_b) < static_cast<unsigned>(Q);
     for (int k0 = 0; k0 < K; k0 += S1_KC) {
         const int kc = min(S1_KC, K - k0);
         __syncthreads();                                   // the previous chunk has been consumed (first pass: w_s is complete)
-        // asynchronous 4-byte copies straight into shared memory (zero-filled outside the image): all of a chunk's
-        // loads are in flight at once.  Thread tx copies tile column tx of every row (the first S-1 threads also
-        // copy the halo columns on the right), so the column tests and offsets are computed once.
-        {
-            const int q_a = q0 + tx, col_b = S1_TW + tx, q_b = q0 + col_b;
-            const bool ok_a = static_cast<unsigned>(q_a) < static_cast<unsigned>(Q);
-            const bool has_b = col_b < PITCH, ok_b = has_b && static_cast<unsigned>(q_b) < static_cast<unsigned>(Q);
-            for (int kk = 0; kk < kc; ++kk) {
-                const float* src = dyn + static_cast<size_t>(k0 + kk) * P * Q;
-                float* dst = dy_s + kk * ROWS * PITCH;
+        // asynchronous 4-byte copies straight into shared memory (zero-filled outside dy): all of a chunk's loads are
+        // in flight at once.  Thread tx copies tile column tx of every row (the first two threads also the halo
+        // columns on the right), so the column tests and offsets are computed once.
+        for (int kk = 0; kk < kc; ++kk) {
+            const float* src = dyn + static_cast<size_t>(k0 + kk) * P * Q;
+            float* dst = dy_s + kk * ROWS * PITCH;
 #pragma unroll
-                for (int tr = 0; tr < ROWS; ++tr) {
-                    const int p = p0 + tr;
-                    const bool row_ok = static_cast<unsigned>(p) < static_cast<unsigned>(P);
-                    const float* rowp = src + (row_ok ? p : 0) * Q;
-                    const bool a = row_ok && ok_a;
-                    __pipeline_memcpy_async(dst + tr * PITCH + tx, rowp + (a ? q_a : 0), sizeof(float), a ? 0 : sizeof(float));
-                    if (has_b) {
-                        const bool b2 = row_ok && ok_b;
-                        __pipeline_memcpy_async(dst + tr * PITCH + col_b, rowp + (b2 ? q_b : 0), sizeof(float), b2 ? 0 : sizeof(float));
-                    }
+            for (int tr = 0; tr < ROWS; ++tr) {
+                const int p = p0 + tr;
+                const bool row_ok = static_cast<unsigned>(p) < static_cast<unsigned>(P);
+                const float* rowp = src + (row_ok ? p : 0) * Q;
+                const bool a = row_ok && ok_a;
+                __pipeline_memcpy_async(dst + tr * PITCH + tx, rowp + (a ? q_a : 0), sizeof(float), a ? 0 : sizeof(float));
+                if (has_b) {
+                    const bool b2 = row_ok && ok_b;
+                    __pipeline_memcpy_async(dst + tr * PITCH + col_b, rowp + (b2 ? q_b : 0), sizeof(float), b2 ? 0 : sizeof(float));
                 }
             }
         }
@@ -174,19 +181,19 @@ __global__ void __launch_bounds__(S1_TW) dgrad_small_c_s1_kernel(int C, int H, i
         __syncthreads();
         for (int kk = 0; kk < kc; ++kk) {
             const float* tile = dy_s + kk * ROWS * PITCH;
-            const float4* wk = w_s + (k0 + kk) * RS;
+            const float4* wk = w_s + (k0 + kk) * 9;
 #pragma unroll
-            for (int s = 0; s < S; ++s) {
+            for (int v = 0; v < 3; ++v) {
                 float colv[ROWS];
 #pragma unroll
-                for (int tr = 0; tr < ROWS; ++tr) colv[tr] = tile[tr * PITCH + tx + (S - 1 - s)];
+                for (int tr = 0; tr < ROWS; ++tr) colv[tr] = tile[tr * PITCH + tx + (2 - v)];
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const float4 w4 = wk[r * S + s];
+                for (int u = 0; u < 3; ++u) {
+                    const float4 w4 = wk[u * 3 + v];
                     const float wc[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
                     for (int i = 0; i < S1_TH; ++i) {
-                        const float g = colv[i + (R - 1) - r];
+                        const float g = colv[i + 2 - u];
 #pragma unroll
                         for (int c = 0; c < CC; ++c) acc[i][c] = fmaf(g, wc[c], acc[i][c]);
                     }
@@ -194,12 +201,12 @@ __global__ void __launch_bounds__(S1_TW) dgrad_small_c_s1_kernel(int C, int H, i
             }
         }
     }
-    const int x = x0 + tx;
-    if (x >= W) return;
+    const int x = st * (j0 + tx) + pb - pad_w;
+    if (x < 0 || x >= W) return;
 #pragma unroll
     for (int i = 0; i < S1_TH; ++i) {
-        const int h = h0 + i;
-        if (h >= H) break;
+        const int h = st * (i0 + i) + pa - pad_h;
+        if (h < 0 || h >= H) continue;
 #pragma unroll
         for (int c = 0; c < CC; ++c) {
             if (c >= C) break;
@@ -211,13 +218,15 @@ __global__ void __launch_bounds__(S1_TW) dgrad_small_c_s1_kernel(int C, int H, i
     }
 }
 
-template <int R, int S, int CC>
-int launch_dgrad_small_c_s1(const vdnn_conv_desc* d, int P, int Q, float alpha, float beta, const float* w, const float* dy,
-                            float* dx, cudaStream_t stream) {
-    const size_t smem = static_cast<size_t>(d->k) * R * S * sizeof(float4) +
-                        static_cast<size_t>(S1_KC) * (S1_TH + R - 1) * (S1_TW + S - 1) * sizeof(float);
-    if (smem > 96 * 1024 || d->n > 65535) return VDNN_ERR_UNSUPPORTED;
-    auto kern = dgrad_small_c_s1_kernel<R, S, CC>;
+template <int TW, int CC>
+int launch_dgrad_small_c_phase(const vdnn_conv_desc* d, int P, int Q, float alpha, float beta, const float* w, const float* dy,
+                               float* dx, cudaStream_t stream) {
+    const int st = d->stride_h;
+    const size_t smem = static_cast<size_t>(d->k) * 9 * sizeof(float4) +
+                        static_cast<size_t>(S1_KC) * (S1_TH + 2) * (TW + 2) * sizeof(float);
+    const long long slices = static_cast<long long>(d->n) * st * st;
+    if (smem > 96 * 1024 || slices > 65535) return VDNN_ERR_UNSUPPORTED;
+    auto kern = dgrad_small_c_phase_kernel<TW, CC>;
     static bool configured[16] = {false};
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
@@ -225,8 +234,10 @@ int launch_dgrad_small_c_s1(const vdnn_conv_desc* d, int P, int Q, float alpha, 
         VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
         configured[dev] = true;
     }
-    dim3 grid(ceil_div(d->w, S1_TW), ceil_div(d->h, S1_TH), d->n);
-    kern<<<grid, S1_TW, smem, stream>>>(d->c, d->h, d->w, d->k, P, Q, d->pad_h, d->pad_w, alpha, beta, w, dy, dx);
+    // class coordinates run over every i with 0 <= st*i + a - pad < H for some phase a: 0 .. (H - 1 + pad) / st
+    const int hv = (d->h - 1 + d->pad_h) / st + 1, wv = (d->w - 1 + d->pad_w) / st + 1;
+    dim3 grid(ceil_div(wv, TW), ceil_div(hv, S1_TH), static_cast<unsigned>(slices));
+    kern<<<grid, TW, smem, stream>>>(d->c, d->h, d->w, d->k, d->r, d->s, P, Q, d->pad_h, d->pad_w, st, alpha, beta, w, dy, dx);
     VDNN_LAUNCHED();
     return VDNN_OK;
 }
@@ -438,9 +449,14 @@ int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, cons
     if (is_full_extent(d))      // dX[n][j] = sum_k W[k][j] dY[n][k]   (the FC data-gradient product, layer.cu:725-733)
         return vdnn_sgemm(0, 0, d->c * rs, d->n, d->k, alpha, w, d->c * rs, dy, d->k, beta, dx, d->c * rs, algo_mode, workspace,
                           workspace_bytes, stream);
-    if (d->c <= SMALL_C_MAX && d->stride_h == 1 && d->stride_w == 1 && d->r == 3 && d->s == 3) {
-        const int st = d->c == 3 ? launch_dgrad_small_c_s1<3, 3, 3>(d, P, Q, alpha, beta, w, dy, dx, as_stream(stream))
-                                 : launch_dgrad_small_c_s1<3, 3, 4>(d, P, Q, alpha, beta, w, dy, dx, as_stream(stream));
+    if (d->c <= SMALL_C_MAX && d->stride_h == d->stride_w && d->r <= 3 * d->stride_h && d->s <= 3 * d->stride_w) {
+        const bool narrow = (d->w - 1 + d->pad_w) / d->stride_w + 1 <= 64;      // class coordinates fit a 64-wide tile
+        cudaStream_t cs = as_stream(stream);
+        int st;
+        if (d->c == 3) st = narrow ? launch_dgrad_small_c_phase<64, 3>(d, P, Q, alpha, beta, w, dy, dx, cs)
+                                   : launch_dgrad_small_c_phase<128, 3>(d, P, Q, alpha, beta, w, dy, dx, cs);
+        else st = narrow ? launch_dgrad_small_c_phase<64, 4>(d, P, Q, alpha, beta, w, dy, dx, cs)
+                         : launch_dgrad_small_c_phase<128, 4>(d, P, Q, alpha, beta, w, dy, dx, cs);
         if (st != VDNN_ERR_UNSUPPORTED) return st;
     }
     const size_t small_smem = static_cast<size_t>(d->k) * d->c * rs * sizeof(float);
