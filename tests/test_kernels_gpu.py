@@ -34,6 +34,10 @@ CONV_CASES = [  # n, c, h, w, k, r, pad, stride
     (4, 64, 28, 28, 128, 3, 1, 1),     # several full tiles, K = 576
     (3, 3, 32, 32, 64, 3, 1, 1),       # first-layer shape (C = 3, K = 27)
     (2, 130, 7, 7, 130, 3, 1, 1),      # ragged tile edges in every dimension
+    (2, 3, 17, 17, 8, 5, 2, 2),        # few input channels with stride and padding: the phase-class data gradient
+    (2, 2, 12, 12, 5, 3, 1, 2),
+    (2, 4, 11, 11, 6, 3, 0, 3),
+    (1, 3, 70, 150, 9, 3, 1, 1),       # wider than one 128-column tile of that kernel
 ]
 ENGINES = ["ffma", "tcgen05"]
 
