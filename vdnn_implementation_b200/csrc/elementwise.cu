@@ -200,10 +200,20 @@ __global__ void __launch_bounds__(kThreads) bwd_bias_kernel(int n, int k, int pq
         const float* p = dy + (static_cast<size_t>(in) * k + ch) * pq;
         if (vec) {
             const float4* p4 = reinterpret_cast<const float4*>(p);
-            for (int i = threadIdx.x; i < pq / 4; i += blockDim.x) {
-                float4 v = __ldcs(p4 + i);
-                acc += (v.x + v.y) + (v.z + v.w);
+            const int n4 = pq / 4, step = blockDim.x;
+            int i = threadIdx.x;
+            // four independent 16-byte loads in flight per thread
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            for (; i + 3 * step < n4; i += 4 * step) {
+                const float4 v0 = __ldcs(p4 + i), v1 = __ldcs(p4 + i + step), v2 = __ldcs(p4 + i + 2 * step), v3 = __ldcs(p4 + i + 3 * step);
+                a0 += (v0.x + v0.y) + (v0.z + v0.w); a1 += (v1.x + v1.y) + (v1.z + v1.w);
+                a2 += (v2.x + v2.y) + (v2.z + v2.w); a3 += (v3.x + v3.y) + (v3.z + v3.w);
             }
+            for (; i < n4; i += step) {
+                const float4 v = __ldcs(p4 + i);
+                a0 += (v.x + v.y) + (v.z + v.w);
+            }
+            acc += (a0 + a1) + (a2 + a3);
         } else {
             for (int i = threadIdx.x; i < pq; i += blockDim.x) acc += p[i];
         }
