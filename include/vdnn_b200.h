@@ -56,9 +56,18 @@ typedef enum { VDNN_ENGINE_AUTO = 0, VDNN_ENGINE_FFMA = 1, VDNN_ENGINE_TCGEN05 =
 int vdnn_set_engine(int engine);   /* process-wide; returns the previous value */
 int vdnn_get_engine(void);
 /* Health of the tensor-core engine.  Its kernels wait on shared-memory barriers with an iteration
- * limit; a wait that expires records a code (101 producer, 102 MMA issuer, 103 epilogue) instead of
+ * limit; a wait that expires records a code (101 producer, 102 MMA issuer, 103 epilogue, 104 self-test) instead of
  * spinning for ever.  Synchronises the device, stores the code (0 = healthy) and clears it. */
 int vdnn_engine_status(int* code);
+/* The same code written to *dst (device memory, or pinned host memory mapped into the device's address space) by a
+ * one-thread kernel in stream order: no synchronisation, nothing cleared.  The network driver calls it at the end of
+ * every backward pass and vdnn_network_synchronize returns VDNN_ERR_TIMEOUT when the word it left is not 0.
+ * No counterpart in the reference (cuDNN reports failures through its return codes, layer.h:73-128). */
+int vdnn_engine_status_publish(int* dst, void* stream);
+/* Self-test of that path: launches one warp that waits at most `limit_cycles` SM cycles (at most 2e9) on a barrier
+ * nothing arrives at.  The wait runs out, code 104 is recorded and the kernel returns; vdnn_engine_status then
+ * reports 104.  Nothing faults or hangs.  No counterpart in the reference. */
+int vdnn_engine_wait_selftest(unsigned long long limit_cycles, void* stream);
 
 /* Shape of one convolution: what the reference spreads over srcTensorDesc, filterDesc and
  * convDesc (layer.cu:152-204).  Dilation is 1, mode is cross-correlation (vdnn.h:20). */

@@ -1,7 +1,7 @@
 """Per-call timing of the contraction engines on the convolution shapes of VGG16.
 
-    python -m vdnn_implementation_b200.opbench --engine tcgen05 --batch 32
-    python -m vdnn_implementation_b200.opbench --engine tcgen05 --batch 32 --layer 5 --op fwd --reps 3   (one kernel, for ncu)
+    python opbench.py --engine tcgen05 --batch 32
+    python opbench.py --engine tcgen05 --batch 32 --layer 5 --op fwd --reps 3   (one kernel, for ncu)
 
 Times vdnn_conv_fwd / vdnn_conv_bwd_data / vdnn_conv_bwd_filter through the C ABI with CUDA events on
 the launching stream; PyTorch only owns the buffers.  Prints algorithmic TFLOP/s (2*M*N*K per call).

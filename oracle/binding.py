@@ -73,7 +73,7 @@ def lib(f32=False):
         L.orc_model_layers.argtypes = [C.c_int, C.c_int, C.POINTER(LayerSpec), C.c_int]
         L.orc_policy_trace.argtypes = [C.POINTER(LayerSpec), C.c_int, C.c_int, C.POINTER(C.c_int64),
                                        C.c_int, C.c_int, C.POINTER(Event), C.c_int,
-                                       C.POINTER(TraceSummary)]
+                                       C.POINTER(TraceSummary), C.c_int]
         _libs[name] = L
     return _libs[name]
 
@@ -270,7 +270,7 @@ def make_specs(tuples):
     return arr
 
 
-def policy_trace(specs, vdnn_type, ws=None, iterations=1, fix_input_leak=False, max_events=8192):
+def policy_trace(specs, vdnn_type, ws=None, iterations=1, fix_input_leak=False, max_events=8192, wide_workspace=False):
     arr = make_specs(list(specs))
     ev = (Event * max_events)()
     summ = TraceSummary()
@@ -279,7 +279,7 @@ def policy_trace(specs, vdnn_type, ws=None, iterations=1, fix_input_leak=False, 
         flat = [int(v) for row in ws for v in row]
         wsp = (C.c_int64 * len(flat))(*flat)
     rc = lib().orc_policy_trace(arr, len(arr), vdnn_type, wsp, iterations, int(fix_input_leak), ev,
-                                max_events, C.byref(summ))
+                                max_events, C.byref(summ), int(wide_workspace))
     assert rc == 0, "event buffer too small"
     events = [(e.kind, e.layer, e.tag, e.bytes, e.used) for e in ev[:summ.num_events]]
     return events, summ

@@ -1,5 +1,6 @@
 """Builds the reference itself, unmodified, from its sources where they lie (the read-only checkout named by
-VDNN_REFERENCE_DIR), into oracle/_ref/ (git-ignored binaries).  TEST INFRASTRUCTURE ONLY.
+VDNN_REFERENCE_DIR, or a directory `reference` beside this repository), into oracle/_ref/ (git-ignored binaries).
+TEST INFRASTRUCTURE ONLY.
 
   oracle/_ref/vdnn_ref      the reference's command-line program (vdnn.cu + network.cu + layer.cu)
   oracle/_ref/ref_harness   oracle/ref/ref_harness.cu linked against the reference's Layer class
@@ -18,7 +19,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-REF = os.environ.get("VDNN_REFERENCE_DIR", "/root/reference")
+# Where the reference checkout is: VDNN_REFERENCE_DIR, else a directory named `reference` beside this repository.
+REF = os.environ.get("VDNN_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
 OUT = os.path.join(HERE, "_ref")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 

@@ -759,13 +759,15 @@ static void emit(tracer* t, int kind, int layer, int tag, int64_t bytes) {
 
 int orc_policy_trace(const orc_layer_spec* specs, int L, int vdnn_type, const int64_t* ws,
                      int iterations, int fix_input_leak, orc_event* events, int max_events,
-                     orc_trace_summary* sum) {
+                     orc_trace_summary* sum, int wide_workspace) {
     tracer t; memset(&t, 0, sizeof t); t.ev = events; t.max = events ? max_events : 0;
     int64_t* srcB = malloc(sizeof(int64_t) * L); int64_t* dstB = malloc(sizeof(int64_t) * L);
     int* types = malloc(sizeof(int) * L);
     unsigned char* off = calloc(L, 1); unsigned char* pre = calloc(L, 1);
     int64_t max_dxdy = 0, pinned = 0, offB = 0, preB = 0;
-    int32_t max_ws = 0;    /* network.cu:1025-1040 keeps the maximum in an int: sizes wrap at 2^31 */
+    /* network.cu:1025-1040 keeps the maximum in an int: sizes wrap at 2^31.  wide_workspace = 1 keeps it in 64 bits
+       instead (what a driver must do whose kernels really write the workspace they asked for). */
+    int64_t max_ws = 0;
     for (int l = 0; l < L; ++l) {
         int n, c, h, w; orc_layer_out_dims(&specs[l], &n, &c, &h, &w);
         srcB[l] = 4 * (int64_t)src_size(&specs[l]); dstB[l] = 4 * (int64_t)n * c * h * w;
@@ -783,7 +785,7 @@ int orc_policy_trace(const orc_layer_spec* specs, int L, int vdnn_type, const in
         if (vdnn_type == ORC_BASELINE) emit(&t, ORC_EV_ALLOC, l, ORC_TAG_DST, dstB[l]);
         if (srcB[l] > max_dxdy) max_dxdy = srcB[l];
         if (IS_C(l)) for (int j = 0; j < 3; ++j) {
-            int32_t temp = (int32_t)(uint32_t)(uint64_t)WS(l, j);
+            int64_t temp = wide_workspace ? WS(l, j) : (int64_t)(int32_t)(uint32_t)(uint64_t)WS(l, j);
             if (max_ws < temp) max_ws = temp;
         }
     }
@@ -791,7 +793,7 @@ int orc_policy_trace(const orc_layer_spec* specs, int L, int vdnn_type, const in
     if (vdnn_type == ORC_BASELINE) {                       /* network.cu:894-906 */
         emit(&t, ORC_EV_ALLOC, -1, ORC_TAG_DXDY, max_dxdy);
         emit(&t, ORC_EV_ALLOC, -1, ORC_TAG_DXDY, max_dxdy);
-        if (max_ws > 0) emit(&t, ORC_EV_ALLOC, -1, ORC_TAG_WS, (int64_t)max_ws);
+        if (max_ws > 0) emit(&t, ORC_EV_ALLOC, -1, ORC_TAG_WS, max_ws);
     } else if (vdnn_type == ORC_VDNN_ALL) {                /* network.cu:913-923 */
         for (int l = 0; l < L - 1; ++l) { off[l] = 1; pinned += srcB[l]; }
     } else if (vdnn_type == ORC_VDNN_CONV) {               /* network.cu:926-938 */

@@ -147,10 +147,12 @@ typedef struct {
  * Replays construction, `iterations` x (forward, backward).  The reference re-prefetches layer 0
  * into a fresh buffer and drops the old input allocation (network.cu:1156,1185): with
  * fix_input_leak = 0 that leak is replayed, with 1 the old input buffer is freed at the end of
- * backward.  Returns 0, or -1 if max_events was too small (summary still valid). */
+ * backward.  wide_workspace = 0 sizes BASELINE's shared workspace as the reference does, as the maximum kept in an
+ * int (network.cu:1025-1040: sizes beyond 2^31 wrap); 1 keeps the maximum in 64 bits.
+ * Returns 0, or -1 if max_events was too small (summary still valid). */
 int orc_policy_trace(const orc_layer_spec* specs, int num_layers, int vdnn_type,
                      const int64_t* ws, int iterations, int fix_input_leak, orc_event* events,
-                     int max_events, orc_trace_summary* summary);
+                     int max_events, orc_trace_summary* summary, int wide_workspace);
 /* findPrefetchLayer (network.cu:1198-1207) over explicit tables. */
 int orc_find_prefetch_layer(const int* layer_types, const unsigned char* is_offload,
                             unsigned char* is_prefetched, int cur);

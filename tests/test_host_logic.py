@@ -289,3 +289,28 @@ def test_custom_topology_dry_run(vdnn, oracle):
         assert net.trace() == ev
     finally:
         net.close()
+
+
+@pytest.mark.parametrize("model", ["ALEXNET", "OVERFEAT", "VGG16_64", "VGG16_128", "VGG16_256"])
+def test_baseline_shared_workspace_covers_every_layer(vdnn, oracle, model):
+    """BASELINE hands one workspace block to all layers (network.cu:894-906).  The reference sizes it as a maximum
+    kept in an int, which wraps for requests beyond 2^31 bytes; a kernel that then writes the workspace it asked for
+    would overrun the block.  Here the maximum is kept in 64 bits: the block is at least as large as every request."""
+    net = vdnn.Network(model, "BASELINE", "VDNN_PERF_OPT_ALGO", device=-1, pool_bytes=170e9)
+    try:
+        specs = [s.astuple() for s in net.layer_specs()]
+        ws = _perf_workspaces(vdnn, specs)
+        largest = max(max(w) for w in ws)
+        shared = [e for e in net.trace() if e[0] == 0 and e[1] == -1 and e[2] == 6]       # alloc, network-owned, workspace
+        assert len(shared) == 1 and shared[0][3] == largest
+        net.step()
+        ev, summ = oracle.policy_trace(specs, oracle.BASELINE, ws=ws, fix_input_leak=True, wide_workspace=True)
+        assert net.trace() == ev and net.stats()["pool_peak_bytes"] == summ.peak_bytes
+    finally:
+        net.close()
+
+
+def test_padded_pooling_is_refused(vdnn):
+    specs = [(7, 2, 3, 8, 8, 1, 1, 2, 2, 0, 2, 2), (6, 2, 3, 5, 5, 0, 0, 0, 0, 0, 0, 0)]
+    with pytest.raises(vdnn.VdnnError):
+        vdnn.Network("CUSTOM_CNN", "VDNN_NONE", "VDNN_MEMORY_OPT_ALGO", device=-1, custom_layers=specs)

@@ -37,6 +37,11 @@ inline int cuda_fail(cudaError_t e) {
 // (queried once per device) so that every SM gets the same number of resident blocks.
 int sm_count();
 
+// True exactly once per device and call site (`seen` is the site's own table): kernels raise their dynamic shared
+// memory limit the first time they run on a device.  The table grows with the device ordinal.
+bool first_use_on_device(void** seen_table, int device);
+#define VDNN_ONCE_PER_DEVICE(dev) ([&]() { static void* _tbl = nullptr; return ::vdnn::first_use_on_device(&_tbl, (dev)); }())
+
 inline cudaStream_t as_stream(void* s) { return static_cast<cudaStream_t>(s); }
 
 template <typename T>

@@ -227,13 +227,10 @@ int launch_dgrad_small_c_phase(const vdnn_conv_desc* d, int P, int Q, float alph
     const long long slices = static_cast<long long>(d->n) * st * st;
     if (smem > 96 * 1024 || slices > 65535) return VDNN_ERR_UNSUPPORTED;
     auto kern = dgrad_small_c_phase_kernel<TW, CC>;
-    static bool configured[16] = {false};
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
-    if (dev < 16 && !configured[dev]) {
+    if (VDNN_ONCE_PER_DEVICE(dev))
         VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
-        configured[dev] = true;
-    }
     // class coordinates run over every i with 0 <= st*i + a - pad < H for some phase a: 0 .. (H - 1 + pad) / st
     const int hv = (d->h - 1 + d->pad_h) / st + 1, wv = (d->w - 1 + d->pad_w) / st + 1;
     dim3 grid(ceil_div(wv, TW), ceil_div(hv, S1_TH), static_cast<unsigned>(slices));
@@ -372,6 +369,20 @@ int vdnn_engine_status(int* code) {
     return tc::take_error(code);
 }
 
+int vdnn_engine_status_publish(int* dst, void* stream) {
+    if (!dst) return VDNN_ERR_BAD_ARG;
+    tc::publish_error_kernel<<<1, 1, 0, as_stream(stream)>>>(dst);
+    VDNN_LAUNCHED();
+    return VDNN_OK;
+}
+
+int vdnn_engine_wait_selftest(unsigned long long limit_cycles, void* stream) {
+    if (limit_cycles == 0 || limit_cycles > 2000000000ull) return VDNN_ERR_BAD_ARG;      // at most about a second
+    tc::wait_probe_kernel<<<1, 32, 0, as_stream(stream)>>>(limit_cycles);
+    VDNN_LAUNCHED();
+    return VDNN_OK;
+}
+
 int vdnn_conv_out_dims(const vdnn_conv_desc* d, int* p, int* q) {
     int P, Q;
     if (!p || !q || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
@@ -461,13 +472,10 @@ int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, cons
     }
     const size_t small_smem = static_cast<size_t>(d->k) * d->c * rs * sizeof(float);
     if (d->c <= SMALL_C_MAX && small_smem <= SMALL_C_SMEM_MAX) {
-        static bool configured[16] = {false};
         int dev = 0;
         VDNN_CUDA(cudaGetDevice(&dev));
-        if (dev < 16 && !configured[dev]) {
+        if (VDNN_ONCE_PER_DEVICE(dev))
             VDNN_CUDA(cudaFuncSetAttribute(dgrad_small_c_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SMALL_C_SMEM_MAX)));
-            configured[dev] = true;
-        }
         const long long total = static_cast<long long>(d->n) * hw;
         long long blocks = (total + 255) / 256;
         const long long cap = static_cast<long long>(sm_count()) * (small_smem > 100 * 1024 ? 1 : 2) * 2;
@@ -550,13 +558,16 @@ namespace {
 // Scratch for vdnn_conv_bwd_filter_static.  In host code this name is only a handle for the
 // symbol, not a device address: the address comes from cudaGetSymbolAddress, per device.
 static __device__ __align__(256) float g_static_scratch[VDNN_STATIC_SCRATCH_BYTES / sizeof(float)];
-float* g_static_scratch_addr[16] = {nullptr};
+constexpr int STATIC_SCRATCH_MAX_DEVICES = 64;
+float* g_static_scratch_addr[STATIC_SCRATCH_MAX_DEVICES] = {nullptr};
 
-// Device address of the scratch array on the current device; resolved on first use per device.
+// Device address of the scratch array on the current device; resolved on first use per device.  The table is not
+// guarded: two host threads making their first call on one device at the same time both look the address up and
+// store the same value.  Device ordinals beyond the table are refused, never silently skipped.
 int static_scratch_address(float** out) {
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= 16) return VDNN_ERR_UNSUPPORTED;
+    if (dev < 0 || dev >= STATIC_SCRATCH_MAX_DEVICES) return VDNN_ERR_UNSUPPORTED;
     if (!g_static_scratch_addr[dev]) {
         void* p = nullptr;
         VDNN_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));

@@ -4,6 +4,9 @@
 // their grids in whole multiples of the SM count.
 #include <math.h>
 
+#include <mutex>
+#include <vector>
+
 #include "common.cuh"
 
 namespace vdnn {
@@ -12,15 +15,30 @@ thread_local int g_last_cuda_error = 0;
 unsigned long long g_kernel_launches = 0;
 
 int sm_count() {
-    static int cached[16] = {0};
+    static std::vector<int> cached;                      // indexed by device ordinal, grown on demand
+    static std::mutex lock;
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 16) return 148;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return 148;
+    std::lock_guard<std::mutex> g(lock);
+    if (cached.size() <= static_cast<size_t>(dev)) cached.resize(dev + 1, 0);
     if (!cached[dev]) {
         int n = 0;
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
         cached[dev] = n;
     }
     return cached[dev];
+}
+
+bool first_use_on_device(void** seen_table, int device) {
+    static std::mutex lock;
+    std::lock_guard<std::mutex> g(lock);
+    if (device < 0) return false;
+    std::vector<char>* seen = static_cast<std::vector<char>*>(*seen_table);
+    if (!seen) { seen = new std::vector<char>(); *seen_table = seen; }     // lives as long as the process
+    if (seen->size() <= static_cast<size_t>(device)) seen->resize(device + 1, 0);
+    if ((*seen)[device]) return false;
+    (*seen)[device] = 1;
+    return true;
 }
 
 namespace {

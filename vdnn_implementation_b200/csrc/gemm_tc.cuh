@@ -34,7 +34,7 @@ constexpr int A_TILE_BYTES = BM * BK * 4;              // 16 KB, one per hi / lo
 constexpr unsigned long long SPIN_CYCLES = 4000000000ull;   // ~2 s at 1.9 GHz
 constexpr unsigned SPIN_TRIES = 1u << 26;
 
-// 0 = healthy; otherwise 100 + role of the first wait that expired (1 producer, 2 mma, 3 epilogue).
+// 0 = healthy; otherwise 100 + role of the first wait that expired (1 producer, 2 mma, 3 epilogue, 4 the self-test).
 __device__ int g_tc_error = 0;
 
 // PAIRED: two CTAs of this configuration share an SM (see STAGES).
@@ -68,14 +68,17 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_for(uint32_t bar, uint32_t parity, unsigned long long cycles, unsigned tries) {
     if (mbar_try(bar, parity)) return true;                  // the common case costs one instruction
     const unsigned long long t0 = clock64();
-    for (unsigned it = 0; it < SPIN_TRIES; ++it) {
+    for (unsigned it = 0; it < tries; ++it) {
         if (mbar_try(bar, parity)) return true;
-        if ((it & 1023u) == 1023u && clock64() - t0 > SPIN_CYCLES) break;
+        if ((it & 1023u) == 1023u && clock64() - t0 > cycles) break;
     }
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    return mbar_wait_for(bar, parity, SPIN_CYCLES, SPIN_TRIES);
 }
 
 // K-major operand tile with 128-byte swizzle: row r is 128 bytes (32 fp32), 8 rows form a 1 KB atom,
@@ -122,6 +125,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
 __device__ __forceinline__ void split_tf32(float x, float& hi, float& lo) {
     hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
     lo = x - hi;
+}
+// The same for the passes that prepare operand images (bandwidth-bound, so two more instructions are free): an
+// infinite x, or one that rounds up to infinity, keeps lo = 0, so that the three partial products give +-inf as one
+// fp32 product would, not inf - inf.
+__device__ __forceinline__ void split_tf32_safe(float x, float& hi, float& lo) {
+    hi = __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
+    lo = (__float_as_uint(hi) & 0x7F800000u) == 0x7F800000u ? 0.0f : x - hi;
 }
 
 // Gathers a ROWS x 32 operand tile into registers and stores its hi / lo images.
@@ -370,7 +380,7 @@ __global__ void __launch_bounds__(256) pack_b_tiles_kernel(const OpB opb, int N,
 #pragma unroll
             for (int e = 0; e < 4; ++e) v[e] = (kk + e < K) ? opb.load(r, opb.col(kk + e)) : 0.0f;
         }
-        split_tf32(v[0], h.x, l.x); split_tf32(v[1], h.y, l.y); split_tf32(v[2], h.z, l.z); split_tf32(v[3], h.w, l.w);
+        split_tf32_safe(v[0], h.x, l.x); split_tf32_safe(v[1], h.y, l.y); split_tf32_safe(v[2], h.z, l.z); split_tf32_safe(v[3], h.w, l.w);
         char* img = out + tile * (2 * Cfg::B_TILE_BYTES);
         *reinterpret_cast<float4*>(img + swz(row, chunk)) = h;
         *reinterpret_cast<float4*>(img + Cfg::B_TILE_BYTES + swz(row, chunk)) = l;
@@ -390,14 +400,11 @@ template <class OpA, class OpB, bool AKC, bool BKC, int BN, bool BBULK>
 int launch_bn(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K, int splits, int k_chunk, cudaStream_t stream,
               char* b_tiles) {
     typedef Config<BN, BN == 64 && !(AKC && BKC)> Cfg;
-    static bool configured[16] = {false};
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
     auto kern = gemm_kernel<OpA, OpB, AKC, BKC, BN, BBULK>;
-    if (dev < 16 && !configured[dev]) {
+    if (VDNN_ONCE_PER_DEVICE(dev))
         VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        configured[dev] = true;
-    }
     dim3 grid(ceil_div(M, BM), ceil_div(N, BN), splits);
     if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
     const int kblocks = ceil_div(K, BK);
@@ -429,6 +436,22 @@ int launch(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K,
     if (bn == 128) return launch_bn<OpA, OpB, AKC, BKC, 128, false>(a, b, epi, M, N, K, splits, k_chunk, stream, nullptr);
     return launch_bn<OpA, OpB, AKC, BKC, 256, false>(a, b, epi, M, N, K, splits, k_chunk, stream, nullptr);
 }
+
+// One warp waits, with a short limit, on a barrier that nothing ever arrives at: the wait runs out, the code 104 is
+// recorded like any expired wait of the engine, and the kernel returns normally.  Exists so that the path
+// "a bounded wait expired -> status word -> host" can be exercised without disturbing the GPU.
+__global__ void wait_probe_kernel(unsigned long long cycles) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0 && !mbar_wait_for(smem_u32(&bar), 0u, cycles, 1u << 20)) atomicCAS(&g_tc_error, 0, 104);
+}
+
+// Copies the error word to *dst (device memory or mapped pinned host memory) in stream order, without clearing it.
+__global__ void publish_error_kernel(int* dst) { *dst = g_tc_error; }
 
 // Reads and clears the device-side error word (synchronises the device).
 inline int take_error(int* code) {

@@ -128,6 +128,9 @@ Layer::Layer(vdnn_t _vdnnMode, vdnnAlgoMode_t _vdnnAlgoMode, Layer_t _layerType,
         setOpAlgos(use);
     } break;
     case POOL:
+        // The reference hands its padding to cudnnSetPooling2dDescriptor (layer.cu:418-428) and every model passes 0;
+        // the pooling kernels here take no padding, so a padded window is refused rather than computed unpadded.
+        if (pad_h != 0 || pad_w != 0) { fprintf(stderr, "Padded pooling is not supported!\n"); return; }
         if (vdnn_pool_out_dims(h_in, w_in, r, s, stride_h, stride_w, &h_out, &w_out) != VDNN_OK) {
             fprintf(stderr, "Invalid pooling window!\n");
             return;
@@ -271,8 +274,10 @@ int Layer::convolutionForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, 
     FWD_PROLOGUE();
     const vdnn_conv_desc d = convDesc();
     // convolution and bias in one pass (the reference: cudnnConvolutionForward + cudnnAddTensor)
+    // a caller-owned (BASELINE: shared) block is announced with its own size, so that the size check of the ABI is real
     DEV(vdnn_conv_fwd(&d, mode, 1.0f, (const float*)srcData, (const float*)filterData, (const float*)biasData, 0.0f,
-                      (float*)dstData, curWorkSpace, fwdWorkSpaceSize, *stream_compute));
+                      (float*)dstData, curWorkSpace, workSpace != NULL ? handle->shared_workspace_bytes : fwdWorkSpaceSize,
+                      *stream_compute));
     if (_offloaded[layerId]) { const int o = offloadSrcData(_offloaded, _offloadedSrcData_h); if (o != 0) return o; }
     MARK(ev_fwd_done);
     if (workSpace == NULL && fwdWorkSpaceSize > 0)
@@ -295,7 +300,8 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
     }
     // data gradient with the weights as they were in forward
     DEV(vdnn_conv_bwd_data(&d, opMode[1], 1.0f, (const float*)filterData, (const float*)diffData, 0.0f, (float*)gradData,
-                           curWorkSpace, bwdDataWorkSpaceSize, *stream_compute));
+                           curWorkSpace, workSpace != NULL ? handle->shared_workspace_bytes : bwdDataWorkSpaceSize,
+                           *stream_compute));
     if (workSpace == NULL && bwdDataWorkSpaceSize > 0) {
         MARK(ev_bwd_done);
         const int f = handle->release(curWorkSpace, bwdDataWorkSpaceSize, layerId, TAG_WS, {*stream_compute});
@@ -312,7 +318,7 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
     }
     DEV(vdnn_conv_bwd_filter(&d, opMode[2], staged ? 1.0f : lr, (const float*)srcData, (const float*)diffData,
                              staged ? 0.0f : 1.0f, staged ? gradFilter : (float*)filterData, curWorkSpace,
-                             bwdFilterWorkSpaceSize, *stream_compute));
+                             workSpace != NULL ? handle->shared_workspace_bytes : bwdFilterWorkSpaceSize, *stream_compute));
     MARK(ev_bwd_done);
     if (workSpace == NULL && bwdFilterWorkSpaceSize > 0)
         return handle->release(curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, {*stream_compute});

@@ -49,6 +49,7 @@ struct vdnnContext {
     bool trace_enabled = true;
     std::vector<vdnn_trace_event> trace;
     int64_t offload_bytes = 0, prefetch_bytes = 0, pinned_bytes = 0, workspace_bytes_max = 0;
+    size_t shared_workspace_bytes = 0;     // BASELINE: size of the one workspace block all layers are handed
 
     // Offloads whose copy has not been enqueued yet.  The single device-to-host engine serves copies in
     // the order they were enqueued, forward produces layers 0..L and backward needs them L..0; so the copies
@@ -189,7 +190,6 @@ public:
 
 private:
     vdnn_conv_desc convDesc() const;
-    int     applyOrStageUpdate(bool isDynamic);
 
     vdnn_t         vdnnMode;
     vdnnAlgoMode_t vdnnAlgoMode;

@@ -269,8 +269,10 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
     if (!dry_run) {
         const size_t stage = sizeof(float) * (static_cast<size_t>(getInputSize()) + getOutputSize());
         if (cudaMallocHost(reinterpret_cast<void**>(&stage_h), stage) != cudaSuccess ||
-            cudaMallocHost(reinterpret_cast<void**>(&loss_h), 2 * sizeof(double)) != cudaSuccess)
+            cudaMallocHost(reinterpret_cast<void**>(&loss_h), 4 * sizeof(double)) != cudaSuccess)
             state = VDNN_ERR_CUDA;
+        else
+            memset(loss_h, 0, 4 * sizeof(double));      // [0..1] loss, [2] the engine's status word as published after backward
     }
     if (ctx.capture) { capDst.resize(numLayers); capGrad.resize(numLayers); }
 }
@@ -475,6 +477,7 @@ void Network::setVdnnType(vdnn_t newVdnnType) {
         if (ctx.alloc(&networkDiffData, dxdyBytes, -1, TAG_DXDY, false, {}) != 0 ||
             ctx.alloc(&networkGradData, dxdyBytes, -1, TAG_DXDY, false, {}) != 0) { state = VDNN_ERR_OUT_OF_MEMORY; return; }
         workSpaceBytes = findMaxWorkSpaceSize();
+        ctx.shared_workspace_bytes = workSpaceBytes;
         if (workSpaceBytes > 0 && ctx.alloc(&workSpace, workSpaceBytes, -1, TAG_WS, false, {}) != 0) state = VDNN_ERR_OUT_OF_MEMORY;
     } break;
     case VDNN_NONE: break;
@@ -501,16 +504,16 @@ size_t Network::findMaxDxDySize() {
     return static_cast<size_t>(ret) * sizeof(DATATYPE);
 }
 
-int Network::findMaxWorkSpaceSize() {       // network.cu:1025-1040: the maximum is kept in an int
-    int ret = 0;
+// network.cu:1025-1040 keeps this maximum in an int.  cuDNN's workspaces of a few GB then wrap and the shared block
+// comes out too small; this library's own workspaces (operand images of the large layers) pass 2^31 bytes as well,
+// and a kernel writing them into a wrapped-size block would overrun it.  The maximum is therefore kept in 64 bits,
+// and BASELINE hands the shared block's true size to every call so that the size check of the C ABI is real.
+size_t Network::findMaxWorkSpaceSize() {
+    size_t ret = 0;
     for (int i = 0; i < numLayers; i++)
-        if (layer[i]->LayerType() == FC_CONV || layer[i]->LayerType() == CONV) {
-            const size_t sizes[3] = {layer[i]->FwdWorkSpaceSize(), layer[i]->BwdDataWorkSpaceSize(), layer[i]->BwdFilterWorkSpaceSize()};
-            for (size_t v : sizes) {
-                const int temp = static_cast<int>(static_cast<unsigned>(v));
-                if (ret < temp) ret = temp;
-            }
-        }
+        if (layer[i]->LayerType() == FC_CONV || layer[i]->LayerType() == CONV)
+            ret = std::max(ret, std::max(layer[i]->FwdWorkSpaceSize(),
+                                         std::max(layer[i]->BwdDataWorkSpaceSize(), layer[i]->BwdFilterWorkSpaceSize())));
     return ret;
 }
 
@@ -721,6 +724,8 @@ int Network::backwardPropagation(bool isDynamic) {
         if (!ctx.dry_run) NET_CU(cudaEventRecord(ctx.ev_input_ready, stream_compute));
     }
     if (ctx.profiling) NET_CU(cudaEventRecord(ctx.pf_step_end, stream_compute));
+    // the tensor-core engine's status word, as it stands behind this step's kernels, goes to pinned host memory
+    if (!ctx.dry_run) NET_TRY(vdnn_engine_status_publish(reinterpret_cast<int*>(loss_h + 2), stream_compute));
     if (!ctx.dry_run) NET_CU(cudaEventRecord(ev_step_end, stream_compute));
     launchesLastStep = vdnn::g_kernel_launches - launchesAtStepStart;
     forwardDone = false;
@@ -736,6 +741,8 @@ int Network::synchronize() {
     NET_CU(cudaStreamSynchronize(stream_memory));
     NET_CU(cudaStreamSynchronize(ctx.stream_h2d));
     NET_CU(cudaStreamSynchronize(ctx.stream_comm));
+    // a bounded wait that ran out inside a contraction kernel left output tiles unwritten: the steps since are void
+    if (loss_h && *reinterpret_cast<volatile int*>(loss_h + 2) != 0) return VDNN_ERR_TIMEOUT;
     return VDNN_OK;
 }
 

@@ -30,7 +30,7 @@ public:
 
     /* Find max dx, dy, workspace size */
     size_t          findMaxDxDySize();
-    int             findMaxWorkSpaceSize();
+    size_t          findMaxWorkSpaceSize();
 
     /* Computation for training network */
     void            calculateFirstDiffData(void* result, void* first, void* second);

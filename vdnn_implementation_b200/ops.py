@@ -151,3 +151,9 @@ def engine_status():
     code = C.c_int()
     check(lib().vdnn_engine_status(C.byref(code)), "engine_status")
     return code.value
+
+
+def engine_wait_selftest(limit_cycles=2_000_000, stream=0):
+    """Runs the engine's bounded barrier wait on a barrier nothing arrives at: it runs out after `limit_cycles` SM
+    cycles, records code 104 and the kernel returns.  engine_status() then reports (and clears) 104."""
+    check(lib().vdnn_engine_wait_selftest(limit_cycles, _s(stream)), "engine_wait_selftest")
