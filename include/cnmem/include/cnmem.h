@@ -84,6 +84,8 @@ cnmemStatus_t vdnnPoolHighWater(size_t* peakBytes, int reset);
  * Host-side fault injection for the soft-OOM return path (layer.h:119-125). */
 cnmemStatus_t vdnnPoolFailAfter(int k);
 int vdnnPoolIsInitialized(void);
+/* Size in bytes of the live block that starts at `ptr` (what the request was rounded up to). */
+cnmemStatus_t vdnnPoolBlockBytes(const void* ptr, size_t* bytes);
 /* Bookkeeping-only pool: hands out addresses from a range that is never backed by memory and
  * never dereferenced.  Lets the allocation schedule of a network be replayed on a machine
  * without a GPU (dry-run networks, allocator unit tests). */

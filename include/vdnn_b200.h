@@ -68,6 +68,11 @@ int vdnn_engine_status_publish(int* dst, void* stream);
  * nothing arrives at.  The wait runs out, code 104 is recorded and the kernel returns; vdnn_engine_status then
  * reports 104.  Nothing faults or hangs.  No counterpart in the reference. */
 int vdnn_engine_wait_selftest(unsigned long long limit_cycles, void* stream);
+/* Measurement aid: one CTA per SM issues 12 * iterations tcgen05.mma kind::tf32 of 128 x 256 x 8 on zero operands in
+ * shared memory (no loads, no epilogue); *flops receives the hardware flops of the launch (2 * 128 * 256 * 8 per MMA).
+ * Time it with events on `stream`: flops / time is the dense TF32 rate of the tensor pipe on this device, and a third
+ * of it is the ceiling of the fp32-accurate 3xTF32 contraction kernels.  No counterpart in the reference. */
+int vdnn_engine_mma_rate_probe(int iterations, double* flops, void* stream);
 
 /* Shape of one convolution: what the reference spreads over srcTensorDesc, filterDesc and
  * convDesc (layer.cu:152-204).  Dilation is 1, mode is cross-correlation (vdnn.h:20). */

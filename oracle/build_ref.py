@@ -4,6 +4,9 @@ TEST INFRASTRUCTURE ONLY.
 
   oracle/_ref/vdnn_ref      the reference's command-line program (vdnn.cu + network.cu + layer.cu)
   oracle/_ref/ref_harness   oracle/ref/ref_harness.cu linked against the reference's Layer class
+  oracle/_ref/ref_warm      oracle/ref/ref_warm.cu: the reference's Network run for several iterations in one process
+  oracle/_ref/vdnn_dropin   the reference's vdnn.cu + network.cu, unmodified, driving this library's Layer class
+                            (libvdnn_b200.so) through csrc/ref_dropin.h: the drop-in claim, compiled
 
 What the reference needs and does not ship is supplied from this repository:
   * cuDNN 7's algorithm-preference calls (removed in cuDNN 8): oracle/ref/ref_compat.h, force-included;
@@ -53,6 +56,16 @@ def build():
     libs = ["-lcudnn", "-lcublas", "-lpthread"]
     run(common + [os.path.join(REF, "vdnn.cu")] + objs + [pool, "-o", os.path.join(OUT, "vdnn_ref")] + libs)
     run(common + [os.path.join(HERE, "ref", "ref_harness.cu"), objs[0], pool, rng, "-o", os.path.join(OUT, "ref_harness")] + libs)
+    run(common + [os.path.join(HERE, "ref", "ref_warm.cu")] + objs + [pool, "-o", os.path.join(OUT, "ref_warm")] + libs)
+    # the reference's driver (vdnn.cu + network.cu, unmodified) on top of THIS library's Layer class: its layer.h / vdnn.h are
+    # displaced by the force-included csrc/ref_dropin.h, layer.cu is not compiled at all, and cuDNN / cuBLAS are not linked
+    pkg = os.path.join(ROOT, "vdnn_implementation_b200")
+    if os.path.exists(os.path.join(pkg, "libvdnn_b200.so")):
+        run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "-w",
+             "-ccbin", "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++",
+             "-include", os.path.join(pkg, "csrc", "ref_dropin.h"), "-I", os.path.join(pkg, "csrc"), "-I", os.path.join(ROOT, "include"),
+             os.path.join(REF, "vdnn.cu"), os.path.join(REF, "network.cu"), "-o", os.path.join(OUT, "vdnn_dropin"),
+             "-L", pkg, "-lvdnn_b200", "-Xlinker", "-rpath=$ORIGIN/../../vdnn_implementation_b200"])
     for o in objs + [pool, rng]:
         os.remove(o)
     return True
@@ -62,3 +75,5 @@ if __name__ == "__main__":
     if build():
         print(os.path.join(OUT, "vdnn_ref"))
         print(os.path.join(OUT, "ref_harness"))
+        print(os.path.join(OUT, "ref_warm"))
+        print(os.path.join(OUT, "vdnn_dropin"))

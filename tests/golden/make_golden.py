@@ -9,6 +9,10 @@ Pipeline (the first two steps need the reference sources and a GPU; their output
          oracle/_ref/vdnn_ref {MODEL} {POLICY} {ALGO} | grep -E "WorkSpaceSize|\[Fwd\]|\[Bwd\]" > <runs_dir>/{MODEL}_{POLICY}_{ALGO}.log
   3. python tests/golden/make_golden.py <raw_dir> <runs_dir>
          writes tests/golden/ref_layers.npz (+ ref_layers.json) and tests/golden/ref_memory.json
+  4. for the layers at benchmark size:   oracle/_ref/ref_harness <big_dir> big    (same environment), then
+     python tests/golden/make_golden.py --big <big_dir>
+         writes tests/golden/ref_big.npz (+ ref_big.json): per tensor 4096 evenly strided samples, and in the json its
+         element count, stride, sum, sum of squares and largest magnitude over the whole tensor
 
 ref_layers: outputs of the reference's Layer::forward / Layer::backward for every layer type on seeded
 inputs (inputs are regenerated in the tests from the same counter-based generator).
@@ -57,6 +61,19 @@ def pack_memory(runs_dir):
     print(f"ref_memory: {len(out)} runs")
 
 
+def pack_big(raw_dir):
+    manifest = json.load(open(os.path.join(raw_dir, "manifest.json")))
+    arrays = {t["name"]: np.fromfile(os.path.join(raw_dir, t["name"] + ".bin"), dtype="<f4") for t in manifest["tensors"]}
+    for t in manifest["tensors"]:
+        assert arrays[t["name"]].size == t["samples"], t
+    np.savez_compressed(os.path.join(HERE, "ref_big.npz"), **arrays)
+    json.dump(manifest, open(os.path.join(HERE, "ref_big.json"), "w"), indent=1)
+    print(f"ref_big: {len(arrays)} tensors reduced to {sum(a.size for a in arrays.values())} samples")
+
+
 if __name__ == "__main__":
-    pack_layers(sys.argv[1])
-    pack_memory(sys.argv[2])
+    if sys.argv[1] == "--big":
+        pack_big(sys.argv[2])
+    else:
+        pack_layers(sys.argv[1])
+        pack_memory(sys.argv[2])

@@ -51,3 +51,29 @@ def tiny_net(n=4, with_lrn=False):
     L.append((FC_GEMM, n, 32, 1, 1, 0, 0, 0, 0, 10, 1, 1))
     L.append((SOFTMAX, n, 10, 1, 1, 0, 0, 0, 0, 0, 0, 0))
     return L
+
+
+def check_reduced(tensor, samples, meta, tol, what=""):
+    """Compares a full tensor with the reduced fixture of a tensor too large to keep: `samples` are its elements at
+    indices 0, stride, 2*stride, ...; `meta` holds count, stride, sum, sumsq and maxabs over the whole tensor.
+      * every sample within tol of the reference, normalised by the reference tensor's largest magnitude;
+      * the L2 norm within tol (relative);
+      * the sum within tol * sqrt(count * sumsq): what per-element errors of tol * rms can add up to at most."""
+    t = np.asarray(tensor, np.float64).ravel()
+    assert t.size == meta["count"], (what, t.size, meta["count"])
+    got = t[::meta["stride"]][:meta["samples"]]
+    err = float(np.abs(got - samples.astype(np.float64)).max()) / max(meta["maxabs"], 1e-30)
+    assert err < tol, (what, "samples", err)
+    norm, ref_norm = float(np.sqrt((t * t).sum())), float(np.sqrt(meta["sumsq"]))
+    assert abs(norm - ref_norm) <= tol * ref_norm, (what, "norm", norm, ref_norm)
+    assert abs(float(t.sum()) - meta["sum"]) <= tol * np.sqrt(meta["count"] * meta["sumsq"]), (what, "sum", float(t.sum()), meta["sum"])
+    return err
+
+
+def outlier_fraction(a, b, tol=1e-4):
+    """Fraction of elements of `a` further than tol (normalised by max|b|) from `b`."""
+    a = np.asarray(a, np.float64).ravel()
+    b = np.asarray(b, np.float64).ravel()
+    assert a.shape == b.shape, (a.shape, b.shape)
+    denom = max(float(np.abs(b).max()), 1e-30)
+    return float((np.abs(a - b) > tol * denom).mean())

@@ -105,3 +105,53 @@ def test_kernels_reproduce_reference_layer_outputs(vdnn, oracle, engine):
         assert ops.engine_status() == 0
     finally:
         ops.set_engine(vdnn.ENGINE_AUTO)
+
+
+BIG_HAVE = os.path.exists(os.path.join(GOLD, "ref_big.json"))
+BIG = json.load(open(os.path.join(GOLD, "ref_big.json"))) if BIG_HAVE else {"cases": [], "tensors": []}
+BIG_ARR = np.load(os.path.join(GOLD, "ref_big.npz")) if BIG_HAVE else {}
+BIG_META = {t["name"]: t for t in BIG["tensors"]}
+
+
+@pytest.mark.skipif(not BIG_HAVE, reason="tests/golden/ref_big.* not generated")
+@pytest.mark.parametrize("algo_mode", [0, 1])
+@pytest.mark.parametrize("cid", [c["id"] for c in BIG["cases"]])
+def test_kernels_reproduce_reference_at_benchmark_sizes(vdnn, oracle, cid, algo_mode):
+    """Layers at or near the sizes the benchmarked networks run them at (every tile width, split plan and special-case
+    kernel of the tensor-core engine) against what the reference's Layer class computed on cuDNN / cuBLAS: strided
+    samples, L2 norm and sum of every output tensor, in the zero-workspace and the workspace-using mode."""
+    from helpers import check_reduced
+    from test_golden_big import big_inputs
+    ops = vdnn.ops
+    c = next(c for c in BIG["cases"] if c["id"] == cid)
+    x, wt, b, dy = big_inputs(oracle, c)
+    lr = float(np.float32(c["lr"]))
+    xd, wd, bd, dyd = dev(x), dev(wt), dev(b), dev(dy)
+    out = {}
+    if c["kind"] == "conv":
+        n, ch, h, w, k, r, pad, st, P, Q = (c[x_] for x_ in ("n", "c", "h", "w", "k", "r", "pad", "stride", "p", "q"))
+        d = ops.conv_desc(n, ch, h, w, k, r, r, (pad, pad), (st, st))
+        need = max(ops.conv_workspace_bytes(op, algo_mode, d) for op in range(3))
+        ws = torch.empty(max(need, 16) // 4 + 64, device="cuda")
+        tag = f"conv{cid}"
+        yd = torch.empty(n * k * P * Q, device="cuda")
+        ops.conv_fwd(d, xd, wd, yd, bias=bd, algo_mode=algo_mode, workspace=ws, workspace_bytes=need)
+        dxd = torch.empty(n * ch * h * w, device="cuda")
+        ops.conv_bwd_data(d, wd, dyd, dxd, algo_mode=algo_mode, workspace=ws, workspace_bytes=need)
+        wz, bz = torch.zeros(k * ch * r * r, device="cuda"), torch.zeros(k, device="cuda")
+        ops.conv_bwd_filter(d, xd, dyd, wz, alpha=-lr, beta=1.0, algo_mode=algo_mode, workspace=ws, workspace_bytes=need)
+        ops.conv_bwd_bias(n, k, P * Q, dyd, bz, alpha=-lr, beta=1.0)
+    else:
+        n, cin, cout = c["n"], c["cin"], c["cout"]
+        tag = f"fc{cid}"
+        yd = torch.empty(n * cout, device="cuda")
+        ops.sgemm(1, 0, cout, n, cin, 1.0, wd, cin, xd, cin, 0.0, yd, cout)
+        ops.add_bias(n, cout, 1, bd, yd)
+        dxd = torch.empty(n * cin, device="cuda")
+        ops.sgemm(0, 0, cin, n, cout, 1.0, wd, cin, dyd, cout, 0.0, dxd, cin)
+        wz, bz = torch.zeros(cin * cout, device="cuda"), torch.zeros(cout, device="cuda")
+        ops.sgemm(0, 1, cin, cout, n, -lr, xd, cin, dyd, cout, 1.0, wz, cin)
+        ops.conv_bwd_bias(n, cout, 1, dyd, bz, alpha=-lr, beta=1.0)
+    for name, t in (("y", yd), ("dx", dxd), ("wstep", wz), ("bstep", bz)):
+        check_reduced(host(t), BIG_ARR[f"{tag}_{name}"], BIG_META[f"{tag}_{name}"], TOL, f"{tag}_{name} mode {algo_mode}")
+    assert ops.engine_status() == 0

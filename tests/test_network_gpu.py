@@ -246,3 +246,78 @@ def test_held_blocks_are_given_back_under_pool_pressure(vdnn):
         for a, b in zip(other[1], roomy[1]):       # layer 0's bias gradient: 1.6 M terms per channel, summed with atomics
             assert rel_err(a, b) < 2e-3
     assert vdnn.ops.engine_status() == 0
+
+
+@pytest.mark.parametrize("cnn,policy,algo,batch", [
+    ("ALEXNET", "VDNN_ALL", "VDNN_MEMORY_OPT_ALGO", 128),          # BASELINE.json configuration 1 (without / with LRN)
+    ("ALEXNET_LRN", "BASELINE", "VDNN_MEMORY_OPT_ALGO", 128),
+    ("OVERFEAT", "VDNN_CONV", "VDNN_PERF_OPT_ALGO", 128),          # configuration 2
+    ("VGG16_64", "VDNN_ALL", "VDNN_PERF_OPT_ALGO", 8),             # configurations 3-5 at the largest batch the oracle steps in seconds
+    ("VGG16_64", "VDNN_NONE", "VDNN_MEMORY_OPT_ALGO", 8),
+])
+def test_benchmark_configurations_against_oracle(vdnn, oracle, cnn, policy, algo, batch):
+    """One training step of the benchmarked networks at their own batch size (VGG16: batch 8) against the CPU oracle.
+
+    At these sizes a handful of ReLU inputs lie within rounding of zero (see helpers.relu_knife_edges): two correct
+    fp32 implementations may set those mask bits differently, which changes single elements of the gradients below.
+    So activations and the loss are compared in full (tensor-normalised 1e-4, loss 1e-5), and gradients and parameter
+    updates by the fraction of elements outside 1e-4: at most 20 per million, where a wrong tile or a dropped k block
+    would show in far more."""
+    from helpers import outlier_fraction
+    specs = [s.astuple() for s in oracle.model_layers(getattr(oracle, cnn), batch)]
+    lr = 1e-3
+    onet = oracle.Net(specs, lr, init_mode=0)
+    net = vdnn.Network(cnn, policy, algo, batch_size=batch, pool_bytes=12e9, learning_rate=lr, init_mode=0, capture=True)
+    try:
+        x = oracle.fill_normal(net.input_size, 1000)
+        t = oracle.fill_onehot(batch, net.output_size // batch, 2000)
+        before = {l: (net.weights(l), net.bias(l)) for l in range(net.num_layers) if net.tensor_size(l, 2) > 0}
+        onet.set_input(x, t)
+        onet.forward()
+        onet.backward()
+        net.set_input(x, t)
+        net.step()
+        net.synchronize()
+        for l in range(net.num_layers):
+            assert rel_err(net.dst(l), onet.dst(l)) < TOL, ("dst", l)
+        sq, ce = net.loss()
+        osq, oce = onet.loss()
+        assert abs(sq - osq) < 1e-5 * max(1.0, abs(osq)) and abs(ce - oce) < 1e-5 * max(1.0, abs(oce))
+        for l in range(net.num_layers - 1, -1, -1):
+            assert outlier_fraction(net.grad(l), onet.grad(l)) < 2e-5, ("grad", l)
+            if l in before:
+                w0, b0 = before[l]
+                assert outlier_fraction(net.weights(l) - w0, onet.weights(l) - w0) < 2e-5, ("dw", l)
+                assert outlier_fraction(net.bias(l) - b0, onet.bias(l) - b0, 1e-3) < 2e-5 + 1.5 / b0.size, ("db", l)
+        assert vdnn.ops.engine_status() == 0
+    finally:
+        net.close()
+        onet.close()
+
+
+def test_vgg16_256_trains_on_the_gpu(vdnn, oracle):
+    """VGG16 at batch 256 (vdnn.cu:20, network.cu:146-147): tensors of 822 M elements, byte counts beyond 2^31
+    (network.cu:1010-1023 keeps them in an int).  One step under VDNN_ALL: the schedule equals the oracle's
+    simulator, the loss is finite and equals the loss of the same step under VDNN_CONV, and so do the updated parameters."""
+    seen = {}
+    for policy in ("VDNN_ALL", "VDNN_CONV"):
+        net = vdnn.Network("VGG16_256", policy, "VDNN_MEMORY_OPT_ALGO", pool_bytes=40e9, learning_rate=1e-6)
+        try:
+            net.seed_input(1000, 2000)
+            net.step()
+            net.synchronize()
+            seen[policy] = (net.loss(), [net.weights(l) for l in (0, 10, 31, 35)], net.stats(), net.trace())
+            if policy == "VDNN_ALL":
+                specs = [s.astuple() for s in net.layer_specs()]
+                assert specs[1][1:5] == (256, 64, 224, 224)
+                ev, summ = oracle.policy_trace(specs, oracle.VDNN_ALL, fix_input_leak=True)
+                assert seen[policy][3] == ev and seen[policy][2]["pool_peak_bytes"] == summ.peak_bytes
+                assert seen[policy][2]["offload_bytes"] == summ.offload_bytes > 2 ** 34       # 29.5 GB each way
+        finally:
+            net.close()
+    assert vdnn.ops.engine_status() == 0
+    (la, wa, _, _), (lc, wc, _, _) = seen["VDNN_ALL"], seen["VDNN_CONV"]
+    assert np.isfinite(la[0]) and np.isfinite(la[1])
+    assert abs(la[0] - lc[0]) < 1e-6 and abs(la[1] - lc[1]) < 1e-5 * abs(lc[1])
+    for a, b in zip(wa, wc):
+        assert rel_err(a, b) < 1e-5

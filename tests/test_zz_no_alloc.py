@@ -49,6 +49,36 @@ def test_static_scratch_matches_workspace_entry_point_twice(vdnn):
     assert all(np.isfinite(results)) and ops.engine_status() == 0
 
 
+def test_static_scratch_with_packed_operand_images_against_oracle(vdnn, oracle):
+    """Shapes with at least 128 filters also keep the tile images of dy in the scratch array (images first, partial
+    sums behind them), and a filter as large as its input runs as a plain matrix product.  Each case runs right after a
+    call that left other data in the array, is checked against the CPU oracle, and must not change the amount of free
+    device memory: the entry point allocates nothing."""
+    ops = vdnn.ops
+    # make the array dirty first
+    o0, d0, x0, dy0, w0 = _case(vdnn, 8, 32, 28, 32, 7)
+    ops.conv_bwd_filter_static(d0, x0, dy0, w0.clone())
+    torch.cuda.synchronize()
+    for (n, c, h, k, r, pad) in [(4, 64, 14, 128, 3, 1), (2, 32, 12, 256, 3, 1), (256, 64, 6, 48, 6, 0)]:
+        d = ops.conv_desc(n, c, h, h, k, r, r, (pad, pad), (1, 1))
+        assert ops.conv_workspace_bytes(2, 1, d) <= ops.STATIC_SCRATCH_BYTES
+        p = h + 2 * pad - r + 1
+        x = oracle.fill_normal(n * c * h * h, 11).reshape(n, c, h, h)
+        dy = oracle.fill_normal(n * k * p * p, 12).reshape(n, k, p, p)
+        w0 = oracle.fill_normal(k * c * r * r, 13, 0.0, 0.1).reshape(k, c, r, r)
+        want = oracle.conv_bwd_filter(x, dy, w0.shape, (pad, pad), (1, 1), alpha=-0.01, beta=1.0, dw=w0.copy())
+        xd, dyd = torch.from_numpy(x).cuda(), torch.from_numpy(dy).cuda()
+        for rep in range(2):                     # the second call finds the array as the first left it
+            got = torch.from_numpy(w0.copy()).cuda()
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
+            ops.conv_bwd_filter_static(d, xd, dyd, got, alpha=-0.01, beta=1.0)
+            torch.cuda.synchronize()
+            assert torch.cuda.mem_get_info()[0] == free_before, (n, c, h, k, rep)
+            assert rel_err(got.cpu().numpy(), want) < 1e-4, (n, c, h, k, rep)
+    assert ops.engine_status() == 0
+
+
 def test_static_scratch_refuses_what_does_not_fit(vdnn):
     ops = vdnn.ops
     # 512 -> 512 channels at 14x14: few output tiles, many splits, 18 MiB of partial sums, beyond the 16 MiB array

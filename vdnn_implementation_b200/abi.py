@@ -81,6 +81,7 @@ SIGNATURES = {
     "vdnn_engine_status": (_I, [C.POINTER(_I)]),
     "vdnn_engine_status_publish": (_I, [_P, _P]),
     "vdnn_engine_wait_selftest": (_I, [C.c_ulonglong, _P]),
+    "vdnn_engine_mma_rate_probe": (_I, [_I, C.POINTER(C.c_double), _P]),
     "vdnn_conv_out_dims": (_I, [_D, C.POINTER(_I), C.POINTER(_I)]),
     "vdnn_pool_out_dims": (_I, [_I] * 6 + [C.POINTER(_I), C.POINTER(_I)]),
     "vdnn_conv_workspace_bytes": (_Z, [_I, _I, _D]),

@@ -383,6 +383,20 @@ int vdnn_engine_wait_selftest(unsigned long long limit_cycles, void* stream) {
     return VDNN_OK;
 }
 
+int vdnn_engine_mma_rate_probe(int iterations, double* flops, void* stream) {
+    if (iterations <= 0 || iterations > (1 << 24) || !flops) return VDNN_ERR_BAD_ARG;
+    int dev = 0;
+    VDNN_CUDA(cudaGetDevice(&dev));
+    constexpr int smem = 200 * 1024;            // more than half an SM's shared memory: one CTA per SM
+    if (VDNN_ONCE_PER_DEVICE(dev))
+        VDNN_CUDA(cudaFuncSetAttribute(tc::mma_rate_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    const int ctas = sm_count();
+    tc::mma_rate_probe_kernel<<<ctas, 128, smem, as_stream(stream)>>>(iterations);
+    VDNN_LAUNCHED();
+    *flops = 2.0 * 128 * 256 * 8 * 12 * static_cast<double>(iterations) * ctas;
+    return VDNN_OK;
+}
+
 int vdnn_conv_out_dims(const vdnn_conv_desc* d, int* p, int* q) {
     int P, Q;
     if (!p || !q || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;

@@ -450,6 +450,50 @@ __global__ void wait_probe_kernel(unsigned long long cycles) {
     if (threadIdx.x == 0 && !mbar_wait_for(smem_u32(&bar), 0u, cycles, 1u << 20)) atomicCAS(&g_tc_error, 0, 104);
 }
 
+// Tensor-pipe rate probe: every CTA (one per SM, 227 KB of shared memory so that no second one fits) issues
+// `iterations` groups of 12 tcgen05.mma kind::tf32 128 x 256 x 8 on whatever its shared memory holds, with no loads
+// and no epilogue, and waits (bounded) for the last commit.  2 * 128 * 256 * 8 * 12 * iterations * CTAs flops over the
+// kernel's duration is what the tensor pipe sustains when nothing else limits it: the ceiling the contraction
+// kernels are measured against (a product that is exact to fp32 costs three of these MMAs).
+__global__ void __launch_bounds__(128, 1) mma_rate_probe_kernel(int iterations) {
+    extern __shared__ char smem_raw[];
+    char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tmem_slot;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // operands: finite values (zeros) so that no NaN handling path is involved
+    for (int i = threadIdx.x; i < (16384 + 32768) / 16; i += blockDim.x) reinterpret_cast<float4*>(tiles)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(256) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+    if (warp == 1 && lane == 0) {
+        const uint32_t a = smem_u32(tiles), b = a + 16384;
+        for (int it = 0; it < iterations; ++it) {
+#pragma unroll
+            for (int j = 0; j < 12; ++j)
+                mma_tf32(tmem_base, make_desc(a + (j & 3) * 32), make_desc(b + (j & 3) * 32), Config<256>::IDESC, (it | j) ? 1u : 0u);
+        }
+        mma_commit(smem_u32(&bar));
+        if (!mbar_wait(smem_u32(&bar), 0u)) atomicCAS(&g_tc_error, 0, 105);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256) : "memory");
+    }
+}
+
 // Copies the error word to *dst (device memory or mapped pinned host memory) in stream order, without clearing it.
 __global__ void publish_error_kernel(int* dst) { *dst = g_tc_error; }
 

@@ -86,6 +86,42 @@ int vdnnContext::upload(void* dst, const void* src_h, size_t bytes) {
     return cudaMemcpy(dst, src_h, bytes, cudaMemcpyHostToDevice) == cudaSuccess ? VDNN_OK : VDNN_ERR_CUDA;
 }
 
+/* ------------------------------------------------------------------ handle shims for a foreign driver */
+
+int vdnnCreate(vdnnHandle_t* handle) {
+    static vdnnContext shared;              // one per process, like the pool
+    if (!handle) return VDNN_ERR_BAD_ARG;
+    *handle = &shared;
+    return VDNN_OK;
+}
+
+int vdnnSetStream(vdnnHandle_t handle, cudaStream_t stream_compute) {
+    if (!handle) return VDNN_ERR_BAD_ARG;
+    handle->stream_compute = stream_compute;
+    if (!handle->ev_fwd_done.empty()) return VDNN_OK;
+    auto make = [&](std::vector<cudaEvent_t>& v) {
+        v.assign(DEFAULT_NUM_LAYER, NULL);
+        for (auto& e : v) if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return false;
+        return true;
+    };
+    if (!make(handle->ev_fwd_done) || !make(handle->ev_bwd_done) || !make(handle->ev_offload_done) ||
+        !make(handle->ev_prefetch_done) || !make(handle->ev_weights_ready) ||
+        cudaEventCreateWithFlags(&handle->ev_input_ready, cudaEventDisableTiming) != cudaSuccess)
+        return VDNN_ERR_CUDA;
+    handle->weights_pending.assign(DEFAULT_NUM_LAYER, 0);
+    return VDNN_OK;
+}
+
+int vdnnDestroy(vdnnHandle_t handle) {
+    if (!handle) return VDNN_ERR_BAD_ARG;
+    auto drop = [](std::vector<cudaEvent_t>& v) { for (auto e : v) if (e) cudaEventDestroy(e); v.clear(); };
+    drop(handle->ev_fwd_done); drop(handle->ev_bwd_done); drop(handle->ev_offload_done);
+    drop(handle->ev_prefetch_done); drop(handle->ev_weights_ready);
+    for (auto& v : handle->ev_offload_chunk) drop(v);
+    if (handle->ev_input_ready) { cudaEventDestroy(handle->ev_input_ready); handle->ev_input_ready = NULL; }
+    return VDNN_OK;
+}
+
 /* ------------------------------------------------------------------ construction (layer.cu:40-485) */
 
 static const char* type_name(Layer_t t) {
@@ -110,6 +146,13 @@ Layer::Layer(vdnn_t _vdnnMode, vdnnAlgoMode_t _vdnnAlgoMode, Layer_t _layerType,
       srcData(NULL), filterData(NULL), biasData(NULL), dstData(NULL), diffData(NULL), gradData(NULL),
       gradFilter(NULL), gradBias(NULL) {
     opMode[0] = opMode[1] = opMode[2] = VDNN_ALGO_MEMORY_OPT;
+    // A context that was not set up by this library's Network (the reference's driver creating layers through
+    // the handle shims) copies on the one memory stream the reference has, in both directions.
+    if (!handle->dry_run && _stream_memory && *_stream_memory) {
+        if (!handle->stream_d2h) handle->stream_d2h = *_stream_memory;
+        if (!handle->stream_h2d) handle->stream_h2d = *_stream_memory;
+    }
+    if (!handle->stream_compute && _stream_compute) handle->stream_compute = *_stream_compute;
     switch (layerType) {
     case FC_GEMM:
         if (!(h_in == 1 && w_in == 1 && r == 1 && s == 1)) { fprintf(stderr, "Invalid dimensions!\n"); return; }
@@ -252,6 +295,22 @@ int Layer::backward(int _layer_id_to_prefetch, DATATYPE* _prefetchedSrcData_h, v
     if (handle->profiling) CU(cudaEventRecord(handle->pf_bwd_beg[layerId], *stream_compute));
 #define MARK(ev) CU(cudaEventRecord(handle->ev[layerId], *stream_compute))
 
+// layer.cu:1091-1147: per operation the fastest algorithm whose workspace can be had from the pool right now.  Here
+// that is the workspace-using algorithm when its workspace can be allocated at this moment, else the zero-workspace one.
+int Layer::findDynamicAlgo() {
+    if (layerType != CONV && layerType != FC_CONV) return 0;
+    const vdnn_conv_desc d = convDesc();
+    bool use[3];
+    for (int op = 0; op < 3; ++op) {
+        const size_t need = vdnn_conv_workspace_bytes(op, VDNN_ALGO_PERF_OPT, &d);
+        void* probe = NULL;
+        use[op] = need == 0 || cnmemMalloc(&probe, need, NULL) == CNMEM_STATUS_SUCCESS;
+        if (probe) cnmemFree(probe, NULL);
+    }
+    setOpAlgos(use);
+    return 0;
+}
+
 void Layer::setOpAlgos(const bool use[3]) {
     for (int op = 0; op < 3; ++op) opMode[op] = use[op] ? VDNN_ALGO_PERF_OPT : VDNN_ALGO_MEMORY_OPT;
     if (layerType != CONV && layerType != FC_CONV) return;
@@ -262,6 +321,14 @@ void Layer::setOpAlgos(const bool use[3]) {
 }
 
 /* ------------------------------------------------------------------ CONV (layer.cu:539-665) */
+
+// Bytes behind a workspace pointer the caller owns (BASELINE's shared block): what the driver announced, else
+// what the pool says the block holds.  The C ABI checks its needs against this figure.
+static size_t caller_workspace_bytes(vdnnContext* ctx, const void* workSpace) {
+    if (ctx->shared_workspace_bytes) return ctx->shared_workspace_bytes;
+    size_t bytes = 0;
+    return vdnnPoolBlockBytes(workSpace, &bytes) == CNMEM_STATUS_SUCCESS ? bytes : 0;
+}
 
 int Layer::convolutionForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, void* workSpace, bool isDynamic) {
     void* curWorkSpace = NULL;
@@ -276,7 +343,7 @@ int Layer::convolutionForward(bool* _offloaded, DATATYPE** _offloadedSrcData_h, 
     // convolution and bias in one pass (the reference: cudnnConvolutionForward + cudnnAddTensor)
     // a caller-owned (BASELINE: shared) block is announced with its own size, so that the size check of the ABI is real
     DEV(vdnn_conv_fwd(&d, mode, 1.0f, (const float*)srcData, (const float*)filterData, (const float*)biasData, 0.0f,
-                      (float*)dstData, curWorkSpace, workSpace != NULL ? handle->shared_workspace_bytes : fwdWorkSpaceSize,
+                      (float*)dstData, curWorkSpace, workSpace != NULL ? caller_workspace_bytes(handle, workSpace) : fwdWorkSpaceSize,
                       *stream_compute));
     if (_offloaded[layerId]) { const int o = offloadSrcData(_offloaded, _offloadedSrcData_h); if (o != 0) return o; }
     MARK(ev_fwd_done);
@@ -300,7 +367,7 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
     }
     // data gradient with the weights as they were in forward
     DEV(vdnn_conv_bwd_data(&d, opMode[1], 1.0f, (const float*)filterData, (const float*)diffData, 0.0f, (float*)gradData,
-                           curWorkSpace, workSpace != NULL ? handle->shared_workspace_bytes : bwdDataWorkSpaceSize,
+                           curWorkSpace, workSpace != NULL ? caller_workspace_bytes(handle, workSpace) : bwdDataWorkSpaceSize,
                            *stream_compute));
     if (workSpace == NULL && bwdDataWorkSpaceSize > 0) {
         MARK(ev_bwd_done);
@@ -318,7 +385,7 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
     }
     DEV(vdnn_conv_bwd_filter(&d, opMode[2], staged ? 1.0f : lr, (const float*)srcData, (const float*)diffData,
                              staged ? 0.0f : 1.0f, staged ? gradFilter : (float*)filterData, curWorkSpace,
-                             workSpace != NULL ? handle->shared_workspace_bytes : bwdFilterWorkSpaceSize, *stream_compute));
+                             workSpace != NULL ? caller_workspace_bytes(handle, workSpace) : bwdFilterWorkSpaceSize, *stream_compute));
     MARK(ev_bwd_done);
     if (workSpace == NULL && bwdFilterWorkSpaceSize > 0)
         return handle->release(curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, {*stream_compute});

@@ -94,6 +94,14 @@ struct vdnnContext {
 };
 typedef vdnnContext* vdnnHandle_t;
 
+/* Handle life cycle for a driver that is not this library's Network: the calls the reference makes on its cuDNN /
+   cuBLAS handles (network.cu:39-40, 56-57, 96-97).  vdnnCreate hands out the process-wide context (every "handle"
+   is the same object, as all layers of the reference share its two handles); vdnnSetStream names the compute stream
+   and creates the per-layer events the layers record. */
+int vdnnCreate(vdnnHandle_t* handle);
+int vdnnSetStream(vdnnHandle_t handle, cudaStream_t stream_compute);
+int vdnnDestroy(vdnnHandle_t handle);
+
 enum {
     TAG_WEIGHT = 0, TAG_BIAS = 1, TAG_DST = 2, TAG_DIFF = 3, TAG_GRAD = 4, TAG_SRC = 5, TAG_WS = 6,
     TAG_ONES = 7, TAG_INPUT = 8, TAG_LABEL = 9, TAG_DXDY = 10, TAG_NONE = 11
@@ -184,6 +192,7 @@ public:
     /* VDNN_DYNAMIC_ALGO (layer.cu:1091-1147): per operation, the workspace-using algorithm when `use[op]`
        is set, else the zero-workspace one; op = 0 forward, 1 data gradient, 2 filter gradient. */
     void    setOpAlgos(const bool use[3]);
+    int     findDynamicAlgo();
     void    opAlgos(int out[3]) const { out[0] = opMode[0]; out[1] = opMode[1]; out[2] = opMode[2]; }
     void    printDstData();
     void    printFilterData();

@@ -387,6 +387,16 @@ cnmemStatus_t vdnnPoolInitVirtual(size_t size) {
     return CNMEM_STATUS_SUCCESS;
 }
 
+cnmemStatus_t vdnnPoolBlockBytes(const void* ptr, size_t* bytes) {
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
+    if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
+    if (!ptr || !bytes) return CNMEM_STATUS_INVALID_ARGUMENT;
+    auto it = g_pool.blocks.find(static_cast<size_t>(static_cast<const char*>(ptr) - g_pool.base));
+    if (it == g_pool.blocks.end() || it->second.free) return CNMEM_STATUS_INVALID_ARGUMENT;
+    *bytes = it->second.size;
+    return CNMEM_STATUS_SUCCESS;
+}
+
 int vdnnPoolIsInitialized(void) {
     std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     return g_pool.ready ? 1 : 0;

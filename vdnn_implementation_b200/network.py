@@ -186,3 +186,61 @@ def _host_ptr(a, expect):
     # torch CPU tensor (possibly pinned)
     assert a.device.type == "cpu" and a.is_contiguous() and a.numel() == expect and a.element_size() == 4
     return C.c_void_p(a.data_ptr())
+
+
+def dp_consistency_check(model, policy, per_rank, steps, lr, dist, local_device, algo="VDNN_PERF_OPT_ALGO", pool_bytes=8e9):
+    """Data-parallel training against one GPU on the whole batch (call on every rank of an initialised NCCL group).
+
+    Every rank trains its shard of `steps` seeded batches with the per-layer gradient all-reduce; then rank 0 repeats
+    the same steps alone on the whole batches.  Gradients are batch sums (layer.cu:631-660, 736-760 of the reference
+    fold alpha = -lr sums into the weights), so the sum over the shards' gradients is the whole batch's gradient and
+    the two runs must agree to rounding.  Returns on rank 0 a dict with `checksums` (one per rank; equal = weights
+    bit-identical across ranks), `max_rel_err_vs_single_gpu`, `grad_buffer_bytes`, `engine_status`; None elsewhere."""
+    import torch
+    from . import ops
+    rank, world = dist.get_rank(), dist.get_world_size()
+    L = lib()
+    net = Network(model, policy, algo, batch_size=per_rank, device=local_device, pool_bytes=pool_bytes, learning_rate=lr, init_mode=0)
+    uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+    if rank == 0:
+        uid.copy_(torch.frombuffer(bytearray(dp_unique_id()), dtype=torch.uint8))
+    dist.broadcast(uid, 0)
+    net.enable_dp(rank, world, uid.cpu().numpy().tobytes())
+    in_per_image, classes = net.input_size // per_rank, net.output_size // per_rank
+    data = []
+    for step in range(steps):
+        x = np.empty(world * per_rank * in_per_image, np.float32)
+        t = np.empty((world * per_rank, classes), np.float32)
+        L.vdnn_host_fill_normal(x.ctypes.data_as(C.c_void_p), x.size, 1000 + step, 0.0, 1.0)
+        L.vdnn_host_fill_onehot(t.ctypes.data_as(C.c_void_p), world * per_rank, classes, 2000 + step)
+        data.append((x.reshape(world, -1), t.reshape(world, -1)))
+    for x, t in data:
+        net.set_input(np.ascontiguousarray(x[rank]), np.ascontiguousarray(t[rank]))
+        net.step()
+    net.synchronize()
+    sums = [None] * world
+    dist.all_gather_object(sums, net.weight_checksum())
+    stats = net.stats()
+    with_weights = [l for l in range(net.num_layers) if net.tensor_size(l, abi.TENSOR_WEIGHT) > 0]
+    probe = (with_weights[0], with_weights[len(with_weights) // 2], with_weights[-1])
+    dp_weights = {l: net.weights(l) for l in probe}
+    dp_bias = {l: net.bias(l) for l in probe}
+    status = ops.engine_status()
+    net.close()
+    result = None
+    if rank == 0:
+        one = Network(model, policy, algo, batch_size=per_rank * world, device=local_device, pool_bytes=pool_bytes,
+                      learning_rate=lr, init_mode=0)
+        for x, t in data:
+            one.set_input(np.ascontiguousarray(x.ravel()), np.ascontiguousarray(t.ravel()))
+            one.step()
+        one.synchronize()
+        errs = []
+        for l in probe:
+            for a, b in ((dp_weights[l], one.weights(l)), (dp_bias[l], one.bias(l))):
+                errs.append(float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30)))
+        one.close()
+        result = {"checksums": [str(s) for s in sums], "grad_buffer_bytes": stats["grad_buffer_bytes"], "engine_status": status,
+                  "max_rel_err_vs_single_gpu": max(errs)}
+    dist.barrier()
+    return result

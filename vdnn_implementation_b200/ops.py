@@ -157,3 +157,10 @@ def engine_wait_selftest(limit_cycles=2_000_000, stream=0):
     """Runs the engine's bounded barrier wait on a barrier nothing arrives at: it runs out after `limit_cycles` SM
     cycles, records code 104 and the kernel returns.  engine_status() then reports (and clears) 104."""
     check(lib().vdnn_engine_wait_selftest(limit_cycles, _s(stream)), "engine_wait_selftest")
+
+
+def engine_mma_rate_probe(iterations, stream=0):
+    """Enqueues the tensor-pipe rate probe; returns the hardware flops of the launch (time it with events)."""
+    flops = C.c_double()
+    check(lib().vdnn_engine_mma_rate_probe(iterations, C.byref(flops), _s(stream)), "engine_mma_rate_probe")
+    return flops.value
