@@ -215,11 +215,12 @@ def _perf_workspaces(vdnn, specs):
     return ws
 
 
-@pytest.mark.parametrize("pool_gb,expect", [(40, (1, 1)), (13.5, (3, 1)), (10.5, (2, 1)), (5, None)])
+@pytest.mark.parametrize("pool_gb,expect", [(40, (1, 1)), (14.5, (3, 1)), (11, (2, 1)), (5, None)])
 def test_dynamic_algo_picks_the_first_policy_that_fits(vdnn, oracle, pool_gb, expect):
     """VDNN_DYNAMIC_ALGO (network.cu:946-1008): NONE, then CONV, then ALL with the workspace-using algorithms;
     a model that does not even fit under VDNN_ALL with zero workspace is refused.  Pool sizes are chosen away
-    from the boundaries (peaks 15.4 / 11.2 / 8.9 GB), where peak bytes and a real allocator agree."""
+    from the boundaries (peaks 15.6 / 11.8 / 9.2 GB with the workspace-using algorithms), where peak bytes and a real
+    allocator agree."""
     specs = [s.astuple() for s in oracle.model_layers(oracle.VGG16_128, 128)]
     assert oracle.dynamic_choice(specs, pool_gb * 1e9, _perf_workspaces(vdnn, specs)) == expect
     if expect is None:
@@ -253,7 +254,7 @@ def test_dynamic_algo_per_layer(vdnn, oracle):
     ws = _perf_workspaces(vdnn, specs)
     assert ws[0][0] > 8e6 and ws[2][0] > 4e6
     picks = {}
-    for pool in (3_500_000, 4_496_896, 8_611_840, 16_000_000):
+    for pool in (3_500_000, 4_496_896, 9_000_000, 16_000_000):
         assert (oracle.dynamic_choice(specs, pool, ws) is None) == (pool == 3_500_000)
         try:
             net = vdnn.Network("CUSTOM_CNN", "VDNN_NONE", "VDNN_DYNAMIC_ALGO", device=-1, pool_bytes=pool, custom_layers=specs)
@@ -268,7 +269,7 @@ def test_dynamic_algo_per_layer(vdnn, oracle):
             net.close()
     assert picks[3_500_000] == -5                                         # not even VDNN_ALL with zero workspace
     assert picks[4_496_896] == ((2, 2), (0, 0, 0), (0, 0, 0))             # VDNN_ALL, no room for any workspace
-    assert picks[8_611_840] == ((2, 2), (0, 0, 1), (1, 1, 1))             # room for the second layer's 4.2 MB (and 0.3 MB of dy tiles)
+    assert picks[9_000_000] == ((2, 2), (0, 0, 1), (1, 1, 1))             # room for the second layer's 4.2 MB (and 0.3 MB of dy tiles)
     assert picks[16_000_000] == ((1, 1), (1, 1, 1), (1, 1, 1))            # everything fits without offloading
 
 

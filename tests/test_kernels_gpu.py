@@ -38,6 +38,16 @@ CONV_CASES = [  # n, c, h, w, k, r, pad, stride
     (2, 2, 12, 12, 5, 3, 1, 2),
     (2, 4, 11, 11, 6, 3, 0, 3),
     (1, 3, 70, 150, 9, 3, 1, 1),       # wider than one 128-column tile of that kernel
+    # stride 1 with reduction channels in whole blocks of 32: in PERF_OPT forward and data gradient fetch their operand by
+    # tensor copies from channels-last images (boxes of 32 pixels, zero fill outside the image)
+    (2, 32, 14, 14, 40, 3, 1, 1),      # 14 x 14 grid under 16 x 2 boxes: overhang on both edges, 40 of 64 columns used
+    (3, 64, 13, 13, 96, 5, 2, 1),      # 5 x 5 taps, padding 2, odd grid
+    (2, 96, 12, 12, 32, 5, 0, 1),      # no padding: the output grid (8 x 8) is smaller than the image
+    (1, 256, 9, 30, 288, 3, 1, 1),     # 256-column tile plus a ragged second one, wide rows
+    (2, 32, 10, 10, 64, 1, 0, 1),      # 1 x 1 filter
+    (5, 32, 7, 7, 32, 3, 2, 1),        # padding beyond the filter radius: the output grid (9 x 9) is larger than the image
+    (2, 512, 6, 6, 64, 3, 1, 1),       # one output tile, 4608-long reduction: split along k with partial sums
+    (9, 64, 40, 24, 64, 3, 1, 1),      # many tiles of 64 columns, tiles that straddle images
 ]
 ENGINES = ["ffma", "tcgen05"]
 

@@ -78,7 +78,7 @@ def test_dynamic_algo_trains_with_mixed_algorithms(vdnn, oracle):
     layer 0 runs its zero-workspace kernels, layer 2 the workspace-using ones, and the step equals the oracle's."""
     from test_host_logic import workspace_heavy_net
     specs = workspace_heavy_net()
-    _run(vdnn, oracle, specs, "CUSTOM_CNN", "BASELINE", "VDNN_DYNAMIC_ALGO", 2, 0.01, pool_bytes=8_611_840, expect_selected=(2, 2))
+    _run(vdnn, oracle, specs, "CUSTOM_CNN", "BASELINE", "VDNN_DYNAMIC_ALGO", 2, 0.01, pool_bytes=9_000_000, expect_selected=(2, 2))
     # and with room for everything the first candidate (VDNN_NONE, workspace-using algorithms) is taken
     _run(vdnn, oracle, specs, "CUSTOM_CNN", "BASELINE", "VDNN_DYNAMIC_ALGO", 2, 0.01, pool_bytes=64e6, expect_selected=(1, 1))
 

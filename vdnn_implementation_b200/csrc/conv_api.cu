@@ -8,11 +8,16 @@
 #include "common.cuh"
 #include "gemm_ffma.cuh"
 #include "gemm_tc.cuh"
+#include "conv_tma.cuh"
 
 namespace vdnn {
 namespace {
 
 int g_engine = VDNN_ENGINE_AUTO;
+// VDNN_NO_TMA=1 in the environment keeps PERF_OPT forward / data gradient on the gather-fed kernel (A/B measurements).
+const bool g_no_tma = []() { const char* v = getenv("VDNN_NO_TMA"); return v && *v && *v != '0'; }();
+// VDNN_TMA_WGRAD=1: the PERF_OPT filter gradient of eligible layers also runs on the TMA-fed engine.
+const bool g_tma_wgrad = []() { const char* v = getenv("VDNN_TMA_WGRAD"); return v && *v && *v != '0'; }();
 
 struct SplitPlan { int splits; int k_chunk; };
 
@@ -259,6 +264,37 @@ size_t packed_dy_bytes(const vdnn_conv_desc* d, int P, int Q) {
     return d->k >= 128 ? tc::bulk_bytes(d->k, d->n * P * Q) : 0;
 }
 
+// Forward and data gradient of a stride-1 convolution whose reduction channels (C for forward, K for the data
+// gradient) come in whole blocks of 32 run on the TMA-fed engine in PERF_OPT: the gathered tensor is rewritten once into
+// two channels-last images (tf32 hi / lo halves) in workspace and the kernel fetches its operand tiles by tensor copies.
+bool tma_shape(const vdnn_conv_desc* d, int op) {
+    if (op != VDNN_CONV_FWD && op != VDNN_CONV_BWD_DATA) return false;
+    if (d->stride_h != 1 || d->stride_w != 1 || is_full_extent(d)) return false;
+    if (op == VDNN_CONV_BWD_DATA && d->c <= SMALL_C_MAX) return false;          // the first layer has its own kernels
+    return (op == VDNN_CONV_FWD ? d->c : d->k) % 32 == 0;
+}
+
+bool tma_wgrad_shape(const vdnn_conv_desc* d) {
+    return g_tma_wgrad && !g_no_tma && d->stride_h == 1 && d->stride_w == 1 && !is_full_extent(d) && d->c % 32 == 0 && d->k % 32 == 0;
+}
+
+tma::WgradProblem wgrad_problem(const vdnn_conv_desc* d, int P, int Q) {
+    return tma::WgradProblem{d->n, d->c, d->h, d->w, d->k, P, Q, d->r, d->s, d->pad_h, d->pad_w};
+}
+
+// Operand images of at most this many bytes are kept in workspace at a time.
+constexpr size_t TMA_IMAGE_BUDGET = static_cast<size_t>(384) << 20;
+int tma_slab_images(int n, size_t bytes_per_image) {
+    if (bytes_per_image * n <= TMA_IMAGE_BUDGET) return n;
+    const size_t fit = TMA_IMAGE_BUDGET / bytes_per_image;
+    return fit > 1 ? static_cast<int>(fit) : 1;
+}
+
+size_t tma_image_bytes(const vdnn_conv_desc* d, int op, int P, int Q) {
+    const size_t one = op == VDNN_CONV_FWD ? tma::image_bytes(1, d->c, d->h, d->w) : tma::image_bytes(1, d->k, P, Q);
+    return one * tma_slab_images(d->n, one);
+}
+
 int stream_blocks(size_t n) {
     size_t want = ceil_div<size_t>(n, 256);
     const size_t cap = static_cast<size_t>(sm_count()) * 8;
@@ -317,6 +353,65 @@ int contract(const OpA& a, const OpB& b, Epilogue epi, int M, int N, int K, size
     }
     epi.mode = EPI_ATOMIC;
     return run_engine<OpA, OpB, AKC, BKC>(a, b, epi, M, N, K, plan.splits, plan.k_chunk, stream, b_tiles);
+}
+
+// The TMA-fed contraction with the split handling of contract(): `ws` holds the images, then the per-split partials.
+// Layers whose images would pass TMA_IMAGE_BUDGET are walked in slabs of whole images (transform a slab, contract it,
+// reuse the image buffer), so the workspace stays at the budget whatever the batch size.
+int contract_tma(const tma::Problem& q, const float* src, const char* b_tiles, Epilogue epi, size_t out_elems, char* ws,
+                 size_t ws_bytes, cudaStream_t stream) {
+    const int slab = tma_slab_images(q.n, tma::image_bytes(1, q.cin, q.in_h, q.in_w));
+    const size_t img = tma::image_bytes(slab, q.cin, q.in_h, q.in_w);
+    if (ws_bytes < img) return VDNN_ERR_WORKSPACE;
+    const int M = q.n * q.out_h * q.out_w, K = q.R * q.S * q.cin;
+    SplitPlan plan = plan_split(M, q.n_cols, K);
+    if (epi.bias || slab < q.n) { plan.splits = 1; plan.k_chunk = K; }
+    if (plan.splits == 1) {
+        const size_t src_img = static_cast<size_t>(q.cin) * q.in_h * q.in_w, out_img = static_cast<size_t>(q.n_cols) * q.out_h * q.out_w;
+        for (int n0 = 0; n0 < q.n; n0 += slab) {
+            tma::Problem part = q;
+            part.n = min(slab, q.n - n0);
+            const int st = tma::launch(part, src + n0 * src_img, ws, b_tiles, epi.out + n0 * out_img, epi.bias, epi.alpha, epi.beta,
+                                       EPI_DIRECT, 0, 1, plan.k_chunk, stream);
+            if (st != VDNN_OK) return st;
+        }
+        return VDNN_OK;
+    }
+    const size_t need = static_cast<size_t>(plan.splits) * out_elems * sizeof(float);
+    if (ws_bytes - img < need) return VDNN_ERR_WORKSPACE;
+    float* partial = reinterpret_cast<float*>(ws + img);
+    const int st = tma::launch(q, src, ws, b_tiles, partial, nullptr, 1.0f, 0.0f, EPI_PARTIAL, out_elems, plan.splits, plan.k_chunk, stream);
+    if (st != VDNN_OK) return st;
+    reduce_partials_kernel<<<stream_blocks(out_elems), 256, 0, stream>>>(out_elems, plan.splits, epi.alpha, epi.beta, partial, epi.out);
+    VDNN_LAUNCHED();
+    return VDNN_OK;
+}
+
+// Filter gradient on the TMA-fed engine, in slabs of whole images where the four operand images would pass the budget:
+// every slab adds its pixels' share, dw = alpha * (sum over slabs) + beta * dw.
+int wgrad_tma(const tma::WgradProblem& q, const float* x, const float* dy, char* ws, size_t ws_bytes, float* dw, float alpha,
+              float beta, cudaStream_t stream) {
+    tma::WgradProblem one = q;
+    one.n = 1;
+    const int slab = tma_slab_images(q.n, tma::wgrad_image_bytes(one));
+    tma::WgradProblem part = q;
+    part.n = slab;
+    if (ws_bytes < tma::wgrad_image_bytes(part) + tma::wgrad_partial_bytes(part)) return VDNN_ERR_WORKSPACE;
+    const size_t x_img = static_cast<size_t>(q.c) * q.h * q.w, dy_img = static_cast<size_t>(q.k) * q.p * q.q;
+    const size_t elems = static_cast<size_t>(q.k) * q.c * q.R * q.S;
+    for (int n0 = 0; n0 < q.n; n0 += slab) {
+        part.n = min(slab, q.n - n0);
+        int splits = 1;
+        float* partial = nullptr;
+        const float b = n0 == 0 ? beta : 1.0f;
+        const int st = tma::wgrad_launch(part, x + n0 * x_img, dy + n0 * dy_img, ws, dw, alpha, b, stream, &splits, &partial);
+        if (st != VDNN_OK) return st;
+        if (splits > 1) {
+            reduce_partials_kernel<<<stream_blocks(elems), 256, 0, stream>>>(elems, splits, alpha, b, partial, dw);
+            VDNN_LAUNCHED();
+        }
+    }
+    return VDNN_OK;
 }
 
 bool valid_desc(const vdnn_conv_desc* d, int* P, int* Q) {
@@ -410,6 +505,12 @@ size_t vdnn_conv_workspace_bytes(int op, int algo_mode, const vdnn_conv_desc* d)
     int M, N, K;
     size_t out;
     const int crs = d->c * d->r * d->s;
+    if (op == VDNN_CONV_BWD_FILTER && tma_wgrad_shape(d)) {
+        tma::WgradProblem q = wgrad_problem(d, P, Q);
+        q.n = 1;
+        q.n = tma_slab_images(d->n, tma::wgrad_image_bytes(q));
+        return tma::wgrad_image_bytes(q) + tma::wgrad_partial_bytes(q);
+    }
     if (is_full_extent(d)) {        // runs as the corresponding FC product
         switch (op) {
         case VDNN_CONV_FWD: return vdnn_sgemm_workspace_bytes(algo_mode, d->k, d->n, crs);
@@ -428,6 +529,7 @@ size_t vdnn_conv_workspace_bytes(int op, int algo_mode, const vdnn_conv_desc* d)
     size_t bytes = plan.splits > 1 ? static_cast<size_t>(plan.splits) * out * sizeof(float) : 0;
     if (op == VDNN_CONV_FWD || op == VDNN_CONV_BWD_DATA) bytes += packed_weight_bytes(d, op);
     else bytes += packed_dy_bytes(d, P, Q);
+    if (tma_shape(d, op)) bytes += tma_image_bytes(d, op, P, Q);
     return bytes;
 }
 
@@ -456,6 +558,12 @@ int vdnn_conv_fwd(const vdnn_conv_desc* d, int algo_mode, float alpha, const flo
         SplitDense B = make_dense(w, d->k, crs, crs, 1);
         B.col_div = FastDiv(d->c); B.col_hi = 1; B.col_lo = rs;
         char* tiles = (g_engine != VDNN_ENGINE_FFMA && (reinterpret_cast<uintptr_t>(workspace) & 127u) == 0) ? static_cast<char*>(workspace) : nullptr;
+        if (tiles && tma_shape(d, VDNN_CONV_FWD) && !g_no_tma) {
+            int st = tc::pack_b<SplitDense, true>(B, d->k, crs, s, tiles);
+            if (st != VDNN_OK) return st;
+            tma::Problem q{d->n, d->c, d->h, d->w, P, Q, d->k, d->r, d->s, 1, -d->pad_h, -d->pad_w};
+            return contract_tma(q, x, tiles, e, static_cast<size_t>(M) * d->k, tiles + pack, workspace_bytes - pack, s);
+        }
         return contract<XGatherPixRowsTap, SplitDense, false, true>(A, B, e, M, d->k, crs, static_cast<size_t>(M) * d->k, 0, algo_mode,
                                                                     static_cast<char*>(workspace) + pack, workspace_bytes - pack, s, tiles);
     }
@@ -521,6 +629,13 @@ int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, cons
         const size_t pack = packed_weight_bytes(d, VDNN_CONV_BWD_DATA);
         if (!workspace || workspace_bytes < pack) return VDNN_ERR_WORKSPACE;
         char* tiles = (g_engine != VDNN_ENGINE_FFMA && (reinterpret_cast<uintptr_t>(workspace) & 127u) == 0) ? static_cast<char*>(workspace) : nullptr;
+        if (tiles && tma_shape(d, VDNN_CONV_BWD_DATA) && !g_no_tma) {
+            int st = tc::pack_b<SplitDense, false>(B, d->c, d->k * rs, s, tiles);
+            if (st != VDNN_OK) return st;
+            // dx[h][w] = sum over taps of dy[h + pad - r][w + pad - s] (stride 1)
+            tma::Problem q{d->n, d->k, P, Q, d->h, d->w, d->c, d->r, d->s, -1, d->pad_h, d->pad_w};
+            return contract_tma(q, dy, tiles, e, static_cast<size_t>(M) * d->c, tiles + pack, workspace_bytes - pack, s);
+        }
         return contract<DyGather, SplitDense, false, false>(A, B, e, M, d->c, d->k * rs, static_cast<size_t>(M) * d->c, 0, algo_mode,
                                                             static_cast<char*>(workspace) + pack, workspace_bytes - pack, s, tiles);
     }
@@ -550,6 +665,11 @@ int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, co
     Epilogue e{};
     e.out = dw; e.bias = nullptr; e.alpha = alpha; e.beta = beta;
     e.row_div = FastDiv(1u << 30); e.row_hi = 0; e.row_lo = 1; e.col_stride = crs;
+    if (algo_mode == VDNN_ALGO_PERF_OPT && tma_wgrad_shape(d) && g_engine != VDNN_ENGINE_FFMA && workspace &&
+        (reinterpret_cast<uintptr_t>(workspace) & 127u) == 0) {
+        // both operands as channels-last tf32 hi / lo images, fetched by tensor copies (conv_tma.cuh)
+        return wgrad_tma(wgrad_problem(d, P, Q), x, dy, static_cast<char*>(workspace), workspace_bytes, dw, alpha, beta, as_stream(stream));
+    }
     if (algo_mode == VDNN_ALGO_PERF_OPT) {
         // workspace variant: dy, which every row tile of the gathered input needs again, is split into tf32 halves and
         // laid out as tile images once; the kernel's producers then gather x only

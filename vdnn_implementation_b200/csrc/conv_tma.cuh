@@ -1,0 +1,680 @@
+// TMA-fed convolution engine for sm_100a (PERF_OPT forward and data gradient of stride-1 convolutions whose
+// reduction channel count is a multiple of 32).
+//
+// The gathered operand is first rewritten once, by a bandwidth-bound pass, into two channels-last images in
+// workspace: hi = tf32(x) and lo = x - hi, both [n][row][col][channel] fp32.  The contraction kernel then spends no
+// instruction on operand elements at all:
+//   warp 16    one thread issues, per 32-wide k block (one filter tap, 32 channels), eight tiled
+//              cp.async.bulk.tensor loads -- four 32-pixel boxes of the hi image and of the lo image, shifted by the
+//              tap, zero-filled by the TMA unit outside the image (that is the padding) -- plus one cp.async.bulk for
+//              the packed weight tile; all nine complete the stage's "full" barrier by byte count;
+//   warp 17    allocates TMEM and issues the 3xTF32 tcgen05.mma sequence of gemm_tc.cuh on the stage;
+//   warps 0-15 add each finished accumulator buffer (two k blocks = 24 chained MMAs) into fp32 registers and run the
+//              epilogue (alpha / beta / bias / split-K partials), as in gemm_tc.cuh.
+// An output tile is 128 pixels = four boxes of bw x bh = 32 pixels of one image; the box shape is chosen per layer
+// so that the boxes cover the output grid with the least overhang.  Every barrier wait is bounded.
+//
+// No load carries a cluster multicast qualifier, and every tensor map covers this GPU's own workspace only.
+#pragma once
+
+#include <cuda.h>
+
+#include "gemm_tc.cuh"
+
+namespace vdnn {
+namespace tma {
+
+using tc::A_TILE_BYTES;
+using tc::BK;
+using tc::BM;
+
+constexpr int DRAIN_WARPS = 16;
+constexpr int THREADS = (DRAIN_WARPS + 2) * 32;      // + the TMA warp and the MMA warp
+constexpr int BOX_PIXELS = 32, BOXES = BM / BOX_PIXELS;
+constexpr int BOX_BYTES = BOX_PIXELS * BK * 4;       // 4 KB: four swizzle atoms
+
+template <int BN> struct Config {
+    static constexpr int B_TILE_BYTES = BN * BK * 4;
+    static constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;
+    static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr uint32_t IDESC = tc::Config<BN>::IDESC;
+};
+
+struct Params {
+    // output pixel grid, covered by boxes of (1 << bw_log2) x bh pixels
+    int n_img, out_h, out_w, bw_log2, bh;
+    int boxes_w, total_boxes;
+    FastDiv div_boxes_img, div_boxes_w;
+    // reduction index k = tap * channels + channel, walked in blocks of 32 channels
+    FastDiv div_cblocks, div_s;
+    int tap_sign, off_h, off_w;          // image row of output row y under tap (r, s): y + tap_sign * r + off_h
+    int K, k_chunk, kblocks_total;
+    const char* b_tiles;                 // packed weight tiles (tc::pack_b_tiles_kernel)
+    // output: NCHW tensor of n_cols channels over the output grid
+    float* out;
+    const float* bias;
+    float alpha, beta;
+    int mode, n_cols;
+    size_t partial_stride;
+};
+
+__device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int x, int y, int n) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(x), "r"(y), "r"(n) : "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+conv_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo, const Params p) {
+    typedef Config<BN> Cfg;
+    constexpr int S = Cfg::STAGES;
+    extern __shared__ char smem_raw[];
+    char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + S * Cfg::STAGE_BYTES);
+    // bars[0..S) stage full, [S..2S) stage empty, [2S..2S+2) accumulator buffer ready, [2S+2..2S+4) buffer drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int n0 = blockIdx.y * BN;
+    const int kbeg = blockIdx.z * p.k_chunk;
+    const int kend = min(p.K, kbeg + p.k_chunk);
+    const int nkb = kbeg < kend ? (kend - kbeg) / BK : 0;
+    const int npairs = (nkb + 1) / 2;
+
+    if (t == 0) {
+        for (int s = 0; s < S; ++s) {
+            tc::mbar_init(tc::smem_u32(&bars[s]), 1);
+            tc::mbar_init(tc::smem_u32(&bars[S + s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            tc::mbar_init(tc::smem_u32(&bars[2 * S + b]), 1);
+            tc::mbar_init(tc::smem_u32(&bars[2 * S + 2 + b]), DRAIN_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == DRAIN_WARPS + 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < DRAIN_WARPS) {
+        // ------------------------------------------------------------------ accumulator drain + epilogue
+        constexpr int NACC = BN / (DRAIN_WARPS / 4);
+        const int col_beg = (warp >> 2) * NACC;
+        const uint32_t tmem_mine = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(col_beg);
+        float acc[NACC];
+#pragma unroll
+        for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
+        bool alive = true;
+        for (int pair = 0; pair < npairs && alive; ++pair) {
+            const int b = pair & 1;
+            bool ok = tc::mbar_wait(tc::smem_u32(&bars[2 * S + b]), static_cast<uint32_t>(pair >> 1) & 1u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { atomicCAS(&tc::g_tc_error, 0, 103); alive = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < NACC; c += 16) {
+                float v[16];
+                tc::tmem_ld16(tmem_mine + static_cast<uint32_t>(b * BN + c), v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[c + j] += v[j];
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(tc::smem_u32(&bars[2 * S + 2 + b]));      // this warp's part of the buffer is free again
+        }
+        // this thread's pixel: box (warp & 3) of the tile, pixel `lane` of the box
+        const int box = blockIdx.x * BOXES + (warp & 3);
+        if (alive && box < p.total_boxes) {
+            uint32_t n, rem, by, bx;
+            p.div_boxes_img.divmod(static_cast<uint32_t>(box), n, rem);
+            p.div_boxes_w.divmod(rem, by, bx);
+            const int y = static_cast<int>(by) * p.bh + (lane >> p.bw_log2);
+            const int x = (static_cast<int>(bx) << p.bw_log2) + (lane & ((1 << p.bw_log2) - 1));
+            if (y < p.out_h && x < p.out_w) {
+                const size_t plane = static_cast<size_t>(p.out_h) * p.out_w;
+                float* o = p.out + (static_cast<size_t>(n) * p.n_cols) * plane + static_cast<size_t>(y) * p.out_w + x;
+                if (p.mode == EPI_PARTIAL) o += static_cast<size_t>(blockIdx.z) * p.partial_stride;
+#pragma unroll
+                for (int j = 0; j < NACC; ++j) {
+                    const int col = n0 + col_beg + j;
+                    if (col < p.n_cols) {
+                        float* q = o + static_cast<size_t>(col) * plane;
+                        if (p.mode == EPI_DIRECT) {
+                            float v = p.alpha * acc[j];
+                            if (p.bias) v += p.bias[col];
+                            if (p.beta != 0.0f) v = fmaf(p.beta, *q, v);
+                            *q = v;
+                        } else if (p.mode == EPI_ATOMIC) {
+                            atomicAdd(q, p.alpha * acc[j]);
+                        } else {
+                            *q = acc[j];
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == DRAIN_WARPS) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int bx0[BOXES], by0[BOXES], bn[BOXES];
+#pragma unroll
+            for (int j = 0; j < BOXES; ++j) {
+                const int box = blockIdx.x * BOXES + j;
+                if (box < p.total_boxes) {
+                    uint32_t n, rem, by, bx;
+                    p.div_boxes_img.divmod(static_cast<uint32_t>(box), n, rem);
+                    p.div_boxes_w.divmod(rem, by, bx);
+                    bn[j] = static_cast<int>(n); by0[j] = static_cast<int>(by) * p.bh; bx0[j] = static_cast<int>(bx) << p.bw_log2;
+                } else {
+                    bn[j] = p.n_img; by0[j] = 0; bx0[j] = 0;       // past the last image: the whole box reads as zeros
+                }
+            }
+            const char* b_src = p.b_tiles + (static_cast<size_t>(blockIdx.y) * p.kblocks_total + kbeg / BK) * (2 * Cfg::B_TILE_BYTES);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % S;
+                const uint32_t phase = static_cast<uint32_t>(i / S) & 1u;
+                if (!tc::mbar_wait(tc::smem_u32(&bars[S + s]), phase ^ 1u)) { atomicCAS(&tc::g_tc_error, 0, 101); break; }
+                uint32_t tap, cb, r, sx;
+                p.div_cblocks.divmod(static_cast<uint32_t>(kbeg / BK + i), tap, cb);
+                p.div_s.divmod(tap, r, sx);
+                const int dy = p.tap_sign * static_cast<int>(r) + p.off_h, dx = p.tap_sign * static_cast<int>(sx) + p.off_w;
+                const uint32_t bar = tc::smem_u32(&bars[s]);
+                const uint32_t st = tc::smem_u32(tiles + s * Cfg::STAGE_BYTES);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(Cfg::STAGE_BYTES) : "memory");
+#pragma unroll
+                for (int j = 0; j < BOXES; ++j) {
+                    tma_load_box(st + j * BOX_BYTES, &map_hi, bar, static_cast<int>(cb) * BK, bx0[j] + dx, by0[j] + dy, bn[j]);
+                    tma_load_box(st + A_TILE_BYTES + j * BOX_BYTES, &map_lo, bar, static_cast<int>(cb) * BK, bx0[j] + dx, by0[j] + dy, bn[j]);
+                }
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(st + 2 * A_TILE_BYTES), "l"(b_src + static_cast<size_t>(i) * (2 * Cfg::B_TILE_BYTES)),
+                               "r"(2 * Cfg::B_TILE_BYTES), "r"(bar) : "memory");
+            }
+        }
+    } else if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % S, pair = i >> 1, b = pair & 1;
+            const uint32_t phase = static_cast<uint32_t>(i / S) & 1u;
+            // pairs p and p - 2 share an accumulator buffer: the drain warps must have emptied it
+            if (!(i & 1) && pair >= 2 &&
+                !tc::mbar_wait(tc::smem_u32(&bars[2 * S + 2 + b]), static_cast<uint32_t>((pair >> 1) - 1) & 1u)) {
+                atomicCAS(&tc::g_tc_error, 0, 102);
+                break;
+            }
+            if (!tc::mbar_wait(tc::smem_u32(&bars[s]), phase)) { atomicCAS(&tc::g_tc_error, 0, 102); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_hi = tc::smem_u32(tiles + s * Cfg::STAGE_BYTES);
+            const uint32_t a_lo = a_hi + A_TILE_BYTES;
+            const uint32_t b_hi = a_hi + 2 * A_TILE_BYTES;
+            const uint32_t b_lo = b_hi + Cfg::B_TILE_BYTES;
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * BN);
+#pragma unroll
+            for (int ks = 0; ks < BK / 8; ++ks) {
+                const uint64_t dah = tc::make_desc(a_hi + ks * 32), dal = tc::make_desc(a_lo + ks * 32);
+                const uint64_t dbh = tc::make_desc(b_hi + ks * 32), dbl = tc::make_desc(b_lo + ks * 32);
+                tc::mma_tf32(d_tmem, dal, dbh, Cfg::IDESC, (ks != 0 || (i & 1)) ? 1u : 0u);     // small terms first
+                tc::mma_tf32(d_tmem, dah, dbl, Cfg::IDESC, 1u);
+                tc::mma_tf32(d_tmem, dah, dbh, Cfg::IDESC, 1u);
+            }
+            tc::mma_commit(tc::smem_u32(&bars[S + s]));
+            if ((i & 1) || i == nkb - 1) tc::mma_commit(tc::smem_u32(&bars[2 * S + b]));
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == DRAIN_WARPS + 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Filter gradient on the same images:  dw[k][c][r][s] = sum over pixels of x[pixel + tap][c] * dy[pixel][k].
+// The reduction runs over pixels, and in channels-last images the channels are the contiguous direction, so both
+// operands are "MN-major" for the tensor core: a box of 32 pixels x 32 channels, as the TMA unit drops it (one pixel
+// per 128-byte row, 128-byte swizzle), is four 8-pixel k slices of a 32-wide strip of rows (x) or columns (dy).
+//   rows     128 per tile = four "row groups" of 32 channels; row group g = tap * (C / 32) + channel block, so layers
+//            with few channels fill the tile with several taps (each group is fetched with its own tap shift);
+//   columns  up to 256 filters = up to eight boxes of the dy image, unshifted, shared by the four row groups;
+//   k        boxes of bw x bh = 32 pixels of one image; the reduction over all boxes is split across blockIdx.z.
+struct WgradParams {
+    int n_img, bw_log2, bh, boxes_w, total_boxes, box_chunk;
+    FastDiv div_boxes_img, div_boxes_w;
+    int row_groups, cblocks, taps_s;         // row_groups = R * S * cblocks
+    int off_h, off_w;                        // image row of grid row y under tap r: y + r + off_h
+    int C, taps, n_cols;                     // dw is [n_cols][C][taps]
+    float* out;
+    float alpha, beta;
+    int mode;
+    size_t partial_stride;
+};
+
+// Shared-memory descriptor of an MN-major operand made of 32-wide strips: inside a strip (one TMA box) the 8-pixel
+// k slices follow each other at 1024 bytes, strips follow each other at BOX_BYTES; 128-byte swizzle, descriptor version 1.
+__device__ __forceinline__ uint64_t make_desc_mn(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(BOX_BYTES >> 4) << 16;      // leading dimension: next strip of 32 rows / columns
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;           // stride dimension: next 8-pixel k slice
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ CUtensorMap x_lo,
+             const __grid_constant__ CUtensorMap dy_hi, const __grid_constant__ CUtensorMap dy_lo, const WgradParams p) {
+    typedef Config<BN> Cfg;
+    constexpr int S = Cfg::STAGES;
+    constexpr uint32_t IDESC_MN = Cfg::IDESC | (1u << 15) | (1u << 16);      // both operands MN-major
+    extern __shared__ char smem_raw[];
+    char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + S * Cfg::STAGE_BYTES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int n0 = blockIdx.y * BN;
+    const int box_beg = blockIdx.z * p.box_chunk;
+    const int box_end = min(p.total_boxes, box_beg + p.box_chunk);
+    const int nkb = box_beg < box_end ? box_end - box_beg : 0;
+    const int npairs = (nkb + 1) / 2;
+
+    if (t == 0) {
+        for (int s = 0; s < S; ++s) {
+            tc::mbar_init(tc::smem_u32(&bars[s]), 1);
+            tc::mbar_init(tc::smem_u32(&bars[S + s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            tc::mbar_init(tc::smem_u32(&bars[2 * S + b]), 1);
+            tc::mbar_init(tc::smem_u32(&bars[2 * S + 2 + b]), DRAIN_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == DRAIN_WARPS + 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < DRAIN_WARPS) {
+        constexpr int NACC = BN / (DRAIN_WARPS / 4);
+        const int col_beg = (warp >> 2) * NACC;
+        const uint32_t tmem_mine = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(col_beg);
+        float acc[NACC];
+#pragma unroll
+        for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
+        bool alive = true;
+        for (int pair = 0; pair < npairs && alive; ++pair) {
+            const int b = pair & 1;
+            bool ok = tc::mbar_wait(tc::smem_u32(&bars[2 * S + b]), static_cast<uint32_t>(pair >> 1) & 1u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { atomicCAS(&tc::g_tc_error, 0, 103); alive = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < NACC; c += 16) {
+                float v[16];
+                tc::tmem_ld16(tmem_mine + static_cast<uint32_t>(b * BN + c), v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[c + j] += v[j];
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(tc::smem_u32(&bars[2 * S + 2 + b]));
+        }
+        // this thread's row: row group (warp & 3) of the tile, channel `lane` of its block
+        const int group = blockIdx.x * BOXES + (warp & 3);
+        if (alive && group < p.row_groups) {
+            const int tap = group / p.cblocks, cb = group - tap * p.cblocks;
+            const size_t crs = static_cast<size_t>(p.C) * p.taps;
+            float* o = p.out + static_cast<size_t>(cb * 32 + lane) * p.taps + tap;
+            if (p.mode == EPI_PARTIAL) o += static_cast<size_t>(blockIdx.z) * p.partial_stride;
+#pragma unroll
+            for (int j = 0; j < NACC; ++j) {
+                const int col = n0 + col_beg + j;
+                if (col < p.n_cols) {
+                    float* q = o + static_cast<size_t>(col) * crs;
+                    if (p.mode == EPI_DIRECT) {
+                        float v = p.alpha * acc[j];
+                        if (p.beta != 0.0f) v = fmaf(p.beta, *q, v);
+                        *q = v;
+                    } else if (p.mode == EPI_ATOMIC) {
+                        atomicAdd(q, p.alpha * acc[j]);
+                    } else {
+                        *q = acc[j];
+                    }
+                }
+            }
+        }
+    } else if (warp == DRAIN_WARPS) {
+        if (lane == 0) {
+            int gc[BOXES], gdy[BOXES], gdx[BOXES];
+            int groups = 0;
+#pragma unroll
+            for (int j = 0; j < BOXES; ++j) {
+                const int group = blockIdx.x * BOXES + j;
+                if (group < p.row_groups) {
+                    const int tap = group / p.cblocks, cb = group - tap * p.cblocks;
+                    const int r = tap / p.taps_s, sx = tap - r * p.taps_s;
+                    gc[j] = cb * 32; gdy[j] = r + p.off_h; gdx[j] = sx + p.off_w;
+                    groups = j + 1;
+                } else {
+                    gc[j] = 0; gdy[j] = 0; gdx[j] = 0;
+                }
+            }
+            const int col_boxes = min(BN, p.n_cols - n0) / 32;
+            const uint32_t stage_tx = static_cast<uint32_t>(2 * (groups + col_boxes) * BOX_BYTES);
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % S;
+                const uint32_t phase = static_cast<uint32_t>(i / S) & 1u;
+                if (!tc::mbar_wait(tc::smem_u32(&bars[S + s]), phase ^ 1u)) { atomicCAS(&tc::g_tc_error, 0, 101); break; }
+                uint32_t n, rem, by, bx;
+                p.div_boxes_img.divmod(static_cast<uint32_t>(box_beg + i), n, rem);
+                p.div_boxes_w.divmod(rem, by, bx);
+                const int y0 = static_cast<int>(by) * p.bh, x0 = static_cast<int>(bx) << p.bw_log2;
+                const uint32_t bar = tc::smem_u32(&bars[s]);
+                const uint32_t st = tc::smem_u32(tiles + s * Cfg::STAGE_BYTES);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(stage_tx) : "memory");
+#pragma unroll
+                for (int j = 0; j < BOXES; ++j) {
+                    if (j < groups) {
+                        tma_load_box(st + j * BOX_BYTES, &x_hi, bar, gc[j], x0 + gdx[j], y0 + gdy[j], static_cast<int>(n));
+                        tma_load_box(st + A_TILE_BYTES + j * BOX_BYTES, &x_lo, bar, gc[j], x0 + gdx[j], y0 + gdy[j], static_cast<int>(n));
+                    }
+                }
+                for (int j = 0; j < col_boxes; ++j) {
+                    tma_load_box(st + 2 * A_TILE_BYTES + j * BOX_BYTES, &dy_hi, bar, n0 + j * 32, x0, y0, static_cast<int>(n));
+                    tma_load_box(st + 2 * A_TILE_BYTES + Cfg::B_TILE_BYTES + j * BOX_BYTES, &dy_lo, bar, n0 + j * 32, x0, y0, static_cast<int>(n));
+                }
+            }
+        }
+    } else if (lane == 0) {
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % S, pair = i >> 1, b = pair & 1;
+            const uint32_t phase = static_cast<uint32_t>(i / S) & 1u;
+            if (!(i & 1) && pair >= 2 &&
+                !tc::mbar_wait(tc::smem_u32(&bars[2 * S + 2 + b]), static_cast<uint32_t>((pair >> 1) - 1) & 1u)) {
+                atomicCAS(&tc::g_tc_error, 0, 102);
+                break;
+            }
+            if (!tc::mbar_wait(tc::smem_u32(&bars[s]), phase)) { atomicCAS(&tc::g_tc_error, 0, 102); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_hi = tc::smem_u32(tiles + s * Cfg::STAGE_BYTES);
+            const uint32_t a_lo = a_hi + A_TILE_BYTES;
+            const uint32_t b_hi = a_hi + 2 * A_TILE_BYTES;
+            const uint32_t b_lo = b_hi + Cfg::B_TILE_BYTES;
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * BN);
+#pragma unroll
+            for (int ks = 0; ks < BK / 8; ++ks) {
+                // one k slice = 8 pixels = one 1024-byte swizzle atom of every strip
+                const uint64_t dah = make_desc_mn(a_hi + ks * 1024), dal = make_desc_mn(a_lo + ks * 1024);
+                const uint64_t dbh = make_desc_mn(b_hi + ks * 1024), dbl = make_desc_mn(b_lo + ks * 1024);
+                tc::mma_tf32(d_tmem, dal, dbh, IDESC_MN, (ks != 0 || (i & 1)) ? 1u : 0u);
+                tc::mma_tf32(d_tmem, dah, dbl, IDESC_MN, 1u);
+                tc::mma_tf32(d_tmem, dah, dbh, IDESC_MN, 1u);
+            }
+            tc::mma_commit(tc::smem_u32(&bars[S + s]));
+            if ((i & 1) || i == nkb - 1) tc::mma_commit(tc::smem_u32(&bars[2 * S + b]));
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == DRAIN_WARPS + 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    }
+}
+
+// NCHW fp32 -> two channels-last images: hi = tf32(x) (round to nearest), lo = x - hi.  One block moves 32 channels x
+// 128 pixels of one image through shared memory: reads run along the pixels of a channel, writes along the channels
+// of a pixel, both in full 128-byte lines.
+constexpr int TR_PIX = 128;
+__global__ void __launch_bounds__(256) nchw_to_split_nhwc_kernel(const float* __restrict__ x, float* __restrict__ hi,
+                                                                 float* __restrict__ lo, int C, int HW) {
+    __shared__ float tile[32][TR_PIX + 1];
+    const int n = blockIdx.z, c0 = blockIdx.y * 32, p0 = blockIdx.x * TR_PIX;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const float* src = x + (static_cast<size_t>(n) * C + c0) * HW + p0;
+    const int npix = min(TR_PIX, HW - p0);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int c = warp * 4 + j;
+#pragma unroll
+        for (int q = 0; q < TR_PIX / 32; ++q) {
+            const int pix = q * 32 + lane;
+            tile[c][pix] = pix < npix ? __ldg(src + static_cast<size_t>(c) * HW + pix) : 0.0f;
+        }
+    }
+    __syncthreads();
+    const int quad = t & 7;                     // channels 4 * quad .. + 3
+    float* dh = hi + (static_cast<size_t>(n) * HW + p0) * C + c0 + quad * 4;
+    float* dl = lo + (static_cast<size_t>(n) * HW + p0) * C + c0 + quad * 4;
+#pragma unroll
+    for (int pass = 0; pass < TR_PIX / 32; ++pass) {
+        const int pix = pass * 32 + (t >> 3);
+        if (pix < npix) {
+            float4 h, l;
+            tc::split_tf32_safe(tile[quad * 4 + 0][pix], h.x, l.x);
+            tc::split_tf32_safe(tile[quad * 4 + 1][pix], h.y, l.y);
+            tc::split_tf32_safe(tile[quad * 4 + 2][pix], h.z, l.z);
+            tc::split_tf32_safe(tile[quad * 4 + 3][pix], h.w, l.w);
+            *reinterpret_cast<float4*>(dh + static_cast<size_t>(pix) * C) = h;
+            *reinterpret_cast<float4*>(dl + static_cast<size_t>(pix) * C) = l;
+        }
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled from the driver the runtime is bound to (the library links no libcuda stub).
+inline EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = []() -> EncodeTiledFn {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+            return nullptr;
+        return reinterpret_cast<EncodeTiledFn>(f);
+    }();
+    return fn;
+}
+
+// Tensor map over a channels-last image [n][h][w][c] (fp32, dense) with boxes of 32 channels x bw x bh pixels of one
+// image, 128-byte swizzle, zeros outside the image.
+inline int make_image_map(CUtensorMap* map, const float* image, int n, int h, int w, int c, int bw, int bh) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return VDNN_ERR_UNSUPPORTED;
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(c), static_cast<cuuint64_t>(w), static_cast<cuuint64_t>(h), static_cast<cuuint64_t>(n)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(c) * 4, static_cast<cuuint64_t>(w) * c * 4, static_cast<cuuint64_t>(h) * w * c * 4};
+    const cuuint32_t box[4] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(bw), static_cast<cuuint32_t>(bh), 1u};
+    const cuuint32_t elem[4] = {1u, 1u, 1u, 1u};
+    const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(image), dims, strides, box, elem,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? VDNN_OK : VDNN_ERR_CUDA;
+}
+
+// Box shape (bw x bh = 32 pixels, bw a power of two) that covers a grid of out_h x out_w pixels with the fewest boxes.
+inline void pick_box(int out_h, int out_w, int* bw_log2, int* bh) {
+    long best = -1;
+    for (int lg = 5; lg >= 2; --lg) {
+        const int bw = 1 << lg, h = BOX_PIXELS / bw;
+        const long boxes = static_cast<long>(ceil_div(out_w, bw)) * ceil_div(out_h, h);
+        if (best < 0 || boxes < best) { best = boxes; *bw_log2 = lg; *bh = h; }
+    }
+}
+
+// Bytes of the two images of an n x c x h x w tensor.
+inline size_t image_bytes(int n, int c, int h, int w) { return 2 * sizeof(float) * static_cast<size_t>(n) * c * h * w; }
+
+struct Problem {
+    int n, cin, in_h, in_w;        // the gathered tensor (x for forward, dy for the data gradient)
+    int out_h, out_w, n_cols;      // output grid and channels
+    int R, S, tap_sign, off_h, off_w;
+};
+
+// Transforms `src` (NCHW) into images at `images` (image_bytes() bytes, 128-byte aligned) and runs the contraction
+// against packed weight tiles.  `splits` / `k_chunk` as planned by the caller (k_chunk a multiple of 32).
+template <int BN>
+int launch_bn(const Problem& q, const float* src, char* images, const char* b_tiles, float* out, const float* bias, float alpha,
+              float beta, int mode, size_t partial_stride, int splits, int k_chunk, cudaStream_t stream) {
+    typedef Config<BN> Cfg;
+    int dev = 0;
+    VDNN_CUDA(cudaGetDevice(&dev));
+    auto kern = conv_kernel<BN>;
+    if (VDNN_ONCE_PER_DEVICE(dev))
+        VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    const size_t elems = static_cast<size_t>(q.n) * q.cin * q.in_h * q.in_w;
+    float* hi = reinterpret_cast<float*>(images);
+    float* lo = hi + elems;
+    Params p;
+    p.n_img = q.n; p.out_h = q.out_h; p.out_w = q.out_w;
+    pick_box(q.out_h, q.out_w, &p.bw_log2, &p.bh);
+    const int bw = 1 << p.bw_log2;
+    p.boxes_w = ceil_div(q.out_w, bw);
+    const int boxes_h = ceil_div(q.out_h, p.bh);
+    const long total = static_cast<long>(q.n) * boxes_h * p.boxes_w;
+    if (total > 0x7fffffffL / 2) return VDNN_ERR_UNSUPPORTED;
+    p.total_boxes = static_cast<int>(total);
+    p.div_boxes_img = FastDiv(boxes_h * p.boxes_w); p.div_boxes_w = FastDiv(p.boxes_w);
+    p.div_cblocks = FastDiv(q.cin / BK); p.div_s = FastDiv(q.S);
+    p.tap_sign = q.tap_sign; p.off_h = q.off_h; p.off_w = q.off_w;
+    p.K = q.R * q.S * q.cin; p.k_chunk = k_chunk; p.kblocks_total = p.K / BK;
+    p.b_tiles = b_tiles;
+    p.out = out; p.bias = bias; p.alpha = alpha; p.beta = beta; p.mode = mode; p.n_cols = q.n_cols;
+    p.partial_stride = partial_stride;
+    CUtensorMap map_hi, map_lo;
+    int st = make_image_map(&map_hi, hi, q.n, q.in_h, q.in_w, q.cin, bw, p.bh);
+    if (st != VDNN_OK) return st;
+    st = make_image_map(&map_lo, lo, q.n, q.in_h, q.in_w, q.cin, bw, p.bh);
+    if (st != VDNN_OK) return st;
+    const int hw = q.in_h * q.in_w;
+    dim3 tgrid(ceil_div(hw, TR_PIX), q.cin / 32, q.n);
+    if (tgrid.y > 65535u || tgrid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
+    nchw_to_split_nhwc_kernel<<<tgrid, 256, 0, stream>>>(src, hi, lo, q.cin, hw);
+    VDNN_LAUNCHED();
+    dim3 grid(ceil_div(p.total_boxes, BOXES), ceil_div(q.n_cols, BN), splits);
+    if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
+    kern<<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_hi, map_lo, p);
+    VDNN_LAUNCHED();
+    return VDNN_OK;
+}
+
+inline int launch(const Problem& q, const float* src, char* images, const char* b_tiles, float* out, const float* bias, float alpha,
+                  float beta, int mode, size_t partial_stride, int splits, int k_chunk, cudaStream_t stream) {
+    const int bn = tc::tile_n(q.n_cols);
+    if (bn == 64) return launch_bn<64>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, k_chunk, stream);
+    if (bn == 128) return launch_bn<128>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, k_chunk, stream);
+    return launch_bn<256>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, k_chunk, stream);
+}
+
+struct WgradProblem {
+    int n, c, h, w;          // x
+    int k, p, q;             // dy: n x k x p x q
+    int R, S, pad_h, pad_w;
+};
+
+// Reduction split for the filter gradient: the tiles (row-group quadruples x column tiles) are few, the reduction over
+// pixel boxes is long; as many splits as fill two waves of CTAs, at least two boxes each.
+inline void wgrad_plan(const WgradProblem& q, int total_boxes, int* splits, int* box_chunk) {
+    const int bn = tc::tile_n(q.k);
+    const long tiles = static_cast<long>(ceil_div(q.R * q.S * (q.c / 32), BOXES)) * ceil_div(q.k, bn);
+    long s = (2L * sm_count()) / tiles;
+    if (s > total_boxes / 2) s = total_boxes / 2;
+    if (s > 1024) s = 1024;
+    if (s < 1) s = 1;
+    *box_chunk = ceil_div(total_boxes, static_cast<int>(s));
+    *splits = ceil_div(total_boxes, *box_chunk);
+}
+
+inline int wgrad_boxes(const WgradProblem& q, int* bw_log2, int* bh) {
+    pick_box(q.p, q.q, bw_log2, bh);
+    return q.n * ceil_div(q.p, *bh) * ceil_div(q.q, 1 << *bw_log2);
+}
+
+// Bytes of split partials the filter gradient needs behind its four images.
+inline size_t wgrad_partial_bytes(const WgradProblem& q) {
+    int lg, bh, splits, chunk;
+    const int total = wgrad_boxes(q, &lg, &bh);
+    wgrad_plan(q, total, &splits, &chunk);
+    return splits > 1 ? static_cast<size_t>(splits) * q.k * q.c * q.R * q.S * sizeof(float) : 0;
+}
+
+template <int BN>
+int wgrad_launch_bn(const WgradProblem& q, const float* x, const float* dy, char* ws, float* dw, float alpha, float beta,
+                    cudaStream_t stream, int* splits_out, float** partial_out) {
+    typedef Config<BN> Cfg;
+    int dev = 0;
+    VDNN_CUDA(cudaGetDevice(&dev));
+    auto kern = wgrad_kernel<BN>;
+    if (VDNN_ONCE_PER_DEVICE(dev))
+        VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    const size_t xe = static_cast<size_t>(q.n) * q.c * q.h * q.w, ye = static_cast<size_t>(q.n) * q.k * q.p * q.q;
+    float* xh = reinterpret_cast<float*>(ws);
+    float* xl = xh + xe;
+    float* yh = xl + xe;
+    float* yl = yh + ye;
+    float* partial = yl + ye;
+    WgradParams p;
+    p.n_img = q.n;
+    p.total_boxes = wgrad_boxes(q, &p.bw_log2, &p.bh);
+    const int bw = 1 << p.bw_log2;
+    p.boxes_w = ceil_div(q.q, bw);
+    p.div_boxes_img = FastDiv(ceil_div(q.p, p.bh) * p.boxes_w); p.div_boxes_w = FastDiv(p.boxes_w);
+    int splits = 1;
+    wgrad_plan(q, p.total_boxes, &splits, &p.box_chunk);
+    p.cblocks = q.c / 32; p.taps_s = q.S; p.row_groups = q.R * q.S * p.cblocks;
+    p.off_h = -q.pad_h; p.off_w = -q.pad_w;
+    p.C = q.c; p.taps = q.R * q.S; p.n_cols = q.k;
+    p.partial_stride = static_cast<size_t>(q.k) * q.c * q.R * q.S;
+    if (splits > 1) { p.out = partial; p.alpha = 1.0f; p.beta = 0.0f; p.mode = EPI_PARTIAL; }
+    else { p.out = dw; p.alpha = alpha; p.beta = beta; p.mode = EPI_DIRECT; }
+    CUtensorMap mxh, mxl, myh, myl;
+    int st;
+    if ((st = make_image_map(&mxh, xh, q.n, q.h, q.w, q.c, bw, p.bh)) != VDNN_OK) return st;
+    if ((st = make_image_map(&mxl, xl, q.n, q.h, q.w, q.c, bw, p.bh)) != VDNN_OK) return st;
+    if ((st = make_image_map(&myh, yh, q.n, q.p, q.q, q.k, bw, p.bh)) != VDNN_OK) return st;
+    if ((st = make_image_map(&myl, yl, q.n, q.p, q.q, q.k, bw, p.bh)) != VDNN_OK) return st;
+    dim3 tx(ceil_div(q.h * q.w, TR_PIX), q.c / 32, q.n), ty(ceil_div(q.p * q.q, TR_PIX), q.k / 32, q.n);
+    if (tx.y > 65535u || tx.z > 65535u || ty.y > 65535u) return VDNN_ERR_UNSUPPORTED;
+    nchw_to_split_nhwc_kernel<<<tx, 256, 0, stream>>>(x, xh, xl, q.c, q.h * q.w);
+    VDNN_LAUNCHED();
+    nchw_to_split_nhwc_kernel<<<ty, 256, 0, stream>>>(dy, yh, yl, q.k, q.p * q.q);
+    VDNN_LAUNCHED();
+    dim3 grid(ceil_div(p.row_groups, BOXES), ceil_div(q.k, BN), splits);
+    if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
+    kern<<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(mxh, mxl, myh, myl, p);
+    VDNN_LAUNCHED();
+    *splits_out = splits;
+    *partial_out = partial;
+    return VDNN_OK;
+}
+
+// Bytes of the four images of the filter gradient's operands.
+inline size_t wgrad_image_bytes(const WgradProblem& q) {
+    return image_bytes(q.n, q.c, q.h, q.w) + image_bytes(q.n, q.k, q.p, q.q);
+}
+
+inline int wgrad_launch(const WgradProblem& q, const float* x, const float* dy, char* ws, float* dw, float alpha, float beta,
+                        cudaStream_t stream, int* splits, float** partial) {
+    const int bn = tc::tile_n(q.k);
+    if (bn == 64) return wgrad_launch_bn<64>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial);
+    if (bn == 128) return wgrad_launch_bn<128>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial);
+    return wgrad_launch_bn<256>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial);
+}
+
+}  // namespace tma
+}  // namespace vdnn

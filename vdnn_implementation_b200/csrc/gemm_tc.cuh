@@ -396,6 +396,26 @@ inline size_t bulk_bytes(int N, int K) {
     return static_cast<size_t>(ceil_div(N, bn)) * ceil_div(K, BK) * 2 * bn * BK * sizeof(float);
 }
 
+// Packs all B tiles of an N x K operand for the column tile tile_n(N) into `b_tiles` (bulk_bytes(N, K) bytes).
+template <class OpB, bool BKC, int BN>
+int pack_b_bn(const OpB& b, int N, int K, cudaStream_t stream, char* b_tiles) {
+    const int n_tiles = ceil_div(N, BN), kblocks = ceil_div(K, BK);
+    const size_t chunks = static_cast<size_t>(n_tiles) * kblocks * BN * 8;
+    size_t blocks = ceil_div<size_t>(chunks, 256);
+    const size_t cap = static_cast<size_t>(sm_count()) * 8;
+    if (blocks > cap) blocks = cap;
+    pack_b_tiles_kernel<OpB, BN, BKC><<<static_cast<int>(blocks), 256, 0, stream>>>(b, N, K, n_tiles, kblocks, b_tiles);
+    VDNN_LAUNCHED();
+    return VDNN_OK;
+}
+template <class OpB, bool BKC>
+int pack_b(const OpB& b, int N, int K, cudaStream_t stream, char* b_tiles) {
+    const int bn = tile_n(N);
+    if (bn == 64) return pack_b_bn<OpB, BKC, 64>(b, N, K, stream, b_tiles);
+    if (bn == 128) return pack_b_bn<OpB, BKC, 128>(b, N, K, stream, b_tiles);
+    return pack_b_bn<OpB, BKC, 256>(b, N, K, stream, b_tiles);
+}
+
 template <class OpA, class OpB, bool AKC, bool BKC, int BN, bool BBULK>
 int launch_bn(const OpA& a, const OpB& b, const Epilogue& epi, int M, int N, int K, int splits, int k_chunk, cudaStream_t stream,
               char* b_tiles) {
