@@ -326,7 +326,8 @@ int vdnn_network_layer_algos(vdnn_network* net, int layer, int* out3);
  * reference enqueues each copy in its own layer (layer.cu:969-977) and waits for it there
  * (network.cu:1090-1091).  Without those waits the engine serves copies first in, first out, while
  * backward needs the last layer's data first; so by default (forward_order = 0) only as many bytes of
- * the first layers as the copy engine moves under the forward kernels are enqueued in their own layer,
+ * the first layers as the copy engine moves under the forward kernels (measured from the second step on; the
+ * environment variable VDNN_EAGER_OFFLOAD_BYTES fixes the figure, 0 = none) are enqueued in their own layer,
  * and the rest after the last layer's forward, latest layer first.  Which layers are offloaded, the
  * bytes moved, the host-side allocation order and the pool's byte counts are the same either way.
  * forward_order = 1 (or the environment variable VDNN_OFFLOAD_ORDER=forward) restores layer order. */

@@ -77,3 +77,11 @@ def outlier_fraction(a, b, tol=1e-4):
     assert a.shape == b.shape, (a.shape, b.shape)
     denom = max(float(np.abs(b).max()), 1e-30)
     return float((np.abs(a - b) > tol * denom).mean())
+
+
+def l2_err(a, b):
+    """Relative L2 error ||a - b|| / ||b||."""
+    a = np.asarray(a, np.float64).ravel()
+    b = np.asarray(b, np.float64).ravel()
+    assert a.shape == b.shape, (a.shape, b.shape)
+    return float(np.sqrt(((a - b) ** 2).sum()) / max(np.sqrt((b * b).sum()), 1e-30))

@@ -245,6 +245,8 @@ conv_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ 
 //            with few channels fill the tile with several taps (each group is fetched with its own tap shift);
 //   columns  up to 256 filters = up to eight boxes of the dy image, unshifted, shared by the four row groups;
 //   k        boxes of bw x bh = 32 pixels of one image; the reduction over all boxes is split across blockIdx.z.
+// (The images are the ones forward and data gradient use; only the swizzle the TMA unit applies on the way into
+// shared memory differs, see make_desc_mn.)
 struct WgradParams {
     int n_img, bw_log2, bh, boxes_w, total_boxes, box_chunk;
     FastDiv div_boxes_img, div_boxes_w;
@@ -257,15 +259,19 @@ struct WgradParams {
     size_t partial_stride;
 };
 
-// Shared-memory descriptor of an MN-major operand made of 32-wide strips: inside a strip (one TMA box) the 8-pixel
-// k slices follow each other at 1024 bytes, strips follow each other at BOX_BYTES; 128-byte swizzle, descriptor version 1.
+// Shared-memory descriptor of an MN-major tf32 operand made of 32-wide strips.  32-bit operands can only be read
+// MN-major in the "128-byte swizzle with 32-byte atoms" layout: rows of 128 bytes (one pixel, 32 channels) whose
+// 32-byte quarters are XORed with the row number modulo 4, the pattern repeating every 4 rows (512 bytes); the TMA
+// unit writes exactly that with CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B.  One MMA takes 8 pixels = two such groups, 512
+// bytes apart (stride dimension); strips of 32 rows / columns (one TMA box each) follow each other at BOX_BYTES
+// (leading dimension).  Descriptor version 1, layout type 1.
 __device__ __forceinline__ uint64_t make_desc_mn(uint32_t saddr) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
-    d |= static_cast<uint64_t>(BOX_BYTES >> 4) << 16;      // leading dimension: next strip of 32 rows / columns
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;           // stride dimension: next 8-pixel k slice
+    d |= static_cast<uint64_t>(BOX_BYTES >> 4) << 16;
+    d |= static_cast<uint64_t>(512 >> 4) << 32;
     d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
+    d |= static_cast<uint64_t>(1) << 61;
     return d;
 }
 
@@ -494,7 +500,8 @@ inline EncodeTiledFn encode_tiled() {
 
 // Tensor map over a channels-last image [n][h][w][c] (fp32, dense) with boxes of 32 channels x bw x bh pixels of one
 // image, 128-byte swizzle, zeros outside the image.
-inline int make_image_map(CUtensorMap* map, const float* image, int n, int h, int w, int c, int bw, int bh) {
+inline int make_image_map(CUtensorMap* map, const float* image, int n, int h, int w, int c, int bw, int bh,
+                          CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return VDNN_ERR_UNSUPPORTED;
     const cuuint64_t dims[4] = {static_cast<cuuint64_t>(c), static_cast<cuuint64_t>(w), static_cast<cuuint64_t>(h), static_cast<cuuint64_t>(n)};
@@ -502,7 +509,7 @@ inline int make_image_map(CUtensorMap* map, const float* image, int n, int h, in
     const cuuint32_t box[4] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(bw), static_cast<cuuint32_t>(bh), 1u};
     const cuuint32_t elem[4] = {1u, 1u, 1u, 1u};
     const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(image), dims, strides, box, elem,
-                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? VDNN_OK : VDNN_ERR_CUDA;
 }
@@ -644,10 +651,11 @@ int wgrad_launch_bn(const WgradProblem& q, const float* x, const float* dy, char
     else { p.out = dw; p.alpha = alpha; p.beta = beta; p.mode = EPI_DIRECT; }
     CUtensorMap mxh, mxl, myh, myl;
     int st;
-    if ((st = make_image_map(&mxh, xh, q.n, q.h, q.w, q.c, bw, p.bh)) != VDNN_OK) return st;
-    if ((st = make_image_map(&mxl, xl, q.n, q.h, q.w, q.c, bw, p.bh)) != VDNN_OK) return st;
-    if ((st = make_image_map(&myh, yh, q.n, q.p, q.q, q.k, bw, p.bh)) != VDNN_OK) return st;
-    if ((st = make_image_map(&myl, yl, q.n, q.p, q.q, q.k, bw, p.bh)) != VDNN_OK) return st;
+    const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
+    if ((st = make_image_map(&mxh, xh, q.n, q.h, q.w, q.c, bw, p.bh, sw)) != VDNN_OK) return st;
+    if ((st = make_image_map(&mxl, xl, q.n, q.h, q.w, q.c, bw, p.bh, sw)) != VDNN_OK) return st;
+    if ((st = make_image_map(&myh, yh, q.n, q.p, q.q, q.k, bw, p.bh, sw)) != VDNN_OK) return st;
+    if ((st = make_image_map(&myl, yl, q.n, q.p, q.q, q.k, bw, p.bh, sw)) != VDNN_OK) return st;
     dim3 tx(ceil_div(q.h * q.w, TR_PIX), q.c / 32, q.n), ty(ceil_div(q.p * q.q, TR_PIX), q.k / 32, q.n);
     if (tx.y > 65535u || tx.z > 65535u || ty.y > 65535u) return VDNN_ERR_UNSUPPORTED;
     nchw_to_split_nhwc_kernel<<<tx, 256, 0, stream>>>(x, xh, xl, q.c, q.h * q.w);

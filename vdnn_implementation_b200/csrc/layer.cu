@@ -523,7 +523,8 @@ int Layer::offloadSrcData(bool* _offloaded, DATATYPE** _offloadedSrcData_h) {
     handle->offload_bytes += static_cast<int64_t>(bytes);
     if (handle->dry_run) return 0;
     const vdnnContext::PendingOffload p{layerId, _offloadedSrcData_h[layerId], srcData, bytes};
-    if (handle->defer_offloads && handle->eager_offload_used + static_cast<int64_t>(bytes) > handle->eager_offload_budget) {
+    // a layer may pass the budget by a quarter: better a short delay of the queue behind it than a whole tensor left for later
+    if (handle->defer_offloads && handle->eager_offload_used + static_cast<int64_t>(bytes) > handle->eager_offload_budget + handle->eager_offload_budget / 4) {
         handle->eager_offload_used = handle->eager_offload_budget;     // nothing later overtakes a deferred copy
         handle->pending_offloads.push_back(p);
         return 0;

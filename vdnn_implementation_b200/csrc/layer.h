@@ -56,12 +56,15 @@ struct vdnnContext {
     // are enqueued after the last layer's forward, latest layer first: the prefetch of layer l then follows
     // its offload closely and both PCIe directions run at the same time.  Blocks released meanwhile are held
     // in the pool; when only held bytes fit a request, the pool has the oldest copies enqueued at once.
-    // `eager_offload_budget` bytes of the first layers (environment variable VDNN_EAGER_OFFLOAD_BYTES) are
-    // still enqueued in their own layer, for networks whose forward is long enough to hide them.
+    // `eager_offload_budget` bytes of the first layers are still enqueued in their own layer: the copy engine is idle
+    // under the forward kernels, and the first layers are needed last in backward.  By default the budget is what the
+    // engine moves during one forward pass (measured: duration of the pass x EAGER_OFFLOAD_RATE; a layer may pass the
+    // budget by a quarter); the environment variable VDNN_EAGER_OFFLOAD_BYTES fixes it instead (0 = none).
     struct PendingOffload { int layer; void* host; const void* dev; size_t bytes; };
     bool defer_offloads = false;
     std::vector<PendingOffload> pending_offloads;
     int64_t eager_offload_budget = 0, eager_offload_used = 0, forced_offloads = 0;
+    bool eager_offload_auto = false;
     // Copies go out in pieces of this many bytes with an event after each, so that the prefetch of a tensor
     // can start behind the first piece of its offload instead of behind the whole tensor.
     size_t copy_chunk_bytes = static_cast<size_t>(256) << 20;
@@ -93,6 +96,9 @@ struct vdnnContext {
     int upload(void* dst, const void* src_h, size_t bytes);        // synchronous H2D (initialisation)
 };
 typedef vdnnContext* vdnnHandle_t;
+// Device-to-host rate assumed when forward time is turned into an eager-offload budget (bytes per second): what one
+// direction of the link carries while the other is idle, rounded down.
+#define EAGER_OFFLOAD_RATE 50e9
 
 /* Handle life cycle for a driver that is not this library's Network: the calls the reference makes on its cuDNN /
    cuBLAS handles (network.cu:39-40, 56-57, 96-97).  vdnnCreate hands out the process-wide context (every "handle"

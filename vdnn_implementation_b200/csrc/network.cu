@@ -150,6 +150,7 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
     customLayers = cfg.custom_layers; numCustomLayers = cfg.num_custom_layers;
     externalInput = false; forwardDone = false; stepCounter = 0;
     stage_h = NULL; loss_h = NULL; ev_loss = NULL; ev_step_end = NULL;
+    ev_fwd_t0 = ev_fwd_t1 = NULL; fwdTimed = false; fwdMsBest = 0.0f;
     launchesAtStepStart = launchesLastStep = 0;
     n_in = c_in = h_in = w_in = n_out = c_out = h_out = w_out = 0;
     for (int i = 0; i < DEFAULT_NUM_LAYER; i++) {
@@ -242,7 +243,13 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
         ctx.defer_offloads = !packed && !ctx.host_sync_per_layer && !(order && strcmp(order, "forward") == 0);
         vdnnPoolSetPacked(packed ? 1 : 0);
         packedPool = packed;
+        // How many bytes of the first layers leave in their own layer (under the forward kernels): a fixed figure from the
+        // environment, else measured -- the forward pass's duration on the compute stream times the copy engine's rate.
         if (const char* eager = getenv("VDNN_EAGER_OFFLOAD_BYTES")) ctx.eager_offload_budget = strtoll(eager, NULL, 10);
+        else if (ctx.defer_offloads) {
+            ctx.eager_offload_auto = true;
+            if (cudaEventCreate(&ev_fwd_t0) != cudaSuccess || cudaEventCreate(&ev_fwd_t1) != cudaSuccess) state = VDNN_ERR_CUDA;
+        }
         vdnnPoolSetResolver([](void* user, unsigned long long token) {
             static_cast<vdnnContext*>(user)->flushOffloads(static_cast<int>(token) - 1);
         }, &ctx);
@@ -297,6 +304,8 @@ Network::~Network() {
     for (auto& v : ctx.ev_offload_chunk) drop(v);
     if (ctx.pf_step_beg) cudaEventDestroy(ctx.pf_step_beg);
     if (ctx.pf_step_end) cudaEventDestroy(ctx.pf_step_end);
+    if (ev_fwd_t0) cudaEventDestroy(ev_fwd_t0);
+    if (ev_fwd_t1) cudaEventDestroy(ev_fwd_t1);
     if (ev_loss) cudaEventDestroy(ev_loss);
     if (ev_step_end) cudaEventDestroy(ev_step_end);
     if (stage_h) cudaFreeHost(stage_h);
@@ -598,6 +607,17 @@ int Network::forwardPropagation(bool isDynamic) {
     if (ctx.profiling) NET_CU(cudaEventRecord(ctx.pf_step_beg, stream_compute));
     ctx.eager_offload_used = 0;
     ctx.forced_offloads = 0;
+    if (ctx.eager_offload_auto && !ctx.dry_run) {
+        // the last measured forward pass (if its events have completed) sets this pass's budget; the shortest one counts,
+        // since a pass that waited for copies says nothing about the time the kernels give the copy engine
+        float ms = 0.0f;
+        if (fwdTimed && cudaEventElapsedTime(&ms, ev_fwd_t0, ev_fwd_t1) == cudaSuccess && ms > 0.0f) {
+            if (fwdMsBest <= 0.0f || ms < fwdMsBest) fwdMsBest = ms;
+            ctx.eager_offload_budget = static_cast<int64_t>(fwdMsBest * 1e-3 * EAGER_OFFLOAD_RATE);
+        }
+        (void)cudaGetLastError();
+        NET_CU(cudaEventRecord(ev_fwd_t0, stream_compute));
+    }
 
     for (int l = 0; l < numLayers; l++) {
         layer[l]->copySrcData(l == 0 ? inputData : layer[l - 1]->DstData());
@@ -628,6 +648,7 @@ int Network::forwardPropagation(bool isDynamic) {
         ctx.record(4, l, TAG_NONE, 0);
         memoryLine("Fwd", l, layer[l]->FwdWorkSpaceSize());
     }
+    if (ctx.eager_offload_auto && !ctx.dry_run) { NET_CU(cudaEventRecord(ev_fwd_t1, stream_compute)); fwdTimed = true; }
     if (!ctx.dry_run) NET_TRY(ctx.flushOffloads(-1));
     if (!ctx.dry_run && externalInput) {
         NET_TRY(vdnn_loss(n_out, c_out * h_out * w_out, (const float*)layer[numLayers - 1]->DstData(),
@@ -806,6 +827,7 @@ int Network::writeTensor(int l, int kind, const float* src_h, size_t count) {
 int Network::setOffloadOrder(bool forwardOrder) {
     if (state != VDNN_OK) return state;
     ctx.defer_offloads = !forwardOrder && !ctx.host_sync_per_layer && !ctx.dry_run && !packedPool;
+    if (!ctx.defer_offloads) { ctx.eager_offload_auto = false; ctx.eager_offload_budget = 0; }
     return VDNN_OK;
 }
 

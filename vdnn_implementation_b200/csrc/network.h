@@ -122,6 +122,9 @@ private:
     uint64_t            stepCounter;
     float*              stage_h;               // pinned staging for generated input / labels
     double*             loss_h;
+    cudaEvent_t         ev_fwd_t0, ev_fwd_t1;  // timing events around the forward pass (eager offload budget)
+    bool                fwdTimed;
+    float               fwdMsBest;
     cudaEvent_t         ev_loss;
     cudaEvent_t         ev_step_end;
     std::vector<std::vector<float>> capDst, capGrad;
