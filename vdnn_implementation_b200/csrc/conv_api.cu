@@ -16,8 +16,11 @@ namespace {
 int g_engine = VDNN_ENGINE_AUTO;
 // VDNN_NO_TMA=1 in the environment keeps PERF_OPT forward / data gradient on the gather-fed kernel (A/B measurements).
 const bool g_no_tma = []() { const char* v = getenv("VDNN_NO_TMA"); return v && *v && *v != '0'; }();
-// VDNN_TMA_WGRAD=1: the PERF_OPT filter gradient of eligible layers also runs on the TMA-fed engine.
-const bool g_tma_wgrad = []() { const char* v = getenv("VDNN_TMA_WGRAD"); return v && *v && *v != '0'; }();
+// VDNN_TMA_BOXES=1: forward / data gradient fetch one box of pixels per tap (conv_kernel) instead of one strip of positions
+// per filter row (strip_kernel).
+const bool g_tma_boxes = []() { const char* v = getenv("VDNN_TMA_BOXES"); return v && *v && *v != '0'; }();
+// VDNN_TMA_WGRAD=0: the PERF_OPT filter gradient stays on the gather-fed kernel (default: TMA-fed where the shape allows).
+const bool g_tma_wgrad = []() { const char* v = getenv("VDNN_TMA_WGRAD"); return !(v && *v == '0'); }();
 
 struct SplitPlan { int splits; int k_chunk; };
 
@@ -290,9 +293,24 @@ int tma_slab_images(int n, size_t bytes_per_image) {
     return fit > 1 ? static_cast<int>(fit) : 1;
 }
 
+tma::Problem tma_problem(const vdnn_conv_desc* d, int op, int P, int Q) {
+    if (op == VDNN_CONV_FWD) return tma::Problem{d->n, d->c, d->h, d->w, P, Q, d->k, d->r, d->s, 1, -d->pad_h, -d->pad_w};
+    // dx[h][w] = sum over taps of dy[h + pad - r][w + pad - s] (stride 1)
+    return tma::Problem{d->n, d->k, P, Q, d->h, d->w, d->c, d->r, d->s, -1, d->pad_h, d->pad_w};
+}
+
+bool tma_use_strips(const tma::Problem& q) { return !g_tma_boxes && tma::strip_geometry(q).ok; }
+
+// Bytes of the two operand images of `images` images of the problem, in the layout the chosen kernel reads.
+size_t tma_operand_bytes(const tma::Problem& q, int images) {
+    tma::Problem part = q;
+    part.n = images;
+    return tma_use_strips(q) ? tma::strip_image_bytes(part) : tma::image_bytes(images, q.cin, q.in_h, q.in_w);
+}
+
 size_t tma_image_bytes(const vdnn_conv_desc* d, int op, int P, int Q) {
-    const size_t one = op == VDNN_CONV_FWD ? tma::image_bytes(1, d->c, d->h, d->w) : tma::image_bytes(1, d->k, P, Q);
-    return one * tma_slab_images(d->n, one);
+    const tma::Problem q = tma_problem(d, op, P, Q);
+    return tma_operand_bytes(q, tma_slab_images(d->n, tma_operand_bytes(q, 1)));
 }
 
 int stream_blocks(size_t n) {
@@ -360,29 +378,38 @@ int contract(const OpA& a, const OpB& b, Epilogue epi, int M, int N, int K, size
 // reuse the image buffer), so the workspace stays at the budget whatever the batch size.
 int contract_tma(const tma::Problem& q, const float* src, const char* b_tiles, Epilogue epi, size_t out_elems, char* ws,
                  size_t ws_bytes, cudaStream_t stream) {
-    const int slab = tma_slab_images(q.n, tma::image_bytes(1, q.cin, q.in_h, q.in_w));
-    const size_t img = tma::image_bytes(slab, q.cin, q.in_h, q.in_w);
+    const bool strips = tma_use_strips(q);
+    const int slab = tma_slab_images(q.n, tma_operand_bytes(q, 1));
+    const size_t img = tma_operand_bytes(q, slab);
     if (ws_bytes < img) return VDNN_ERR_WORKSPACE;
     const int M = q.n * q.out_h * q.out_w, K = q.R * q.S * q.cin;
     SplitPlan plan = plan_split(M, q.n_cols, K);
     if (epi.bias || slab < q.n) { plan.splits = 1; plan.k_chunk = K; }
-    if (plan.splits == 1) {
+    // the strip kernel splits the reduction between (filter row, channel block) groups of S k blocks
+    const int groups = q.R * (q.cin / 32);
+    int group_chunk = ceil_div(plan.k_chunk / 32, q.S);
+    if (group_chunk < 1) group_chunk = 1;
+    const int splits = strips ? ceil_div(groups, group_chunk) : plan.splits;
+    auto run = [&](const tma::Problem& part, const float* s, float* o, const float* bias, float alpha, float beta, int mode) {
+        return strips ? tma::strip_launch(part, s, ws, b_tiles, o, bias, alpha, beta, mode, out_elems, splits, group_chunk, stream)
+                      : tma::launch(part, s, ws, b_tiles, o, bias, alpha, beta, mode, out_elems, splits, plan.k_chunk, stream);
+    };
+    if (splits == 1) {
         const size_t src_img = static_cast<size_t>(q.cin) * q.in_h * q.in_w, out_img = static_cast<size_t>(q.n_cols) * q.out_h * q.out_w;
         for (int n0 = 0; n0 < q.n; n0 += slab) {
             tma::Problem part = q;
             part.n = min(slab, q.n - n0);
-            const int st = tma::launch(part, src + n0 * src_img, ws, b_tiles, epi.out + n0 * out_img, epi.bias, epi.alpha, epi.beta,
-                                       EPI_DIRECT, 0, 1, plan.k_chunk, stream);
+            const int st = run(part, src + n0 * src_img, epi.out + n0 * out_img, epi.bias, epi.alpha, epi.beta, EPI_DIRECT);
             if (st != VDNN_OK) return st;
         }
         return VDNN_OK;
     }
-    const size_t need = static_cast<size_t>(plan.splits) * out_elems * sizeof(float);
+    const size_t need = static_cast<size_t>(splits) * out_elems * sizeof(float);
     if (ws_bytes - img < need) return VDNN_ERR_WORKSPACE;
     float* partial = reinterpret_cast<float*>(ws + img);
-    const int st = tma::launch(q, src, ws, b_tiles, partial, nullptr, 1.0f, 0.0f, EPI_PARTIAL, out_elems, plan.splits, plan.k_chunk, stream);
+    const int st = run(q, src, partial, nullptr, 1.0f, 0.0f, EPI_PARTIAL);
     if (st != VDNN_OK) return st;
-    reduce_partials_kernel<<<stream_blocks(out_elems), 256, 0, stream>>>(out_elems, plan.splits, epi.alpha, epi.beta, partial, epi.out);
+    reduce_partials_kernel<<<stream_blocks(out_elems), 256, 0, stream>>>(out_elems, splits, epi.alpha, epi.beta, partial, epi.out);
     VDNN_LAUNCHED();
     return VDNN_OK;
 }
@@ -561,8 +588,8 @@ int vdnn_conv_fwd(const vdnn_conv_desc* d, int algo_mode, float alpha, const flo
         if (tiles && tma_shape(d, VDNN_CONV_FWD) && !g_no_tma) {
             int st = tc::pack_b<SplitDense, true>(B, d->k, crs, s, tiles);
             if (st != VDNN_OK) return st;
-            tma::Problem q{d->n, d->c, d->h, d->w, P, Q, d->k, d->r, d->s, 1, -d->pad_h, -d->pad_w};
-            return contract_tma(q, x, tiles, e, static_cast<size_t>(M) * d->k, tiles + pack, workspace_bytes - pack, s);
+            return contract_tma(tma_problem(d, VDNN_CONV_FWD, P, Q), x, tiles, e, static_cast<size_t>(M) * d->k, tiles + pack,
+                                workspace_bytes - pack, s);
         }
         return contract<XGatherPixRowsTap, SplitDense, false, true>(A, B, e, M, d->k, crs, static_cast<size_t>(M) * d->k, 0, algo_mode,
                                                                     static_cast<char*>(workspace) + pack, workspace_bytes - pack, s, tiles);
@@ -632,9 +659,8 @@ int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, cons
         if (tiles && tma_shape(d, VDNN_CONV_BWD_DATA) && !g_no_tma) {
             int st = tc::pack_b<SplitDense, false>(B, d->c, d->k * rs, s, tiles);
             if (st != VDNN_OK) return st;
-            // dx[h][w] = sum over taps of dy[h + pad - r][w + pad - s] (stride 1)
-            tma::Problem q{d->n, d->k, P, Q, d->h, d->w, d->c, d->r, d->s, -1, d->pad_h, d->pad_w};
-            return contract_tma(q, dy, tiles, e, static_cast<size_t>(M) * d->c, tiles + pack, workspace_bytes - pack, s);
+            return contract_tma(tma_problem(d, VDNN_CONV_BWD_DATA, P, Q), dy, tiles, e, static_cast<size_t>(M) * d->c, tiles + pack,
+                                workspace_bytes - pack, s);
         }
         return contract<DyGather, SplitDense, false, false>(A, B, e, M, d->c, d->k * rs, static_cast<size_t>(M) * d->c, 0, algo_mode,
                                                             static_cast<char*>(workspace) + pack, workspace_bytes - pack, s, tiles);

@@ -32,6 +32,7 @@ constexpr int DRAIN_WARPS = 16;
 constexpr int THREADS = (DRAIN_WARPS + 2) * 32;      // + the TMA warp and the MMA warp
 constexpr int BOX_PIXELS = 32, BOXES = BM / BOX_PIXELS;
 constexpr int BOX_BYTES = BOX_PIXELS * BK * 4;       // 4 KB: four swizzle atoms
+constexpr int TR_PIX = 128;                          // pixels per block of the image transform passes
 
 template <int BN> struct Config {
     static constexpr int B_TILE_BYTES = BN * BK * 4;
@@ -57,6 +58,13 @@ struct Params {
     float alpha, beta;
     int mode, n_cols;
     size_t partial_stride;
+};
+
+// One contraction: image row of output row y under tap r is y + tap_sign * r + off_h (columns likewise).
+struct Problem {
+    int n, cin, in_h, in_w;        // the gathered tensor (x for forward, dy for the data gradient)
+    int out_h, out_w, n_cols;      // output grid and channels
+    int R, S, tap_sign, off_h, off_w;
 };
 
 __device__ __forceinline__ void tma_load_box(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int x, int y, int n) {
@@ -233,6 +241,272 @@ conv_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ 
     if (warp == DRAIN_WARPS + 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Strip engine: the same contraction with every operand row fetched once per filter row instead of once per tap.
+//
+// The gathered tensor is laid out as ONE long list of pixel positions: image after image, row after row, each row
+// followed by `gap_w` zero pixels and each image by `gap_h` zero rows, wide enough that a tap's shift never reaches
+// real data of a neighbouring row or image (the zeros are the padding).  Position q of the list holds 32-channel
+// blocks of 128 bytes, so a filter tap is a constant shift of the position: the operand tile of tap (r, s) for the 128
+// output positions m0 .. m0 + 127 is rows  m0 + dh(r) * Wp + dw(s) ...  of the list, and the tiles of the S taps of
+// one filter row are windows, one row apart, of a single strip of 128 + S - 1 rows.  The TMA unit fetches that strip
+// once (two copies: hi and lo image); the MMA reads tap s through a shared-memory descriptor whose start address is s
+// rows into the strip, with the descriptor's base-offset field naming the phase of the 128-byte swizzle at that row.
+// Shared-memory fill per k block drops from 32 KB to about 11 KB for the gathered operand; the packed weight tiles
+// (their own, deeper ring) are fetched as before.  Output tiles are 128 consecutive positions; results at gap
+// positions are computed and dropped.
+struct StripParams {
+    int n_img, img_h, img_w;             // gathered tensor: images, rows, columns
+    int wp, lp;                          // padded row length and positions per image: lp = (img_h + gap_h) * wp
+    long long total_pos;                 // n_img * lp
+    FastDiv div_lp, div_wp;
+    int out_h, out_w, n_cols;            // output grid (inside the padded geometry) and channels
+    int R, S, cblocks;                   // taps and 32-channel blocks of the reduction
+    int dh0, dh_step, row0, row_step;    // tap (r, s): strip starts dh0 + dh_step * r rows of wp above/below, tap window at row row0 + row_step * s
+    int dw_min;                          // column shift of the strip's first row
+    int groups_total, group_chunk;       // groups = (r, channel block); each split walks group_chunk of them
+    int kblocks_total;
+    const char* b_tiles;
+    float* out;
+    const float* bias;
+    float alpha, beta;
+    int mode;
+    size_t partial_stride;
+};
+
+constexpr int STRIP_MAX_TAPS = 9;                                  // taps per filter row the strip buffer has room for
+constexpr int STRIP_HALF_BYTES = (BM + 8) * BK * 4;                // 136 rows of 128 bytes, a multiple of the swizzle period
+
+template <int BN> struct StripConfig {
+    static constexpr int B_TILE_BYTES = BN * BK * 4;
+    static constexpr int A_STAGE_BYTES = 2 * STRIP_HALF_BYTES;
+    static constexpr int B_STAGE_BYTES = 2 * B_TILE_BYTES;
+    static constexpr int SA = 2;
+    static constexpr int SB = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+    static constexpr int SMEM_BYTES = SA * A_STAGE_BYTES + SB * B_STAGE_BYTES + 1024 + 256;
+    static constexpr uint32_t IDESC = tc::Config<BN>::IDESC;
+};
+
+// K-major, 128-byte-swizzled tile whose first row is not the first row of a swizzle period: the base-offset field
+// (bits 49-51) carries (address >> 7) & 7, the row's position inside the 1024-byte period.
+__device__ __forceinline__ uint64_t make_desc_at(uint32_t saddr) {
+    return tc::make_desc(saddr) | (static_cast<uint64_t>((saddr >> 7) & 7u) << 49);
+}
+
+__device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int row) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(row) : "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(THREADS, 1)
+strip_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo, const StripParams p) {
+    typedef StripConfig<BN> Cfg;
+    constexpr int SA = Cfg::SA, SB = Cfg::SB;
+    extern __shared__ char smem_raw[];
+    char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    char* b_ring = tiles + SA * Cfg::A_STAGE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(b_ring + SB * Cfg::B_STAGE_BYTES);
+    uint64_t* a_full = bars;               // [SA]
+    uint64_t* a_empty = a_full + SA;       // [SA]
+    uint64_t* b_full = a_empty + SA;       // [SB]
+    uint64_t* b_empty = b_full + SB;       // [SB]
+    uint64_t* acc_ready = b_empty + SB;    // [2]
+    uint64_t* acc_free = acc_ready + 2;    // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 2);
+
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int n0 = blockIdx.y * BN;
+    const long long m0 = static_cast<long long>(blockIdx.x) * BM;
+    const int g_beg = blockIdx.z * p.group_chunk;
+    const int g_end = min(p.groups_total, g_beg + p.group_chunk);
+    const int ngroups = g_beg < g_end ? g_end - g_beg : 0;
+    const int nkb = ngroups * p.S;
+    const int npairs = (nkb + 1) / 2;
+    const uint32_t strip_bytes = static_cast<uint32_t>(BM + p.S - 1) * BK * 4;
+
+    if (t == 0) {
+        for (int s = 0; s < SA; ++s) { tc::mbar_init(tc::smem_u32(&a_full[s]), 1); tc::mbar_init(tc::smem_u32(&a_empty[s]), 1); }
+        for (int s = 0; s < SB; ++s) { tc::mbar_init(tc::smem_u32(&b_full[s]), 1); tc::mbar_init(tc::smem_u32(&b_empty[s]), 1); }
+        for (int b = 0; b < 2; ++b) { tc::mbar_init(tc::smem_u32(&acc_ready[b]), 1); tc::mbar_init(tc::smem_u32(&acc_free[b]), DRAIN_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == DRAIN_WARPS + 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < DRAIN_WARPS) {
+        // ------------------------------------------------------------------ accumulator drain + epilogue
+        constexpr int NACC = BN / (DRAIN_WARPS / 4);
+        const int col_beg = (warp >> 2) * NACC;
+        const uint32_t tmem_mine = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(col_beg);
+        float acc[NACC];
+#pragma unroll
+        for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
+        bool alive = true;
+        for (int pair = 0; pair < npairs && alive; ++pair) {
+            const int b = pair & 1;
+            bool ok = tc::mbar_wait(tc::smem_u32(&acc_ready[b]), static_cast<uint32_t>(pair >> 1) & 1u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { atomicCAS(&tc::g_tc_error, 0, 103); alive = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < NACC; c += 16) {
+                float v[16];
+                tc::tmem_ld16(tmem_mine + static_cast<uint32_t>(b * BN + c), v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[c + j] += v[j];
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) tc::mbar_arrive(tc::smem_u32(&acc_free[b]));
+        }
+        const long long q = m0 + (warp & 3) * 32 + lane;          // this thread's position in the padded list
+        if (alive && q < p.total_pos) {
+            const uint32_t n = static_cast<uint32_t>(q / p.lp), rem = static_cast<uint32_t>(q - static_cast<long long>(n) * p.lp);
+            uint32_t y, x;
+            p.div_wp.divmod(rem, y, x);
+            if (static_cast<int>(y) < p.out_h && static_cast<int>(x) < p.out_w) {
+                const size_t plane = static_cast<size_t>(p.out_h) * p.out_w;
+                float* o = p.out + (static_cast<size_t>(n) * p.n_cols) * plane + static_cast<size_t>(y) * p.out_w + x;
+                if (p.mode == EPI_PARTIAL) o += static_cast<size_t>(blockIdx.z) * p.partial_stride;
+#pragma unroll
+                for (int j = 0; j < NACC; ++j) {
+                    const int col = n0 + col_beg + j;
+                    if (col < p.n_cols) {
+                        float* dst = o + static_cast<size_t>(col) * plane;
+                        if (p.mode == EPI_DIRECT) {
+                            float v = p.alpha * acc[j];
+                            if (p.bias) v += p.bias[col];
+                            if (p.beta != 0.0f) v = fmaf(p.beta, *dst, v);
+                            *dst = v;
+                        } else if (p.mode == EPI_ATOMIC) {
+                            atomicAdd(dst, p.alpha * acc[j]);
+                        } else {
+                            *dst = acc[j];
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == DRAIN_WARPS) {
+        // ------------------------------------------------------------------ TMA producer: strips and weight tiles
+        if (lane == 0) {
+            const char* b_col = p.b_tiles + static_cast<size_t>(blockIdx.y) * p.kblocks_total * Cfg::B_STAGE_BYTES;
+            int i = 0;
+            for (int g = 0; g < ngroups; ++g) {
+                const int group = g_beg + g;
+                const int r = group / p.cblocks, cb = group - r * p.cblocks;
+                const int sa = g % SA;
+                if (!tc::mbar_wait(tc::smem_u32(&a_empty[sa]), (static_cast<uint32_t>(g / SA) & 1u) ^ 1u)) { atomicCAS(&tc::g_tc_error, 0, 101); break; }
+                // first row of the strip: position m0 shifted by the filter row and by the leftmost tap
+                const long long row = m0 + static_cast<long long>(p.dh0 + p.dh_step * r) * p.wp + p.dw_min;
+                const uint32_t abar = tc::smem_u32(&a_full[sa]);
+                const uint32_t ast = tc::smem_u32(tiles + sa * Cfg::A_STAGE_BYTES);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(abar), "r"(2u * strip_bytes) : "memory");
+                tma_load_rows(ast, &map_hi, abar, cb * BK, static_cast<int>(row));
+                tma_load_rows(ast + STRIP_HALF_BYTES, &map_lo, abar, cb * BK, static_cast<int>(row));
+                bool ok = true;
+                for (int sx = 0; sx < p.S; ++sx, ++i) {
+                    const int sb = i % SB;
+                    if (!tc::mbar_wait(tc::smem_u32(&b_empty[sb]), (static_cast<uint32_t>(i / SB) & 1u) ^ 1u)) { ok = false; break; }
+                    const int kb = (r * p.S + sx) * p.cblocks + cb;
+                    const uint32_t bbar = tc::smem_u32(&b_full[sb]);
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bbar), "r"(Cfg::B_STAGE_BYTES) : "memory");
+                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                 ::"r"(tc::smem_u32(b_ring + sb * Cfg::B_STAGE_BYTES)), "l"(b_col + static_cast<size_t>(kb) * Cfg::B_STAGE_BYTES),
+                                   "r"(Cfg::B_STAGE_BYTES), "r"(bbar) : "memory");
+                }
+                if (!ok) { atomicCAS(&tc::g_tc_error, 0, 101); break; }
+            }
+        }
+    } else if (lane == 0) {
+        // ------------------------------------------------------------------ MMA issuer
+        int i = 0;
+        bool ok = true;
+        for (int g = 0; g < ngroups && ok; ++g) {
+            const int sa = g % SA;
+            if (!tc::mbar_wait(tc::smem_u32(&a_full[sa]), static_cast<uint32_t>(g / SA) & 1u)) { ok = false; break; }
+            const uint32_t a_hi0 = tc::smem_u32(tiles + sa * Cfg::A_STAGE_BYTES);
+            for (int sx = 0; sx < p.S; ++sx, ++i) {
+                const int sb = i % SB, pair = i >> 1, b = pair & 1;
+                if (!(i & 1) && pair >= 2 && !tc::mbar_wait(tc::smem_u32(&acc_free[b]), static_cast<uint32_t>((pair >> 1) - 1) & 1u)) { ok = false; break; }
+                if (!tc::mbar_wait(tc::smem_u32(&b_full[sb]), static_cast<uint32_t>(i / SB) & 1u)) { ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_hi = a_hi0 + static_cast<uint32_t>(p.row0 + p.row_step * sx) * (BK * 4);
+                const uint32_t a_lo = a_hi + STRIP_HALF_BYTES;
+                const uint32_t b_hi = tc::smem_u32(b_ring + sb * Cfg::B_STAGE_BYTES);
+                const uint32_t b_lo = b_hi + Cfg::B_TILE_BYTES;
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * BN);
+#pragma unroll
+                for (int ks = 0; ks < BK / 8; ++ks) {
+                    const uint64_t dah = make_desc_at(a_hi + ks * 32), dal = make_desc_at(a_lo + ks * 32);
+                    const uint64_t dbh = tc::make_desc(b_hi + ks * 32), dbl = tc::make_desc(b_lo + ks * 32);
+                    tc::mma_tf32(d_tmem, dal, dbh, Cfg::IDESC, (ks != 0 || (i & 1)) ? 1u : 0u);
+                    tc::mma_tf32(d_tmem, dah, dbl, Cfg::IDESC, 1u);
+                    tc::mma_tf32(d_tmem, dah, dbh, Cfg::IDESC, 1u);
+                }
+                tc::mma_commit(tc::smem_u32(&b_empty[sb]));
+                if (sx == p.S - 1) tc::mma_commit(tc::smem_u32(&a_empty[sa]));
+                if ((i & 1) || i == nkb - 1) tc::mma_commit(tc::smem_u32(&acc_ready[b]));
+            }
+        }
+        if (!ok) atomicCAS(&tc::g_tc_error, 0, 102);
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == DRAIN_WARPS + 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+    }
+}
+
+// NCHW fp32 -> the padded position list of the strip engine, as two images (tf32 hi, lo): position q of image n is
+// (row q / wp, column q % wp); rows >= h and columns >= w are the zero gaps.  One block: 32 channels x 128 positions.
+__global__ void __launch_bounds__(256) nchw_to_split_strip_kernel(const float* __restrict__ x, float* __restrict__ hi,
+                                                                  float* __restrict__ lo, int C, int H, int W, int wp, int lp) {
+    __shared__ float tile[32][TR_PIX + 1];
+    const int n = blockIdx.z, c0 = blockIdx.y * 32, q0 = blockIdx.x * TR_PIX;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const int nq = min(TR_PIX, lp - q0);
+    const size_t hw = static_cast<size_t>(H) * W;
+    const float* src = x + (static_cast<size_t>(n) * C + c0) * hw;
+#pragma unroll
+    for (int j = 0; j < TR_PIX / 32; ++j) {
+        const int q = q0 + j * 32 + lane;
+        const int row = q / wp, col = q - row * wp;
+        const bool live = j * 32 + lane < nq && row < H && col < W;
+        const size_t off = static_cast<size_t>(row) * W + col;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int c = warp * 4 + k;
+            tile[c][j * 32 + lane] = live ? __ldg(src + static_cast<size_t>(c) * hw + off) : 0.0f;
+        }
+    }
+    __syncthreads();
+    const int quad = t & 7;
+    const size_t base = (static_cast<size_t>(n) * lp + q0) * C + c0 + quad * 4;
+#pragma unroll
+    for (int pass = 0; pass < TR_PIX / 32; ++pass) {
+        const int pix = pass * 32 + (t >> 3);
+        if (pix < nq) {
+            float4 h, l;
+            tc::split_tf32_safe(tile[quad * 4 + 0][pix], h.x, l.x);
+            tc::split_tf32_safe(tile[quad * 4 + 1][pix], h.y, l.y);
+            tc::split_tf32_safe(tile[quad * 4 + 2][pix], h.z, l.z);
+            tc::split_tf32_safe(tile[quad * 4 + 3][pix], h.w, l.w);
+            *reinterpret_cast<float4*>(hi + base + static_cast<size_t>(pix) * C) = h;
+            *reinterpret_cast<float4*>(lo + base + static_cast<size_t>(pix) * C) = l;
+        }
     }
 }
 
@@ -446,7 +720,6 @@ wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ C
 // NCHW fp32 -> two channels-last images: hi = tf32(x) (round to nearest), lo = x - hi.  One block moves 32 channels x
 // 128 pixels of one image through shared memory: reads run along the pixels of a channel, writes along the channels
 // of a pixel, both in full 128-byte lines.
-constexpr int TR_PIX = 128;
 __global__ void __launch_bounds__(256) nchw_to_split_nhwc_kernel(const float* __restrict__ x, float* __restrict__ hi,
                                                                  float* __restrict__ lo, int C, int HW) {
     __shared__ float tile[32][TR_PIX + 1];
@@ -527,12 +800,6 @@ inline void pick_box(int out_h, int out_w, int* bw_log2, int* bh) {
 // Bytes of the two images of an n x c x h x w tensor.
 inline size_t image_bytes(int n, int c, int h, int w) { return 2 * sizeof(float) * static_cast<size_t>(n) * c * h * w; }
 
-struct Problem {
-    int n, cin, in_h, in_w;        // the gathered tensor (x for forward, dy for the data gradient)
-    int out_h, out_w, n_cols;      // output grid and channels
-    int R, S, tap_sign, off_h, off_w;
-};
-
 // Transforms `src` (NCHW) into images at `images` (image_bytes() bytes, 128-byte aligned) and runs the contraction
 // against packed weight tiles.  `splits` / `k_chunk` as planned by the caller (k_chunk a multiple of 32).
 template <int BN>
@@ -586,6 +853,90 @@ inline int launch(const Problem& q, const float* src, char* images, const char* 
     if (bn == 64) return launch_bn<64>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, k_chunk, stream);
     if (bn == 128) return launch_bn<128>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, k_chunk, stream);
     return launch_bn<256>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, k_chunk, stream);
+}
+
+// Geometry of the strip engine's padded position list for one problem.
+struct StripGeom { int wp, hp, lp, dh0, dh_step, row0, row_step, dw_min; bool ok; };
+
+inline StripGeom strip_geometry(const Problem& q) {
+    StripGeom g;
+    // row shift of tap r: off_h + tap_sign * r; column shift of tap s likewise
+    const int dh_a = q.off_h, dh_b = q.off_h + q.tap_sign * (q.R - 1);
+    const int dw_a = q.off_w, dw_b = q.off_w + q.tap_sign * (q.S - 1);
+    const int dh_min = dh_a < dh_b ? dh_a : dh_b, dh_max = dh_a < dh_b ? dh_b : dh_a;
+    const int dw_min = dw_a < dw_b ? dw_a : dw_b, dw_max = dw_a < dw_b ? dw_b : dw_a;
+    int gap_h = -dh_min > dh_max ? -dh_min : dh_max, gap_w = -dw_min > dw_max ? -dw_min : dw_max;
+    if (gap_h < 0) gap_h = 0;
+    if (gap_w < 0) gap_w = 0;
+    g.wp = q.in_w + gap_w; g.hp = q.in_h + gap_h; g.lp = g.hp * g.wp;
+    g.dh0 = q.off_h; g.dh_step = q.tap_sign;
+    g.dw_min = dw_min;
+    g.row0 = q.tap_sign > 0 ? 0 : q.S - 1; g.row_step = q.tap_sign;
+    g.ok = q.S <= STRIP_MAX_TAPS && q.out_w <= g.wp && q.out_h <= g.hp && static_cast<long long>(q.n) * g.lp < 0x7fffff00LL;
+    return g;
+}
+
+inline size_t strip_image_bytes(const Problem& q) {
+    const StripGeom g = strip_geometry(q);
+    return 2 * sizeof(float) * static_cast<size_t>(q.n) * g.lp * q.cin;
+}
+
+// group_chunk: (filter row, channel block) groups per split; splits = ceil(R * cin / 32 / group_chunk).
+template <int BN>
+int strip_launch_bn(const Problem& q, const float* src, char* images, const char* b_tiles, float* out, const float* bias, float alpha,
+                    float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream) {
+    typedef StripConfig<BN> Cfg;
+    int dev = 0;
+    VDNN_CUDA(cudaGetDevice(&dev));
+    auto kern = strip_kernel<BN>;
+    if (VDNN_ONCE_PER_DEVICE(dev))
+        VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+    const StripGeom g = strip_geometry(q);
+    if (!g.ok) return VDNN_ERR_UNSUPPORTED;
+    const size_t elems = static_cast<size_t>(q.n) * g.lp * q.cin;
+    float* hi = reinterpret_cast<float*>(images);
+    float* lo = hi + elems;
+    StripParams p;
+    p.n_img = q.n; p.img_h = q.in_h; p.img_w = q.in_w; p.wp = g.wp; p.lp = g.lp;
+    p.total_pos = static_cast<long long>(q.n) * g.lp;
+    p.div_lp = FastDiv(g.lp); p.div_wp = FastDiv(g.wp);
+    p.out_h = q.out_h; p.out_w = q.out_w; p.n_cols = q.n_cols;
+    p.R = q.R; p.S = q.S; p.cblocks = q.cin / BK;
+    p.dh0 = g.dh0; p.dh_step = g.dh_step; p.row0 = g.row0; p.row_step = g.row_step; p.dw_min = g.dw_min;
+    p.groups_total = q.R * p.cblocks; p.group_chunk = group_chunk;
+    p.kblocks_total = q.R * q.S * p.cblocks;
+    p.b_tiles = b_tiles;
+    p.out = out; p.bias = bias; p.alpha = alpha; p.beta = beta; p.mode = mode; p.partial_stride = partial_stride;
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return VDNN_ERR_UNSUPPORTED;
+    CUtensorMap map_hi, map_lo;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(q.cin), static_cast<cuuint64_t>(p.total_pos)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(q.cin) * 4};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(BM + q.S - 1)};
+    const cuuint32_t elem[2] = {1u, 1u};
+    for (int half = 0; half < 2; ++half) {
+        const CUresult r = enc(half ? &map_lo : &map_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, half ? lo : hi, dims, strides, box, elem,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return VDNN_ERR_CUDA;
+    }
+    dim3 tgrid(ceil_div(g.lp, TR_PIX), q.cin / 32, q.n);
+    if (tgrid.y > 65535u || tgrid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
+    nchw_to_split_strip_kernel<<<tgrid, 256, 0, stream>>>(src, hi, lo, q.cin, q.in_h, q.in_w, g.wp, g.lp);
+    VDNN_LAUNCHED();
+    dim3 grid(static_cast<unsigned>(ceil_div<long long>(p.total_pos, BM)), ceil_div(q.n_cols, BN), splits);
+    if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
+    kern<<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_hi, map_lo, p);
+    VDNN_LAUNCHED();
+    return VDNN_OK;
+}
+
+inline int strip_launch(const Problem& q, const float* src, char* images, const char* b_tiles, float* out, const float* bias,
+                        float alpha, float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream) {
+    const int bn = tc::tile_n(q.n_cols);
+    if (bn == 64) return strip_launch_bn<64>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
+    if (bn == 128) return strip_launch_bn<128>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
+    return strip_launch_bn<256>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
 }
 
 struct WgradProblem {
