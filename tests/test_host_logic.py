@@ -254,7 +254,7 @@ def test_dynamic_algo_per_layer(vdnn, oracle):
     ws = _perf_workspaces(vdnn, specs)
     assert ws[0][0] > 8e6 and ws[2][0] > 4e6
     picks = {}
-    for pool in (3_500_000, 4_496_896, 9_000_000, 16_000_000):
+    for pool in (3_500_000, 4_496_896, 10_000_000, 16_000_000):
         assert (oracle.dynamic_choice(specs, pool, ws) is None) == (pool == 3_500_000)
         try:
             net = vdnn.Network("CUSTOM_CNN", "VDNN_NONE", "VDNN_DYNAMIC_ALGO", device=-1, pool_bytes=pool, custom_layers=specs)
@@ -269,7 +269,7 @@ def test_dynamic_algo_per_layer(vdnn, oracle):
             net.close()
     assert picks[3_500_000] == -5                                         # not even VDNN_ALL with zero workspace
     assert picks[4_496_896] == ((2, 2), (0, 0, 0), (0, 0, 0))             # VDNN_ALL, no room for any workspace
-    assert picks[9_000_000] == ((2, 2), (0, 0, 1), (1, 1, 1))             # room for the second layer's 4.2 MB (and 0.3 MB of dy tiles)
+    assert picks[10_000_000] == ((2, 2), (0, 0, 1), (1, 1, 1))            # room for the second layer's workspaces and the first one's smallest
     assert picks[16_000_000] == ((1, 1), (1, 1, 1), (1, 1, 1))            # everything fits without offloading
 
 
