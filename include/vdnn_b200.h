@@ -51,7 +51,9 @@ const char* vdnn_build_info(void);
 typedef enum { VDNN_ALGO_MEMORY_OPT = 0, VDNN_ALGO_PERF_OPT = 1, VDNN_ALGO_DYNAMIC = 2 } vdnn_algo_mode;
 typedef enum { VDNN_CONV_FWD = 0, VDNN_CONV_BWD_DATA = 1, VDNN_CONV_BWD_FILTER = 2 } vdnn_conv_op;
 /* Which contraction engine runs CONV/FC.  AUTO picks TCGEN05 (3xTF32 on the 5th-generation
- * tensor cores, fp32-accurate) when the shape is supported by it and FFMA otherwise. */
+ * tensor cores, fp32-accurate) when the shape is supported by it and FFMA otherwise.  In PERF_OPT the tensor-core
+ * engine has a gather-fed and a TMA-fed kernel family; AUTO uses the TMA-fed one for stride-1 convolutions with
+ * enough output tiles to fill the GPU, TCGEN05 for every shape it supports (workspace sizes follow the setting). */
 typedef enum { VDNN_ENGINE_AUTO = 0, VDNN_ENGINE_FFMA = 1, VDNN_ENGINE_TCGEN05 = 2 } vdnn_engine;
 int vdnn_set_engine(int engine);   /* process-wide; returns the previous value */
 int vdnn_get_engine(void);

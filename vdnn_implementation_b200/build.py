@@ -19,9 +19,9 @@ COMMON = ["-std=c++17", "-O3", "-lineinfo", "-I", os.path.join(ROOT, "include"),
 
 CUDA_SOURCES = ["elementwise.cu", "conv_api.cu", "layer.cu", "network.cu"]
 HOST_SOURCES = ["pool_alloc.cpp", "host_rng.cpp", "dp_nccl.cpp", "network_abi.cpp"]
-HEADERS = ["common.cuh", "gemm_operands.cuh", "gemm_ffma.cuh", "gemm_tc.cuh", "layer.h", "network.h", "vdnn.h",
-           "dp_nccl.h", os.path.join(ROOT, "include", "vdnn_b200.h"),
-           os.path.join(ROOT, "include", "cnmem", "include", "cnmem.h")]
+# every header under csrc/ (a source is rebuilt when any of them is newer) plus the two public ones
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))) + [
+    os.path.join(ROOT, "include", "vdnn_b200.h"), os.path.join(ROOT, "include", "cnmem", "include", "cnmem.h")]
 
 
 def _newer(target, deps):

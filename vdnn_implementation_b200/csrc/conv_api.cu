@@ -274,7 +274,15 @@ bool tma_shape(const vdnn_conv_desc* d, int op) {
     if (op != VDNN_CONV_FWD && op != VDNN_CONV_BWD_DATA) return false;
     if (d->stride_h != 1 || d->stride_w != 1 || is_full_extent(d)) return false;
     if (op == VDNN_CONV_BWD_DATA && d->c <= SMALL_C_MAX) return false;          // the first layer has its own kernels
-    return (op == VDNN_CONV_FWD ? d->c : d->k) % 32 == 0;
+    if ((op == VDNN_CONV_FWD ? d->c : d->k) % 32 != 0) return false;
+    // Only where the output has enough tiles to fill the GPU without splitting the reduction: the few-tile layers (14 x 14
+    // maps) stay on the gather kernel, which splits along k at a finer grain and needs no operand images.  With the
+    // engine forced to VDNN_ENGINE_TCGEN05 every eligible shape takes the TMA-fed path (small shapes in the tests).
+    if (g_engine == VDNN_ENGINE_TCGEN05) return true;
+    const int P = (d->h + 2 * d->pad_h - d->r) / d->stride_h + 1, Q = (d->w + 2 * d->pad_w - d->s) / d->stride_w + 1;
+    const long long pixels = static_cast<long long>(d->n) * (op == VDNN_CONV_FWD ? P * Q : d->h * d->w);
+    const int cols = op == VDNN_CONV_FWD ? d->k : d->c;
+    return (pixels + 127) / 128 * ((cols + 255) / 256) >= sm_count();
 }
 
 bool tma_wgrad_shape(const vdnn_conv_desc* d) {
@@ -286,7 +294,7 @@ tma::WgradProblem wgrad_problem(const vdnn_conv_desc* d, int P, int Q) {
 }
 
 // Operand images of at most this many bytes are kept in workspace at a time.
-constexpr size_t TMA_IMAGE_BUDGET = static_cast<size_t>(384) << 20;
+constexpr size_t TMA_IMAGE_BUDGET = static_cast<size_t>(1) << 30;
 int tma_slab_images(int n, size_t bytes_per_image) {
     if (bytes_per_image * n <= TMA_IMAGE_BUDGET) return n;
     const size_t fit = TMA_IMAGE_BUDGET / bytes_per_image;
@@ -586,10 +594,10 @@ int vdnn_conv_fwd(const vdnn_conv_desc* d, int algo_mode, float alpha, const flo
         B.col_div = FastDiv(d->c); B.col_hi = 1; B.col_lo = rs;
         char* tiles = (g_engine != VDNN_ENGINE_FFMA && (reinterpret_cast<uintptr_t>(workspace) & 127u) == 0) ? static_cast<char*>(workspace) : nullptr;
         if (tiles && tma_shape(d, VDNN_CONV_FWD) && !g_no_tma) {
-            int st = tc::pack_b<SplitDense, true>(B, d->k, crs, s, tiles);
+            const tma::Problem q = tma_problem(d, VDNN_CONV_FWD, P, Q);
+            int st = tc::pack_b<SplitDense, true>(B, d->k, crs, s, tiles, tma_use_strips(q) ? tma::strip_tile_n(d->k) : 0);
             if (st != VDNN_OK) return st;
-            return contract_tma(tma_problem(d, VDNN_CONV_FWD, P, Q), x, tiles, e, static_cast<size_t>(M) * d->k, tiles + pack,
-                                workspace_bytes - pack, s);
+            return contract_tma(q, x, tiles, e, static_cast<size_t>(M) * d->k, tiles + pack, workspace_bytes - pack, s);
         }
         return contract<XGatherPixRowsTap, SplitDense, false, true>(A, B, e, M, d->k, crs, static_cast<size_t>(M) * d->k, 0, algo_mode,
                                                                     static_cast<char*>(workspace) + pack, workspace_bytes - pack, s, tiles);
@@ -657,10 +665,10 @@ int vdnn_conv_bwd_data(const vdnn_conv_desc* d, int algo_mode, float alpha, cons
         if (!workspace || workspace_bytes < pack) return VDNN_ERR_WORKSPACE;
         char* tiles = (g_engine != VDNN_ENGINE_FFMA && (reinterpret_cast<uintptr_t>(workspace) & 127u) == 0) ? static_cast<char*>(workspace) : nullptr;
         if (tiles && tma_shape(d, VDNN_CONV_BWD_DATA) && !g_no_tma) {
-            int st = tc::pack_b<SplitDense, false>(B, d->c, d->k * rs, s, tiles);
+            const tma::Problem q = tma_problem(d, VDNN_CONV_BWD_DATA, P, Q);
+            int st = tc::pack_b<SplitDense, false>(B, d->c, d->k * rs, s, tiles, tma_use_strips(q) ? tma::strip_tile_n(d->c) : 0);
             if (st != VDNN_OK) return st;
-            return contract_tma(tma_problem(d, VDNN_CONV_BWD_DATA, P, Q), dy, tiles, e, static_cast<size_t>(M) * d->c, tiles + pack,
-                                workspace_bytes - pack, s);
+            return contract_tma(q, dy, tiles, e, static_cast<size_t>(M) * d->c, tiles + pack, workspace_bytes - pack, s);
         }
         return contract<DyGather, SplitDense, false, false>(A, B, e, M, d->c, d->k * rs, static_cast<size_t>(M) * d->c, 0, algo_mode,
                                                             static_cast<char*>(workspace) + pack, workspace_bytes - pack, s, tiles);

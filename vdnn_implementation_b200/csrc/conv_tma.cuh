@@ -223,14 +223,7 @@ conv_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ 
             const uint32_t b_hi = a_hi + 2 * A_TILE_BYTES;
             const uint32_t b_lo = b_hi + Cfg::B_TILE_BYTES;
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * BN);
-#pragma unroll
-            for (int ks = 0; ks < BK / 8; ++ks) {
-                const uint64_t dah = tc::make_desc(a_hi + ks * 32), dal = tc::make_desc(a_lo + ks * 32);
-                const uint64_t dbh = tc::make_desc(b_hi + ks * 32), dbl = tc::make_desc(b_lo + ks * 32);
-                tc::mma_tf32(d_tmem, dal, dbh, Cfg::IDESC, (ks != 0 || (i & 1)) ? 1u : 0u);     // small terms first
-                tc::mma_tf32(d_tmem, dah, dbl, Cfg::IDESC, 1u);
-                tc::mma_tf32(d_tmem, dah, dbh, Cfg::IDESC, 1u);
-            }
+            tc::mma_block_3xtf32(d_tmem, tc::make_desc(a_hi), tc::make_desc(a_lo), tc::make_desc(b_hi), tc::make_desc(b_lo), Cfg::IDESC, !(i & 1));
             tc::mma_commit(tc::smem_u32(&bars[S + s]));
             if ((i & 1) || i == nkb - 1) tc::mma_commit(tc::smem_u32(&bars[2 * S + b]));
         }
@@ -254,7 +247,9 @@ conv_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ 
 // output positions m0 .. m0 + 127 is rows  m0 + dh(r) * Wp + dw(s) ...  of the list, and the tiles of the S taps of
 // one filter row are windows, one row apart, of a single strip of 128 + S - 1 rows.  The TMA unit fetches that strip
 // once (two copies: hi and lo image); the MMA reads tap s through a shared-memory descriptor whose start address is s
-// rows into the strip, with the descriptor's base-offset field naming the phase of the 128-byte swizzle at that row.
+// rows into the strip.  (Measured on B200: the tensor core derives the 128-byte swizzle phase of every operand row from
+// the row's shared-memory address, so a window that starts inside a swizzle period needs nothing but its start
+// address; putting the phase into the descriptor's base-offset field as well gives wrong operands.)
 // Shared-memory fill per k block drops from 32 KB to about 11 KB for the gathered operand; the packed weight tiles
 // (their own, deeper ring) are fetched as before.  Output tiles are 128 consecutive positions; results at gap
 // positions are computed and dropped.
@@ -268,6 +263,8 @@ struct StripParams {
     int dh0, dh_step, row0, row_step;    // tap (r, s): strip starts dh0 + dh_step * r rows of wp above/below, tap window at row row0 + row_step * s
     int dw_min;                          // column shift of the strip's first row
     int groups_total, group_chunk;       // groups = (r, channel block); each split walks group_chunk of them
+    int inner;                           // taps served by one strip: S, or 1 (one strip per tap: groups = (tap, channel block))
+    int use_base_offset;                 // descriptors of shifted windows carry the swizzle phase in their base-offset field
     int kblocks_total;
     const char* b_tiles;
     float* out;
@@ -280,18 +277,32 @@ struct StripParams {
 constexpr int STRIP_MAX_TAPS = 9;                                  // taps per filter row the strip buffer has room for
 constexpr int STRIP_HALF_BYTES = (BM + 8) * BK * 4;                // 136 rows of 128 bytes, a multiple of the swizzle period
 
-template <int BN> struct StripConfig {
+// MH = 128-row halves of an output tile.  The packed weight tile of a k block (BN * 256 bytes) costs three times the
+// shared-memory fill of a 128-row strip's share of it (~11 KB), and the SM's ingest rate is what bounds these kernels, so
+// a tile of 256 positions x 128 columns (two MMAs per k slice sharing the weight operand) moves a third fewer bytes per
+// flop than 128 x 256: MH = 2 wherever the tensor memory holds the four accumulators (BN <= 128).
+template <int BN, int MH> struct StripConfig {
+    static_assert(MH == 1 || (MH == 2 && BN <= 128), "two row halves need 4 * BN <= 512 columns of tensor memory");
     static constexpr int B_TILE_BYTES = BN * BK * 4;
-    static constexpr int A_STAGE_BYTES = 2 * STRIP_HALF_BYTES;
+    static constexpr int A_STAGE_BYTES = MH * 2 * STRIP_HALF_BYTES;
     static constexpr int B_STAGE_BYTES = 2 * B_TILE_BYTES;
+    static constexpr int TMEM_COLS = 2 * MH * BN;
+    // Ring depths.  A strip is in use for S k blocks, i.e. S * 6 * BN clocks of MMA work, and its refill (a TMA box of
+    // ~130 rows gathered from rows C * 4 bytes apart) takes a few thousand clocks to land: narrow tiles need more strips
+    // in flight than wide ones.  Measured with two strips: 256 columns 77 % tensor-pipe activity (bound by the SM's ingest
+    // rate), 128 columns 54 %, 64 columns 47 % (both waiting for strips).
+    // (Measured, 128-row tiles: deeper strip rings or L2 prefetches of the next tile's strips did not help; two CTAs per
+    // SM for 64-column tiles did, because one thread issues a tile's MMAs and 12 per 384 clocks of tensor work is about
+    // its limit.)
     static constexpr int SA = 2;
-    static constexpr int SB = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+    static constexpr int SB = MH == 2 ? (BN == 128 ? 2 : 4) : (BN == 256 ? 2 : (BN == 128 ? 4 : 2));
+    static constexpr int CTAS_PER_SM = (MH == 1 && BN == 64) ? 2 : 1;
     static constexpr int SMEM_BYTES = SA * A_STAGE_BYTES + SB * B_STAGE_BYTES + 1024 + 256;
     static constexpr uint32_t IDESC = tc::Config<BN>::IDESC;
 };
 
-// K-major, 128-byte-swizzled tile whose first row is not the first row of a swizzle period: the base-offset field
-// (bits 49-51) carries (address >> 7) & 7, the row's position inside the 1024-byte period.
+// The same descriptor with the row's position inside the 1024-byte swizzle period, (address >> 7) & 7, in the
+// base-offset field (bits 49-51).  Kept for the diagnostic mode only: see the note on the strip engine above.
 __device__ __forceinline__ uint64_t make_desc_at(uint32_t saddr) {
     return tc::make_desc(saddr) | (static_cast<uint64_t>((saddr >> 7) & 7u) << 49);
 }
@@ -301,11 +312,12 @@ __device__ __forceinline__ void tma_load_rows(uint32_t dst, const CUtensorMap* m
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(row) : "memory");
 }
 
-template <int BN>
-__global__ void __launch_bounds__(THREADS, 1)
+template <int BN, int MH>
+__global__ void __launch_bounds__(THREADS, StripConfig<BN, MH>::CTAS_PER_SM)
 strip_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo, const StripParams p) {
-    typedef StripConfig<BN> Cfg;
+    typedef StripConfig<BN, MH> Cfg;
     constexpr int SA = Cfg::SA, SB = Cfg::SB;
+    constexpr int TILE_ROWS = BM * MH;
     extern __shared__ char smem_raw[];
     char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     char* b_ring = tiles + SA * Cfg::A_STAGE_BYTES;
@@ -318,15 +330,20 @@ strip_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__
     uint64_t* acc_free = acc_ready + 2;    // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 2);
 
+    // The CTA is persistent along x: it walks output tiles blockIdx.x, blockIdx.x + gridDim.x, ... of its column tile
+    // (blockIdx.y) and reduction split (blockIdx.z).  The three roles loop over the tiles independently and keep their
+    // ring / accumulator counters running, so the loads of the next tile are in flight, and its first MMAs issued, while
+    // the previous tile's results are still being stored: barrier set-up, TMEM allocation and the pipeline fill are paid
+    // once per CTA, not once per tile.
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int n0 = blockIdx.y * BN;
-    const long long m0 = static_cast<long long>(blockIdx.x) * BM;
+    const long long num_tiles = (p.total_pos + TILE_ROWS - 1) / TILE_ROWS;
     const int g_beg = blockIdx.z * p.group_chunk;
     const int g_end = min(p.groups_total, g_beg + p.group_chunk);
     const int ngroups = g_beg < g_end ? g_end - g_beg : 0;
-    const int nkb = ngroups * p.S;
-    const int npairs = (nkb + 1) / 2;
-    const uint32_t strip_bytes = static_cast<uint32_t>(BM + p.S - 1) * BK * 4;
+    const int nkb = ngroups * p.inner;                 // k blocks per tile
+    const int npairs = (nkb + 1) / 2;                  // accumulator hand-overs per tile
+    const uint32_t strip_bytes = static_cast<uint32_t>(BM + p.inner - 1) * BK * 4;
 
     if (t == 0) {
         for (int s = 0; s < SA; ++s) { tc::mbar_init(tc::smem_u32(&a_full[s]), 1); tc::mbar_init(tc::smem_u32(&a_empty[s]), 1); }
@@ -335,7 +352,7 @@ strip_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == DRAIN_WARPS + 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(tmem_slot)), "r"(Cfg::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -348,34 +365,42 @@ strip_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__
         constexpr int NACC = BN / (DRAIN_WARPS / 4);
         const int col_beg = (warp >> 2) * NACC;
         const uint32_t tmem_mine = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(col_beg);
-        float acc[NACC];
-#pragma unroll
-        for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
+        const size_t plane = static_cast<size_t>(p.out_h) * p.out_w;
         bool alive = true;
-        for (int pair = 0; pair < npairs && alive; ++pair) {
-            const int b = pair & 1;
-            bool ok = tc::mbar_wait(tc::smem_u32(&acc_ready[b]), static_cast<uint32_t>(pair >> 1) & 1u);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { atomicCAS(&tc::g_tc_error, 0, 103); alive = false; break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        unsigned pair = 0;                                  // running count of accumulator hand-overs
+        for (long long tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+            float acc[MH][NACC];
 #pragma unroll
-            for (int c = 0; c < NACC; c += 16) {
-                float v[16];
-                tc::tmem_ld16(tmem_mine + static_cast<uint32_t>(b * BN + c), v);
+            for (int h = 0; h < MH; ++h)
 #pragma unroll
-                for (int j = 0; j < 16; ++j) acc[c + j] += v[j];
+                for (int j = 0; j < NACC; ++j) acc[h][j] = 0.0f;
+            for (int pp = 0; pp < npairs && alive; ++pp, ++pair) {
+                const int b = pair & 1;
+                bool ok = tc::mbar_wait(tc::smem_u32(&acc_ready[b]), (pair >> 1) & 1u);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) { atomicCAS(&tc::g_tc_error, 0, 103); alive = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int h = 0; h < MH; ++h)
+#pragma unroll
+                    for (int c = 0; c < NACC; c += 16) {
+                        float v[16];
+                        tc::tmem_ld16(tmem_mine + static_cast<uint32_t>((b * MH + h) * BN + c), v);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) acc[h][c + j] += v[j];
+                    }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) tc::mbar_arrive(tc::smem_u32(&acc_free[b]));
             }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) tc::mbar_arrive(tc::smem_u32(&acc_free[b]));
-        }
-        const long long q = m0 + (warp & 3) * 32 + lane;          // this thread's position in the padded list
-        if (alive && q < p.total_pos) {
-            const uint32_t n = static_cast<uint32_t>(q / p.lp), rem = static_cast<uint32_t>(q - static_cast<long long>(n) * p.lp);
-            uint32_t y, x;
-            p.div_wp.divmod(rem, y, x);
-            if (static_cast<int>(y) < p.out_h && static_cast<int>(x) < p.out_w) {
-                const size_t plane = static_cast<size_t>(p.out_h) * p.out_w;
+#pragma unroll
+            for (int h = 0; h < MH; ++h) {
+                const long long q = tile * TILE_ROWS + h * BM + (warp & 3) * 32 + lane;      // this thread's position in the padded list
+                if (!alive || q >= p.total_pos) continue;
+                const uint32_t n = static_cast<uint32_t>(q / p.lp), rem = static_cast<uint32_t>(q - static_cast<long long>(n) * p.lp);
+                uint32_t y, x;
+                p.div_wp.divmod(rem, y, x);
+                if (static_cast<int>(y) >= p.out_h || static_cast<int>(x) >= p.out_w) continue;
                 float* o = p.out + (static_cast<size_t>(n) * p.n_cols) * plane + static_cast<size_t>(y) * p.out_w + x;
                 if (p.mode == EPI_PARTIAL) o += static_cast<size_t>(blockIdx.z) * p.partial_stride;
 #pragma unroll
@@ -384,14 +409,14 @@ strip_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__
                     if (col < p.n_cols) {
                         float* dst = o + static_cast<size_t>(col) * plane;
                         if (p.mode == EPI_DIRECT) {
-                            float v = p.alpha * acc[j];
+                            float v = p.alpha * acc[h][j];
                             if (p.bias) v += p.bias[col];
                             if (p.beta != 0.0f) v = fmaf(p.beta, *dst, v);
                             *dst = v;
                         } else if (p.mode == EPI_ATOMIC) {
-                            atomicAdd(dst, p.alpha * acc[j]);
+                            atomicAdd(dst, p.alpha * acc[h][j]);
                         } else {
-                            *dst = acc[j];
+                            *dst = acc[h][j];
                         }
                     }
                 }
@@ -401,62 +426,77 @@ strip_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__
         // ------------------------------------------------------------------ TMA producer: strips and weight tiles
         if (lane == 0) {
             const char* b_col = p.b_tiles + static_cast<size_t>(blockIdx.y) * p.kblocks_total * Cfg::B_STAGE_BYTES;
-            int i = 0;
-            for (int g = 0; g < ngroups; ++g) {
-                const int group = g_beg + g;
-                const int r = group / p.cblocks, cb = group - r * p.cblocks;
-                const int sa = g % SA;
-                if (!tc::mbar_wait(tc::smem_u32(&a_empty[sa]), (static_cast<uint32_t>(g / SA) & 1u) ^ 1u)) { atomicCAS(&tc::g_tc_error, 0, 101); break; }
-                // first row of the strip: position m0 shifted by the filter row and by the leftmost tap
-                const long long row = m0 + static_cast<long long>(p.dh0 + p.dh_step * r) * p.wp + p.dw_min;
-                const uint32_t abar = tc::smem_u32(&a_full[sa]);
-                const uint32_t ast = tc::smem_u32(tiles + sa * Cfg::A_STAGE_BYTES);
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(abar), "r"(2u * strip_bytes) : "memory");
-                tma_load_rows(ast, &map_hi, abar, cb * BK, static_cast<int>(row));
-                tma_load_rows(ast + STRIP_HALF_BYTES, &map_lo, abar, cb * BK, static_cast<int>(row));
-                bool ok = true;
-                for (int sx = 0; sx < p.S; ++sx, ++i) {
-                    const int sb = i % SB;
-                    if (!tc::mbar_wait(tc::smem_u32(&b_empty[sb]), (static_cast<uint32_t>(i / SB) & 1u) ^ 1u)) { ok = false; break; }
-                    const int kb = (r * p.S + sx) * p.cblocks + cb;
-                    const uint32_t bbar = tc::smem_u32(&b_full[sb]);
-                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bbar), "r"(Cfg::B_STAGE_BYTES) : "memory");
-                    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                                 ::"r"(tc::smem_u32(b_ring + sb * Cfg::B_STAGE_BYTES)), "l"(b_col + static_cast<size_t>(kb) * Cfg::B_STAGE_BYTES),
-                                   "r"(Cfg::B_STAGE_BYTES), "r"(bbar) : "memory");
+            unsigned i = 0, gcount = 0;                     // running k-block and strip counts (ring positions)
+            bool ok = true;
+            for (long long tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const long long m0 = tile * TILE_ROWS;
+                for (int g = 0; g < ngroups && ok; ++g, ++gcount) {
+                    const int group = g_beg + g;
+                    const int outer = group / p.cblocks, cb = group - outer * p.cblocks;
+                    const int r = p.inner == 1 ? outer / p.S : outer, s_first = p.inner == 1 ? outer - r * p.S : 0;
+                    const int sa = gcount % SA;
+                    if (!tc::mbar_wait(tc::smem_u32(&a_empty[sa]), ((gcount / SA) & 1u) ^ 1u)) { ok = false; break; }
+                    // first row of the strip: position m0 shifted by the filter row and by the leftmost tap (or, with
+                    // one strip per tap, by that tap)
+                    const long long row = m0 + static_cast<long long>(p.dh0 + p.dh_step * r) * p.wp + p.dw_min +
+                                          (p.inner == 1 ? p.row0 + p.row_step * s_first : 0);
+                    const uint32_t abar = tc::smem_u32(&a_full[sa]);
+                    const uint32_t ast = tc::smem_u32(tiles + sa * Cfg::A_STAGE_BYTES);
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(abar), "r"(MH * 2u * strip_bytes) : "memory");
+#pragma unroll
+                    for (int h = 0; h < MH; ++h) {      // one strip pair (hi, lo) per 128-row half of the tile
+                        tma_load_rows(ast + h * 2 * STRIP_HALF_BYTES, &map_hi, abar, cb * BK, static_cast<int>(row) + h * BM);
+                        tma_load_rows(ast + h * 2 * STRIP_HALF_BYTES + STRIP_HALF_BYTES, &map_lo, abar, cb * BK, static_cast<int>(row) + h * BM);
+                    }
+                    for (int sx = 0; sx < p.inner; ++sx, ++i) {
+                        const int sb = i % SB;
+                        if (!tc::mbar_wait(tc::smem_u32(&b_empty[sb]), ((i / SB) & 1u) ^ 1u)) { ok = false; break; }
+                        const int kb = (r * p.S + s_first + sx) * p.cblocks + cb;
+                        const uint32_t bbar = tc::smem_u32(&b_full[sb]);
+                        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bbar), "r"(Cfg::B_STAGE_BYTES) : "memory");
+                        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                                     ::"r"(tc::smem_u32(b_ring + sb * Cfg::B_STAGE_BYTES)), "l"(b_col + static_cast<size_t>(kb) * Cfg::B_STAGE_BYTES),
+                                       "r"(Cfg::B_STAGE_BYTES), "r"(bbar) : "memory");
+                    }
                 }
-                if (!ok) { atomicCAS(&tc::g_tc_error, 0, 101); break; }
             }
+            if (!ok) atomicCAS(&tc::g_tc_error, 0, 101);
         }
     } else if (lane == 0) {
         // ------------------------------------------------------------------ MMA issuer
-        int i = 0;
+        unsigned i = 0, gcount = 0, pair = 0;
         bool ok = true;
-        for (int g = 0; g < ngroups && ok; ++g) {
-            const int sa = g % SA;
-            if (!tc::mbar_wait(tc::smem_u32(&a_full[sa]), static_cast<uint32_t>(g / SA) & 1u)) { ok = false; break; }
-            const uint32_t a_hi0 = tc::smem_u32(tiles + sa * Cfg::A_STAGE_BYTES);
-            for (int sx = 0; sx < p.S; ++sx, ++i) {
-                const int sb = i % SB, pair = i >> 1, b = pair & 1;
-                if (!(i & 1) && pair >= 2 && !tc::mbar_wait(tc::smem_u32(&acc_free[b]), static_cast<uint32_t>((pair >> 1) - 1) & 1u)) { ok = false; break; }
-                if (!tc::mbar_wait(tc::smem_u32(&b_full[sb]), static_cast<uint32_t>(i / SB) & 1u)) { ok = false; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a_hi = a_hi0 + static_cast<uint32_t>(p.row0 + p.row_step * sx) * (BK * 4);
-                const uint32_t a_lo = a_hi + STRIP_HALF_BYTES;
-                const uint32_t b_hi = tc::smem_u32(b_ring + sb * Cfg::B_STAGE_BYTES);
-                const uint32_t b_lo = b_hi + Cfg::B_TILE_BYTES;
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * BN);
+        for (long long tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            int kb_in_tile = 0;
+            for (int g = 0; g < ngroups && ok; ++g, ++gcount) {
+                const int sa = gcount % SA;
+                if (!tc::mbar_wait(tc::smem_u32(&a_full[sa]), (gcount / SA) & 1u)) { ok = false; break; }
+                const uint32_t a_hi0 = tc::smem_u32(tiles + sa * Cfg::A_STAGE_BYTES);
+                for (int sx = 0; sx < p.inner; ++sx, ++i, ++kb_in_tile) {
+                    const int sb = i % SB, b = pair & 1;
+                    const bool first_of_pair = !(kb_in_tile & 1);
+                    // hand-overs `pair` and `pair - 2` share an accumulator buffer: the drain warps must have emptied it
+                    if (first_of_pair && pair >= 2 && !tc::mbar_wait(tc::smem_u32(&acc_free[b]), ((pair >> 1) - 1) & 1u)) { ok = false; break; }
+                    if (!tc::mbar_wait(tc::smem_u32(&b_full[sb]), (i / SB) & 1u)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_hi = a_hi0 + (p.inner == 1 ? 0u : static_cast<uint32_t>(p.row0 + p.row_step * sx) * (BK * 4));
+                    const uint32_t a_lo = a_hi + STRIP_HALF_BYTES;
+                    const uint32_t b_hi = tc::smem_u32(b_ring + sb * Cfg::B_STAGE_BYTES);
+                    const uint32_t b_lo = b_hi + Cfg::B_TILE_BYTES;
+                    const uint64_t dbh = tc::make_desc(b_hi), dbl = tc::make_desc(b_lo);
 #pragma unroll
-                for (int ks = 0; ks < BK / 8; ++ks) {
-                    const uint64_t dah = make_desc_at(a_hi + ks * 32), dal = make_desc_at(a_lo + ks * 32);
-                    const uint64_t dbh = tc::make_desc(b_hi + ks * 32), dbl = tc::make_desc(b_lo + ks * 32);
-                    tc::mma_tf32(d_tmem, dal, dbh, Cfg::IDESC, (ks != 0 || (i & 1)) ? 1u : 0u);
-                    tc::mma_tf32(d_tmem, dah, dbl, Cfg::IDESC, 1u);
-                    tc::mma_tf32(d_tmem, dah, dbh, Cfg::IDESC, 1u);
+                    for (int h = 0; h < MH; ++h) {      // the row halves share the weight operand
+                        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((b * MH + h) * BN);
+                        const uint32_t ah = a_hi + h * 2 * STRIP_HALF_BYTES, al = a_lo + h * 2 * STRIP_HALF_BYTES;
+                        if (p.use_base_offset)      // diagnostic mode only
+                            tc::mma_block_3xtf32(d_tmem, make_desc_at(ah), make_desc_at(al), dbh, dbl, Cfg::IDESC, first_of_pair);
+                        else
+                            tc::mma_block_3xtf32(d_tmem, tc::make_desc(ah), tc::make_desc(al), dbh, dbl, Cfg::IDESC, first_of_pair);
+                    }
+                    tc::mma_commit(tc::smem_u32(&b_empty[sb]));
+                    if (sx == p.inner - 1) tc::mma_commit(tc::smem_u32(&a_empty[sa]));
+                    if (!first_of_pair || kb_in_tile == nkb - 1) { tc::mma_commit(tc::smem_u32(&acc_ready[b])); ++pair; }
                 }
-                tc::mma_commit(tc::smem_u32(&b_empty[sb]));
-                if (sx == p.S - 1) tc::mma_commit(tc::smem_u32(&a_empty[sa]));
-                if ((i & 1) || i == nkb - 1) tc::mma_commit(tc::smem_u32(&acc_ready[b]));
             }
         }
         if (!ok) atomicCAS(&tc::g_tc_error, 0, 102);
@@ -466,7 +506,7 @@ strip_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__
     __syncthreads();
     if (warp == DRAIN_WARPS + 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
     }
 }
 
@@ -695,15 +735,9 @@ wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ C
             const uint32_t b_hi = a_hi + 2 * A_TILE_BYTES;
             const uint32_t b_lo = b_hi + Cfg::B_TILE_BYTES;
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * BN);
-#pragma unroll
-            for (int ks = 0; ks < BK / 8; ++ks) {
-                // one k slice = 8 pixels = one 1024-byte swizzle atom of every strip
-                const uint64_t dah = make_desc_mn(a_hi + ks * 1024), dal = make_desc_mn(a_lo + ks * 1024);
-                const uint64_t dbh = make_desc_mn(b_hi + ks * 1024), dbl = make_desc_mn(b_lo + ks * 1024);
-                tc::mma_tf32(d_tmem, dal, dbh, IDESC_MN, (ks != 0 || (i & 1)) ? 1u : 0u);
-                tc::mma_tf32(d_tmem, dah, dbl, IDESC_MN, 1u);
-                tc::mma_tf32(d_tmem, dah, dbh, IDESC_MN, 1u);
-            }
+            // one k slice = 8 pixels = 1024 bytes further into every strip
+            tc::mma_block_3xtf32<1024 / 16>(d_tmem, make_desc_mn(a_hi), make_desc_mn(a_lo), make_desc_mn(b_hi), make_desc_mn(b_lo),
+                                            IDESC_MN, !(i & 1));
             tc::mma_commit(tc::smem_u32(&bars[S + s]));
             if ((i & 1) || i == nkb - 1) tc::mma_commit(tc::smem_u32(&bars[2 * S + b]));
         }
@@ -882,13 +916,13 @@ inline size_t strip_image_bytes(const Problem& q) {
 }
 
 // group_chunk: (filter row, channel block) groups per split; splits = ceil(R * cin / 32 / group_chunk).
-template <int BN>
+template <int BN, int MH>
 int strip_launch_bn(const Problem& q, const float* src, char* images, const char* b_tiles, float* out, const float* bias, float alpha,
                     float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream) {
-    typedef StripConfig<BN> Cfg;
+    typedef StripConfig<BN, MH> Cfg;
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
-    auto kern = strip_kernel<BN>;
+    auto kern = strip_kernel<BN, MH>;
     if (VDNN_ONCE_PER_DEVICE(dev))
         VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     const StripGeom g = strip_geometry(q);
@@ -903,7 +937,14 @@ int strip_launch_bn(const Problem& q, const float* src, char* images, const char
     p.out_h = q.out_h; p.out_w = q.out_w; p.n_cols = q.n_cols;
     p.R = q.R; p.S = q.S; p.cblocks = q.cin / BK;
     p.dh0 = g.dh0; p.dh_step = g.dh_step; p.row0 = g.row0; p.row_step = g.row_step; p.dw_min = g.dw_min;
-    p.groups_total = q.R * p.cblocks; p.group_chunk = group_chunk;
+    // VDNN_STRIP_MODE (diagnostics): unset / 1 = one strip per filter row, tap windows by start address alone;
+    // 0 = the same with the swizzle phase also in the descriptors' base-offset field (gives wrong results on B200);
+    // 2 = one strip per tap (no shifted windows)
+    static const int strip_mode = []() { const char* v = getenv("VDNN_STRIP_MODE"); return v ? atoi(v) : 1; }();
+    p.inner = strip_mode == 2 ? 1 : q.S;
+    p.use_base_offset = strip_mode == 0 ? 1 : 0;
+    p.groups_total = (strip_mode == 2 ? q.R * q.S : q.R) * p.cblocks;
+    p.group_chunk = strip_mode == 2 ? group_chunk * q.S : group_chunk;
     p.kblocks_total = q.R * q.S * p.cblocks;
     p.b_tiles = b_tiles;
     p.out = out; p.bias = bias; p.alpha = alpha; p.beta = beta; p.mode = mode; p.partial_stride = partial_stride;
@@ -912,7 +953,7 @@ int strip_launch_bn(const Problem& q, const float* src, char* images, const char
     CUtensorMap map_hi, map_lo;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(q.cin), static_cast<cuuint64_t>(p.total_pos)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(q.cin) * 4};
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(BM + q.S - 1)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(BM + p.inner - 1)};
     const cuuint32_t elem[2] = {1u, 1u};
     for (int half = 0; half < 2; ++half) {
         const CUresult r = enc(half ? &map_lo : &map_hi, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, half ? lo : hi, dims, strides, box, elem,
@@ -924,19 +965,51 @@ int strip_launch_bn(const Problem& q, const float* src, char* images, const char
     if (tgrid.y > 65535u || tgrid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
     nchw_to_split_strip_kernel<<<tgrid, 256, 0, stream>>>(src, hi, lo, q.cin, q.in_h, q.in_w, g.wp, g.lp);
     VDNN_LAUNCHED();
-    dim3 grid(static_cast<unsigned>(ceil_div<long long>(p.total_pos, BM)), ceil_div(q.n_cols, BN), splits);
-    if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
+    // persistent along x: as many CTAs as the GPU holds at once (all column tiles and splits of an output tile run side
+    // by side, so that they share its strips through L2), each walking every gridDim.x-th output tile
+    const long long tiles = ceil_div<long long>(p.total_pos, BM * MH);
+    const int ny = ceil_div(q.n_cols, BN);
+    if (ny > 65535 || splits > 65535) return VDNN_ERR_UNSUPPORTED;
+    long long gx = static_cast<long long>(sm_count()) * Cfg::CTAS_PER_SM / (static_cast<long long>(ny) * splits);
+    if (gx < 1) gx = 1;
+    if (gx > tiles) gx = tiles;
+    dim3 grid(static_cast<unsigned>(gx), ny, splits);
     kern<<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(map_hi, map_lo, p);
     VDNN_LAUNCHED();
     return VDNN_OK;
 }
 
+// Tile shape of the strip engine by the number of output columns (measured on B200, VGG16 shapes at batch 32):
+//   up to 64 columns    128 positions x 64, two CTAs per SM   (one thread can issue about 12 MMAs per 384 clocks of
+//                        tensor work: two CTAs give two issuers)
+//   65 .. 128 columns   256 positions x 128: the two 128-row halves share the weight tile (a third fewer bytes per flop)
+//   more                128 positions x 256: with 256-column MMAs the tensor core reads the fewest operand bytes per
+//                        flop from shared memory, which is what bounds the narrower shapes
+// VDNN_STRIP_SHAPE=tall / wide forces 256 x 128 (256 x 64) or 128-row tiles everywhere (comparison runs).
+inline int strip_shape_override() {
+    static const int v = []() { const char* e = getenv("VDNN_STRIP_SHAPE"); return !e ? 0 : (e[0] == 't' ? 2 : (e[0] == 'w' ? 1 : 0)); }();
+    return v;
+}
+inline int strip_halves(int n_cols) {
+    const int o = strip_shape_override();
+    if (o) return o;
+    return (n_cols > 64 && n_cols <= 128) ? 2 : 1;
+}
+inline int strip_tile_n(int n_cols) {
+    if (strip_halves(n_cols) == 2) return n_cols <= 64 ? 64 : 128;
+    return tc::tile_n(n_cols);
+}
+
 inline int strip_launch(const Problem& q, const float* src, char* images, const char* b_tiles, float* out, const float* bias,
                         float alpha, float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream) {
-    const int bn = tc::tile_n(q.n_cols);
-    if (bn == 64) return strip_launch_bn<64>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
-    if (bn == 128) return strip_launch_bn<128>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
-    return strip_launch_bn<256>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
+    const int bn = strip_tile_n(q.n_cols);
+    if (strip_halves(q.n_cols) == 2) {
+        if (bn == 64) return strip_launch_bn<64, 2>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
+        return strip_launch_bn<128, 2>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
+    }
+    if (bn == 64) return strip_launch_bn<64, 1>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
+    if (bn == 128) return strip_launch_bn<128, 1>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
+    return strip_launch_bn<256, 1>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
 }
 
 struct WgradProblem {

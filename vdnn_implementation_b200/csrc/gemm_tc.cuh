@@ -105,6 +105,30 @@ __device__ __forceinline__ void mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64
                  "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the accumulate flag known at compile time (no predicate set-up): D += A * B.
+__device__ __forceinline__ void mma_tf32_acc(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, 1, 1;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc) : "memory");
+}
+// One 32-wide k block of the 3xTF32 product: for each of the four 8-wide k slices, lo*hi, hi*lo, hi*hi (small terms
+// first).  The four descriptors are built once; a k slice is 32 bytes further into the swizzle atom, which is 2 in the
+// descriptors' 16-byte address units.  `fresh` = the first MMA overwrites the accumulator instead of adding to it.
+// (K-major tiles: STEP = 2.  MN-major strips step a whole 8-row group per k slice: STEP = bytes / 16.)
+template <int STEP = 2>
+__device__ __forceinline__ void mma_block_3xtf32(uint32_t d_tmem, uint64_t dah, uint64_t dal, uint64_t dbh, uint64_t dbl,
+                                                 uint32_t idesc, bool fresh) {
+    mma_tf32(d_tmem, dal, dbh, idesc, fresh ? 0u : 1u);
+    mma_tf32_acc(d_tmem, dah, dbl, idesc);
+    mma_tf32_acc(d_tmem, dah, dbh, idesc);
+#pragma unroll
+    for (int ks = 1; ks < BK / 8; ++ks) {
+        dah += STEP; dal += STEP; dbh += STEP; dbl += STEP;
+        mma_tf32_acc(d_tmem, dal, dbh, idesc);
+        mma_tf32_acc(d_tmem, dah, dbl, idesc);
+        mma_tf32_acc(d_tmem, dah, dbh, idesc);
+    }
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -330,15 +354,7 @@ gemm_kernel(const OpA opa, const OpB opb, const Epilogue epi, int M, int N, int 
             const uint32_t b_lo = b_hi + Cfg::B_TILE_BYTES;
             // two consecutive k blocks share an accumulator buffer (a chain of 24 MMAs), then the other buffer is used
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(((i >> 1) & 1) * BN);
-#pragma unroll
-            for (int ks = 0; ks < BK / 8; ++ks) {
-                // one k slice = 8 tf32 = 32 bytes inside the swizzle atom
-                const uint64_t dah = make_desc(a_hi + ks * 32), dal = make_desc(a_lo + ks * 32);
-                const uint64_t dbh = make_desc(b_hi + ks * 32), dbl = make_desc(b_lo + ks * 32);
-                mma_tf32(d_tmem, dal, dbh, Cfg::IDESC, (ks != 0 || (i & 1)) ? 1u : 0u);     // small terms first
-                mma_tf32(d_tmem, dah, dbl, Cfg::IDESC, 1u);
-                mma_tf32(d_tmem, dah, dbh, Cfg::IDESC, 1u);
-            }
+            mma_block_3xtf32(d_tmem, make_desc(a_hi), make_desc(a_lo), make_desc(b_hi), make_desc(b_lo), Cfg::IDESC, !(i & 1));
             mma_commit(smem_u32(&bars[S + s]));             // stage s may be overwritten once these finish
             if ((i & 1) || i == nkb - 1)
                 mma_commit(smem_u32(&bars[2 * S + ((i >> 1) & 1)]));   // and this pair's sums may be collected
@@ -408,9 +424,10 @@ int pack_b_bn(const OpB& b, int N, int K, cudaStream_t stream, char* b_tiles) {
     VDNN_LAUNCHED();
     return VDNN_OK;
 }
+// bn: the column tile the consuming kernel uses (0 = tile_n(N)).
 template <class OpB, bool BKC>
-int pack_b(const OpB& b, int N, int K, cudaStream_t stream, char* b_tiles) {
-    const int bn = tile_n(N);
+int pack_b(const OpB& b, int N, int K, cudaStream_t stream, char* b_tiles, int bn = 0) {
+    if (bn == 0) bn = tile_n(N);
     if (bn == 64) return pack_b_bn<OpB, BKC, 64>(b, N, K, stream, b_tiles);
     if (bn == 128) return pack_b_bn<OpB, BKC, 128>(b, N, K, stream, b_tiles);
     return pack_b_bn<OpB, BKC, 256>(b, N, K, stream, b_tiles);
