@@ -118,6 +118,14 @@ int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, co
                          const float* dy, float beta, float* dw,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* cudnnConvolutionBackwardBias + cudnnConvolutionBackwardFilter (layer.cu:631-660) in one call:
+ *   db = alpha_b * sum_{n,p,q} dy + beta_b * db,   dw = alpha * (x corr dy) + beta * dw.
+ * In PERF_OPT, for stride-1 convolutions whose channel counts are multiples of 32, the bias sums are formed by the pass
+ * that prepares dy for the filter gradient (dy is read once less); otherwise the two separate entry points run. */
+int vdnn_conv_bwd_filter_bias(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* x, const float* dy,
+                              float beta, float* dw, float alpha_b, float beta_b, float* db,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
 /* Filter gradient for callers that cannot provide workspace.  No counterpart in the reference.
  *
  * Same result as vdnn_conv_bwd_filter with VDNN_ALGO_PERF_OPT (fixed-order, deterministic split-K
@@ -345,6 +353,15 @@ int vdnn_network_timeline(vdnn_network* net, float* out);
  * a communication stream as each layer's backward finishes, then applied with vdnn_axpy. */
 int vdnn_dp_unique_id(char* out128);
 int vdnn_network_enable_dp(vdnn_network* net, int rank, int world_size, const char* unique_id128);
+/* With VDNN_DP_FUSED=1 in the environment (ranks = processes on one box, at most 8), vdnn_network_enable_dp also maps
+ * every rank's gradient arena into this process (CUDA IPC) and the per-layer NCCL all-reduce + axpy is replaced by one
+ * kernel per layer: reduce-scatter by peer loads, all-gather by peer stores over NVLink, then the SGD step, ordered by
+ * epoch flags in peer memory whose waits are bounded (an expired wait makes vdnn_network_synchronize return
+ * VDNN_ERR_TIMEOUT).  Sums are taken in rank order on every rank, so weights stay bit-identical across ranks.
+ * vdnn_network_dp_mode: 0 = single device, 1 = NCCL, 2 = fused peer kernel (what the ranks agreed on).
+ * vdnn_dp_slice: the part of a `count`-float gradient that `rank` reduces, [*begin, *end) in floats, whole groups of 4. */
+int vdnn_network_dp_mode(vdnn_network* net);
+int vdnn_dp_slice(size_t count, int world_size, int rank, size_t* begin, size_t* end);
 /* 64-bit checksum of all weights and biases (order-dependent FNV over the raw bits). */
 int vdnn_network_weight_checksum(vdnn_network* net, uint64_t* out);
 

@@ -93,3 +93,48 @@ def test_dry_run_network_accepts_dp_configuration(vdnn):
             net.enable_dp(2, 2, b"\0" * 128)              # rank out of range
     finally:
         net.close()
+
+
+def _two_shot_rank(rank, world, port, count, out_dir):
+    """The partition arithmetic of the fused peer all-reduce (csrc/dp_peer.cu), replayed on CPU ranks over gloo: rank r
+    reduces the slice vdnn_dp_slice gives it -- the contributions of all ranks added in rank order -- and the reduced
+    slices are then handed to everybody."""
+    import ctypes as C
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    import vdnn_implementation_b200 as v
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        padded = (count + 3) // 4 * 4                     # staging buffers are padded to whole groups of 4 floats
+        mine = np.zeros(padded, np.float32)
+        mine[:count] = np.random.default_rng(100 + rank).standard_normal(count).astype(np.float32)
+        everyone = [torch.zeros(padded) for _ in range(world)]
+        dist.all_gather(everyone, torch.from_numpy(mine))                       # "peer-mapped arenas"
+        b, e = C.c_size_t(), C.c_size_t()
+        assert v.lib().vdnn_dp_slice(count, world, rank, C.byref(b), C.byref(e)) == 0
+        assert b.value % 4 == 0 and e.value % 4 == 0 and b.value <= e.value <= padded
+        reduced = np.zeros(e.value - b.value, np.float32)
+        for r in range(world):                                                   # rank order, as the kernel adds
+            reduced += everyone[r].numpy()[b.value:e.value]
+        bounds = [None] * world
+        dist.all_gather_object(bounds, (b.value, e.value))
+        assert bounds[0][0] == 0 and bounds[-1][1] == padded                     # the slices tile the buffer ...
+        assert all(bounds[i][1] == bounds[i + 1][0] for i in range(world - 1))   # ... without gap or overlap
+        pieces = [None] * world
+        dist.all_gather_object(pieces, reduced)                                  # "stores into every peer's arena"
+        total = np.concatenate(pieces)
+        want = torch.from_numpy(mine.copy())
+        dist.all_reduce(want, op=dist.ReduceOp.SUM)
+        np.save(os.path.join(out_dir, f"two_shot_{count}_{rank}.npy"), np.stack([total, want.numpy()]))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,count", [(2, 1000), (2, 7), (3, 4097), (4, 2)])
+def test_two_shot_slices_cover_the_gradient_and_sum_like_allreduce(vdnn, tmp_path, world, count):
+    mp.spawn(_two_shot_rank, args=(world, _free_port(), count, str(tmp_path)), nprocs=world, join=True)
+    results = [np.load(tmp_path / f"two_shot_{count}_{r}.npy") for r in range(world)]
+    for r in range(world):
+        assert np.array_equal(results[r][0], results[0][0])                      # every rank ends with the same bits
+        assert np.allclose(results[r][0], results[r][1], rtol=1e-6, atol=1e-6)   # and with the all-reduce sum

@@ -103,6 +103,17 @@ def test_convolution_trio(vdnn, oracle, case, algo, engine):
         bupd = dev(bias)
         ops.conv_bwd_bias(n, k, P * Q, dyd, bupd, alpha=-lr, beta=1.0)
         assert rel_err(host(bupd), oracle.conv_bwd_bias(dy, alpha=-lr, beta=1.0, db=bias)) < TOL
+        # both gradients in one call (where the filter gradient prepares dy as operand images, that pass sums dy per
+        # channel): folded into the parameters, then staged
+        wupd, bupd = dev(wt), dev(bias)
+        ops.conv_bwd_filter_bias(d, xd, dyd, wupd, bupd, alpha=-lr, beta=1.0, alpha_b=-lr, beta_b=1.0, algo_mode=algo, workspace=ws,
+                                 workspace_bytes=ws_bytes)
+        assert rel_err(host(wupd), oracle.conv_bwd_filter(x, dy, wt.shape, (pad, pad), (st, st), alpha=-lr, beta=1.0, dw=wt)) < TOL
+        assert rel_err(host(bupd), oracle.conv_bwd_bias(dy, alpha=-lr, beta=1.0, db=bias)) < TOL
+        gd, gb = torch.full((k, c, r, r), 5.0, device="cuda"), torch.full((k,), 9.0, device="cuda")
+        ops.conv_bwd_filter_bias(d, xd, dyd, gd, gb, algo_mode=algo, workspace=ws, workspace_bytes=ws_bytes)
+        assert rel_err(host(gd), oracle.conv_bwd_filter(x, dy, wt.shape, (pad, pad), (st, st))) < TOL
+        assert rel_err(host(gb), oracle.conv_bwd_bias(dy)) < TOL
         assert ops.engine_status() == 0
     finally:
         _engine(vdnn, "auto")

@@ -90,6 +90,7 @@ SIGNATURES = {
     "vdnn_conv_bwd_data": (_I, [_D, _I, _F, _P, _P, _F, _P, _P, _Z, _P]),
     "vdnn_conv_bwd_bias": (_I, [_I, _I, _I, _F, _P, _F, _P, _P]),
     "vdnn_conv_bwd_filter": (_I, [_D, _I, _F, _P, _P, _F, _P, _P, _Z, _P]),
+    "vdnn_conv_bwd_filter_bias": (_I, [_D, _I, _F, _P, _P, _F, _P, _F, _F, _P, _P, _Z, _P]),
     "vdnn_conv_bwd_filter_static": (_I, [_D, _F, _P, _P, _F, _P, _P]),
     "vdnn_sgemm_workspace_bytes": (_Z, [_I, _I, _I, _I]),
     "vdnn_sgemm": (_I, [_I, _I, _I, _I, _I, _F, _P, _I, _P, _I, _F, _P, _I, _I, _P, _Z, _P]),
@@ -137,6 +138,8 @@ SIGNATURES = {
     "vdnn_network_timeline": (_I, [_P, _P]),
     "vdnn_dp_unique_id": (_I, [C.c_char_p]),
     "vdnn_network_enable_dp": (_I, [_P, _I, _I, C.c_char_p]),
+    "vdnn_network_dp_mode": (_I, [_P]),
+    "vdnn_dp_slice": (_I, [_Z, _I, _I, C.POINTER(_Z), C.POINTER(_Z)]),
     "vdnn_network_weight_checksum": (_I, [_P, C.POINTER(C.c_uint64)]),
     "vdnn_host_fill_normal": (None, [_P, _Z, C.c_uint64, _F, _F]),
     "vdnn_host_fill_uniform": (None, [_P, _Z, C.c_uint64, _F, _F]),

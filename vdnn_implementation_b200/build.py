@@ -17,7 +17,7 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-std=c++17", "-O3", "-lineinfo", "-I", os.path.join(ROOT, "include"), "-I", CSRC,
           "-ccbin", "/usr/bin/g++" if os.path.exists("/usr/bin/g++") else "g++"]
 
-CUDA_SOURCES = ["elementwise.cu", "conv_api.cu", "layer.cu", "network.cu"]
+CUDA_SOURCES = ["elementwise.cu", "conv_api.cu", "dp_peer.cu", "layer.cu", "network.cu"]
 HOST_SOURCES = ["pool_alloc.cpp", "host_rng.cpp", "dp_nccl.cpp", "network_abi.cpp"]
 # every header under csrc/ (a source is rebuilt when any of them is newer) plus the two public ones
 HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))) + [

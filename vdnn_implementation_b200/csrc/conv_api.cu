@@ -425,7 +425,7 @@ int contract_tma(const tma::Problem& q, const float* src, const char* b_tiles, E
 // Filter gradient on the TMA-fed engine, in slabs of whole images where the four operand images would pass the budget:
 // every slab adds its pixels' share, dw = alpha * (sum over slabs) + beta * dw.
 int wgrad_tma(const tma::WgradProblem& q, const float* x, const float* dy, char* ws, size_t ws_bytes, float* dw, float alpha,
-              float beta, cudaStream_t stream) {
+              float beta, cudaStream_t stream, float* bias_sums = nullptr, float bias_scale = 0.0f) {
     tma::WgradProblem one = q;
     one.n = 1;
     const int slab = tma_slab_images(q.n, tma::wgrad_image_bytes(one));
@@ -439,7 +439,8 @@ int wgrad_tma(const tma::WgradProblem& q, const float* x, const float* dy, char*
         int splits = 1;
         float* partial = nullptr;
         const float b = n0 == 0 ? beta : 1.0f;
-        const int st = tma::wgrad_launch(part, x + n0 * x_img, dy + n0 * dy_img, ws, dw, alpha, b, stream, &splits, &partial);
+        const int st = tma::wgrad_launch(part, x + n0 * x_img, dy + n0 * dy_img, ws, dw, alpha, b, stream, &splits, &partial,
+                                         bias_sums, bias_scale);
         if (st != VDNN_OK) return st;
         if (splits > 1) {
             reduce_partials_kernel<<<stream_blocks(elems), 256, 0, stream>>>(elems, splits, alpha, b, partial, dw);
@@ -717,6 +718,27 @@ int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, co
     }
     return contract<XGatherFiltRows, SplitDense, true, true>(A, B, e, crs, d->k, d->n * pq, static_cast<size_t>(d->k) * crs, 0,
                                                              algo_mode, workspace, workspace_bytes, as_stream(stream));
+}
+
+// Bias gradient and filter gradient of one convolution in one call (layer.cu:631-660: cudnnConvolutionBackwardBias, then
+// cudnnConvolutionBackwardFilter).  Where the filter gradient runs on the TMA-fed engine, the pass that rewrites dy into
+// operand images also forms the per-channel sums of dy, so dy is read once less and one kernel launch is saved; anywhere
+// else this is vdnn_conv_bwd_bias followed by vdnn_conv_bwd_filter.  beta_b must be 0 or 1 for the combined form.
+int vdnn_conv_bwd_filter_bias(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* x, const float* dy, float beta,
+                              float* dw, float alpha_b, float beta_b, float* db, void* workspace, size_t workspace_bytes,
+                              void* stream) {
+    int P, Q;
+    if (!x || !dy || !dw || !db || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
+    const bool combined = algo_mode == VDNN_ALGO_PERF_OPT && !is_full_extent(d) && tma_wgrad_shape(d) && g_engine != VDNN_ENGINE_FFMA && workspace &&
+                          (reinterpret_cast<uintptr_t>(workspace) & 127u) == 0 && (beta_b == 0.0f || beta_b == 1.0f) &&
+                          fits_int32(d, P, Q);
+    if (!combined) {
+        const int st = vdnn_conv_bwd_bias(d->n, d->k, P * Q, alpha_b, dy, beta_b, db, stream);
+        return st != VDNN_OK ? st : vdnn_conv_bwd_filter(d, algo_mode, alpha, x, dy, beta, dw, workspace, workspace_bytes, stream);
+    }
+    if (beta_b == 0.0f) VDNN_CUDA(cudaMemsetAsync(db, 0, sizeof(float) * d->k, as_stream(stream)));
+    return wgrad_tma(wgrad_problem(d, P, Q), x, dy, static_cast<char*>(workspace), workspace_bytes, dw, alpha, beta, as_stream(stream),
+                     db, alpha_b);
 }
 
 }  // extern "C"

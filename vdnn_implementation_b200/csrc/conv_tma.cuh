@@ -754,8 +754,12 @@ wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ C
 // NCHW fp32 -> two channels-last images: hi = tf32(x) (round to nearest), lo = x - hi.  One block moves 32 channels x
 // 128 pixels of one image through shared memory: reads run along the pixels of a channel, writes along the channels
 // of a pixel, both in full 128-byte lines.
+// SUMS: the pass also adds scale * (sum over the block's pixels) of every channel into sums[channel] (fp32 atomics): the
+// bias gradient of a convolution is the per-channel sum of dy, and this pass reads all of dy anyway.
+template <bool SUMS>
 __global__ void __launch_bounds__(256) nchw_to_split_nhwc_kernel(const float* __restrict__ x, float* __restrict__ hi,
-                                                                 float* __restrict__ lo, int C, int HW) {
+                                                                 float* __restrict__ lo, int C, int HW, float* __restrict__ sums,
+                                                                 float scale) {
     __shared__ float tile[32][TR_PIX + 1];
     const int n = blockIdx.z, c0 = blockIdx.y * 32, p0 = blockIdx.x * TR_PIX;
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
@@ -764,10 +768,18 @@ __global__ void __launch_bounds__(256) nchw_to_split_nhwc_kernel(const float* __
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const int c = warp * 4 + j;
+        float part = 0.0f;
 #pragma unroll
         for (int q = 0; q < TR_PIX / 32; ++q) {
             const int pix = q * 32 + lane;
-            tile[c][pix] = pix < npix ? __ldg(src + static_cast<size_t>(c) * HW + pix) : 0.0f;
+            const float v = pix < npix ? __ldg(src + static_cast<size_t>(c) * HW + pix) : 0.0f;
+            tile[c][pix] = v;
+            if (SUMS) part += v;
+        }
+        if (SUMS) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+            if (lane == 0) atomicAdd(sums + c0 + c, scale * part);
         }
     }
     __syncthreads();
@@ -872,7 +884,7 @@ int launch_bn(const Problem& q, const float* src, char* images, const char* b_ti
     const int hw = q.in_h * q.in_w;
     dim3 tgrid(ceil_div(hw, TR_PIX), q.cin / 32, q.n);
     if (tgrid.y > 65535u || tgrid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
-    nchw_to_split_nhwc_kernel<<<tgrid, 256, 0, stream>>>(src, hi, lo, q.cin, hw);
+    nchw_to_split_nhwc_kernel<false><<<tgrid, 256, 0, stream>>>(src, hi, lo, q.cin, hw, nullptr, 0.0f);
     VDNN_LAUNCHED();
     dim3 grid(ceil_div(p.total_boxes, BOXES), ceil_div(q.n_cols, BN), splits);
     if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
@@ -1044,9 +1056,10 @@ inline size_t wgrad_partial_bytes(const WgradProblem& q) {
     return splits > 1 ? static_cast<size_t>(splits) * q.k * q.c * q.R * q.S * sizeof(float) : 0;
 }
 
+// bias_sums (may be null): K floats that receive += bias_scale * (per-channel sums of dy) from the dy transform pass.
 template <int BN>
 int wgrad_launch_bn(const WgradProblem& q, const float* x, const float* dy, char* ws, float* dw, float alpha, float beta,
-                    cudaStream_t stream, int* splits_out, float** partial_out) {
+                    cudaStream_t stream, int* splits_out, float** partial_out, float* bias_sums, float bias_scale) {
     typedef Config<BN> Cfg;
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
@@ -1082,9 +1095,10 @@ int wgrad_launch_bn(const WgradProblem& q, const float* x, const float* dy, char
     if ((st = make_image_map(&myl, yl, q.n, q.p, q.q, q.k, bw, p.bh, sw)) != VDNN_OK) return st;
     dim3 tx(ceil_div(q.h * q.w, TR_PIX), q.c / 32, q.n), ty(ceil_div(q.p * q.q, TR_PIX), q.k / 32, q.n);
     if (tx.y > 65535u || tx.z > 65535u || ty.y > 65535u) return VDNN_ERR_UNSUPPORTED;
-    nchw_to_split_nhwc_kernel<<<tx, 256, 0, stream>>>(x, xh, xl, q.c, q.h * q.w);
+    nchw_to_split_nhwc_kernel<false><<<tx, 256, 0, stream>>>(x, xh, xl, q.c, q.h * q.w, nullptr, 0.0f);
     VDNN_LAUNCHED();
-    nchw_to_split_nhwc_kernel<<<ty, 256, 0, stream>>>(dy, yh, yl, q.k, q.p * q.q);
+    if (bias_sums) nchw_to_split_nhwc_kernel<true><<<ty, 256, 0, stream>>>(dy, yh, yl, q.k, q.p * q.q, bias_sums, bias_scale);
+    else nchw_to_split_nhwc_kernel<false><<<ty, 256, 0, stream>>>(dy, yh, yl, q.k, q.p * q.q, nullptr, 0.0f);
     VDNN_LAUNCHED();
     dim3 grid(ceil_div(p.row_groups, BOXES), ceil_div(q.k, BN), splits);
     if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
@@ -1101,11 +1115,11 @@ inline size_t wgrad_image_bytes(const WgradProblem& q) {
 }
 
 inline int wgrad_launch(const WgradProblem& q, const float* x, const float* dy, char* ws, float* dw, float alpha, float beta,
-                        cudaStream_t stream, int* splits, float** partial) {
+                        cudaStream_t stream, int* splits, float** partial, float* bias_sums = nullptr, float bias_scale = 0.0f) {
     const int bn = tc::tile_n(q.k);
-    if (bn == 64) return wgrad_launch_bn<64>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial);
-    if (bn == 128) return wgrad_launch_bn<128>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial);
-    return wgrad_launch_bn<256>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial);
+    if (bn == 64) return wgrad_launch_bn<64>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale);
+    if (bn == 128) return wgrad_launch_bn<128>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale);
+    return wgrad_launch_bn<256>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale);
 }
 
 }  // namespace tma

@@ -13,6 +13,7 @@ namespace vdnn {
 int dp_unique_id(char* out128);
 int dp_init(vdnnContext* ctx, int rank, int world, const char* unique_id128);
 int dp_allreduce_sum(vdnnContext* ctx, float* buf, size_t count, cudaStream_t stream);
+int dp_map_peers(vdnnContext* ctx, cudaStream_t stream);
 void dp_shutdown(vdnnContext* ctx);
 }
 

@@ -245,13 +245,9 @@ int Layer::initializeFullyConnectedFilterAndBias() {
                         &filterData, &biasData);
 }
 
-int Layer::enableGradientStaging() {
-    if (!HasWeights() || gradFilter || handle->dry_run) return VDNN_OK;
-    const size_t wn = static_cast<size_t>(FilterDataSize());
-    // One allocation for filter and bias gradients so that a single all-reduce covers both.
-    if (cudaMalloc(reinterpret_cast<void**>(&gradFilter), sizeof(float) * (wn + c_out)) != cudaSuccess) return VDNN_ERR_CUDA;
-    gradBias = gradFilter + wn;
-    return VDNN_OK;
+void Layer::setGradientStaging(float* buffer) {
+    gradFilter = buffer;
+    gradBias = buffer ? buffer + static_cast<size_t>(FilterDataSize()) : NULL;
 }
 
 /* ------------------------------------------------------------------ dispatch (layer.cu:489-537) */
@@ -375,17 +371,17 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
         if (f != 0) return f;
     }
     // bias, then filter: gradient folded into the parameters (alpha = -lr, beta = 1), or written to
-    // the staging buffer when gradients are all-reduced across ranks first
-    DEV(vdnn_conv_bwd_bias(n_out, c_out, h_out * w_out, staged ? 1.0f : lr, (const float*)diffData, staged ? 0.0f : 1.0f,
-                           staged ? gradBias : (float*)biasData, *stream_compute));
+    // the staging buffer when gradients are all-reduced across ranks first.  One call: where the filter gradient
+    // prepares dy as operand images, that pass forms the bias sums as well.
     if (workSpace != NULL) curWorkSpace = workSpace;
     else if (bwdFilterWorkSpaceSize > 0) {
         const int a = handle->alloc(&curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, isDynamic, {*stream_compute});
         if (a != 0) return a;
     }
-    DEV(vdnn_conv_bwd_filter(&d, opMode[2], staged ? 1.0f : lr, (const float*)srcData, (const float*)diffData,
-                             staged ? 0.0f : 1.0f, staged ? gradFilter : (float*)filterData, curWorkSpace,
-                             workSpace != NULL ? caller_workspace_bytes(handle, workSpace) : bwdFilterWorkSpaceSize, *stream_compute));
+    DEV(vdnn_conv_bwd_filter_bias(&d, opMode[2], staged ? 1.0f : lr, (const float*)srcData, (const float*)diffData,
+                                  staged ? 0.0f : 1.0f, staged ? gradFilter : (float*)filterData,
+                                  staged ? 1.0f : lr, staged ? 0.0f : 1.0f, staged ? gradBias : (float*)biasData, curWorkSpace,
+                                  workSpace != NULL ? caller_workspace_bytes(handle, workSpace) : bwdFilterWorkSpaceSize, *stream_compute));
     MARK(ev_bwd_done);
     if (workSpace == NULL && bwdFilterWorkSpaceSize > 0)
         return handle->release(curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, {*stream_compute});

@@ -82,6 +82,12 @@ struct vdnnContext {
     // data parallelism
     int dp_rank = 0, dp_world = 1;
     void* nccl_comm = nullptr;
+    // One allocation holds the flag words of the fused peer all-reduce and every layer's gradient staging buffer
+    // (csrc/dp_peer.h); dp_peer[r] is rank r's arena as mapped here when the fused path is on (dp_fused).
+    float* dp_arena = nullptr;
+    size_t dp_arena_floats = 0;
+    float* dp_peer[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    bool dp_fused = false;
 
     // NULL when the context runs without a device (no events exist)
     static cudaEvent_t event(const std::vector<cudaEvent_t>& v, int id) { return v.empty() ? nullptr : v[id]; }
@@ -190,8 +196,9 @@ public:
     void    spec(vdnn_layer_spec* out);
     bool    ok()                     { return constructed; }
 
-    // Data-parallel staging: gradients are produced here instead of being folded into the weights.
-    int     enableGradientStaging();
+    // Data-parallel staging: gradients are produced in `buffer` (FilterDataSize() + OutputC() floats, owned by the
+    // network) instead of being folded into the weights.
+    void    setGradientStaging(float* buffer);
     float*  GradFilter()             { return gradFilter; }
     float*  GradBias()               { return gradBias;   }
 

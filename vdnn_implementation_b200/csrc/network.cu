@@ -14,6 +14,7 @@
 #include <string.h>
 
 #include "dp_nccl.h"
+#include "dp_peer.h"
 
 namespace vdnn { extern unsigned long long g_kernel_launches; }
 
@@ -287,9 +288,9 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
 Network::~Network() {
     if (!ctx.dry_run) cudaDeviceSynchronize();
     vdnn::dp_shutdown(&ctx);
+    if (ctx.dp_arena) cudaFree(ctx.dp_arena);
     for (int i = 0; i < DEFAULT_NUM_LAYER; i++) {
         if (layer[i]) {
-            if (layer[i]->GradFilter()) cudaFree(layer[i]->GradFilter());
             delete layer[i];
         }
         if (offloadedSrcData_h[i]) cudaFreeHost(offloadedSrcData_h[i]);
@@ -666,8 +667,18 @@ int Network::reduceAndApply(int l) {
     Layer* L = layer[l];
     const size_t wn = L->FilterDataSize(), bn = L->OutputC();
     NET_CU(cudaStreamWaitEvent(ctx.stream_comm, ctx.ev_bwd_done[l], 0));
-    NET_TRY(vdnn::dp_allreduce_sum(&ctx, L->GradFilter(), wn + bn, ctx.stream_comm));
     const float lr = ctx.learning_rate * -1.0f;
+    if (ctx.dp_fused) {
+        // reduce-scatter by peer loads, all-gather by peer stores and the SGD step in one kernel (csrc/dp_peer.cu);
+        // its status word sits beside the engine's (read by synchronize())
+        NET_TRY(vdnn::dp_peer_allreduce_sgd(ctx.dp_peer, ctx.dp_world, ctx.dp_rank, dpOffset[l], wn + bn, l,
+                                            static_cast<unsigned>(stepCounter + 1), lr, (float*)L->FilterData(), wn,
+                                            (float*)L->BiasData(), reinterpret_cast<int*>(loss_h + 3), ctx.stream_comm));
+        NET_CU(cudaEventRecord(ctx.ev_weights_ready[l], ctx.stream_comm));
+        ctx.weights_pending[l] = 1;
+        return VDNN_OK;
+    }
+    NET_TRY(vdnn::dp_allreduce_sum(&ctx, L->GradFilter(), wn + bn, ctx.stream_comm));
     NET_TRY(vdnn_axpy(wn, lr, L->GradFilter(), (float*)L->FilterData(), ctx.stream_comm));
     NET_TRY(vdnn_axpy(bn, lr, L->GradBias(), (float*)L->BiasData(), ctx.stream_comm));
     NET_CU(cudaEventRecord(ctx.ev_weights_ready[l], ctx.stream_comm));
@@ -763,7 +774,8 @@ int Network::synchronize() {
     NET_CU(cudaStreamSynchronize(ctx.stream_h2d));
     NET_CU(cudaStreamSynchronize(ctx.stream_comm));
     // a bounded wait that ran out inside a contraction kernel left output tiles unwritten: the steps since are void
-    if (loss_h && *reinterpret_cast<volatile int*>(loss_h + 2) != 0) return VDNN_ERR_TIMEOUT;
+    if (loss_h && (*reinterpret_cast<volatile int*>(loss_h + 2) != 0 || *reinterpret_cast<volatile int*>(loss_h + 3) != 0))
+        return VDNN_ERR_TIMEOUT;
     return VDNN_OK;
 }
 
@@ -932,9 +944,41 @@ int Network::enableDataParallel(int rank, int world, const char* unique_id128) {
     if (world == 1) return VDNN_OK;
     if (ctx.dry_run) { ctx.dp_rank = rank; ctx.dp_world = world; return VDNN_OK; }
     NET_TRY(vdnn::dp_init(&ctx, rank, world, unique_id128));
-    for (int l = 0; l < numLayers; ++l) NET_TRY(layer[l]->enableGradientStaging());
+    // one arena: the flag words of the fused all-reduce, then every layer's staging buffer (filter gradient followed by
+    // bias gradient, so that one collective covers both), each starting on a 128-byte boundary
+    size_t floats = vdnn::DP_FLAG_WORDS;
+    dpOffset.assign(numLayers, 0);
+    for (int l = 0; l < numLayers; ++l) {
+        if (!layer[l]->HasWeights()) continue;
+        dpOffset[l] = floats;
+        floats += (static_cast<size_t>(layer[l]->FilterDataSize()) + layer[l]->OutputC() + 31) / 32 * 32;
+    }
+    NET_CU(cudaMalloc(reinterpret_cast<void**>(&ctx.dp_arena), floats * sizeof(float)));
+    NET_CU(cudaMemset(ctx.dp_arena, 0, floats * sizeof(float)));
+    ctx.dp_arena_floats = floats;
+    for (int l = 0; l < numLayers; ++l)
+        if (layer[l]->HasWeights()) layer[l]->setGradientStaging(ctx.dp_arena + dpOffset[l]);
+    // VDNN_DP_FUSED=1: all-reduce and SGD step in one kernel over peer-mapped arenas instead of NCCL + axpy.  Needs every
+    // rank's arena mapped here; when that fails on any rank the NCCL path stays in charge on this rank, so the ranks
+    // must agree: the outcome is reduced (a 1-float NCCL all-reduce of "I can") before the mode is switched.
+    const char* fused = getenv("VDNN_DP_FUSED");
+    if (fused && *fused && *fused != '0' && world <= vdnn::DP_MAX_RANKS && numLayers <= vdnn::DP_MAX_LAYERS) {
+        const int mapped = vdnn::dp_map_peers(&ctx, ctx.stream_comm);
+        float* vote = ctx.dp_arena + vdnn::DP_FLAG_WORDS - 1;           // last flag word is unused by the kernels
+        const float mine = mapped == VDNN_OK ? 1.0f : 0.0f;
+        NET_CU(cudaMemcpyAsync(vote, &mine, sizeof(float), cudaMemcpyHostToDevice, ctx.stream_comm));
+        NET_TRY(vdnn::dp_allreduce_sum(&ctx, vote, 1, ctx.stream_comm));
+        float sum = 0.0f;
+        NET_CU(cudaMemcpyAsync(&sum, vote, sizeof(float), cudaMemcpyDeviceToHost, ctx.stream_comm));
+        NET_CU(cudaStreamSynchronize(ctx.stream_comm));
+        NET_CU(cudaMemsetAsync(vote, 0, sizeof(float), ctx.stream_comm));
+        ctx.dp_fused = sum > world - 0.5f;
+        if (!ctx.dp_fused && ctx.verbose) fprintf(stderr, "fused peer all-reduce unavailable (%g of %d ranks could map their peers): using NCCL\n", sum, world);
+    }
     return VDNN_OK;
 }
+
+int Network::dpMode() const { return ctx.dp_world <= 1 ? 0 : (ctx.dp_fused ? 2 : 1); }
 
 int Network::weightChecksum(uint64_t* out) {
     if (!out) return VDNN_ERR_BAD_ARG;

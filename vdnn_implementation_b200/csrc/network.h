@@ -69,6 +69,7 @@ public:
     int             timeline(float* out);
     int             enableDataParallel(int rank, int world, const char* unique_id128);
     int             weightChecksum(uint64_t* out);
+    int             dpMode() const;            // 0 single device, 1 NCCL all-reduce + axpy, 2 fused peer all-reduce + SGD
 
 private:
     void            init(const vdnn_network_config& cfg, bool dry_run);
@@ -128,6 +129,7 @@ private:
     cudaEvent_t         ev_loss;
     cudaEvent_t         ev_step_end;
     std::vector<std::vector<float>> capDst, capGrad;
+    std::vector<size_t> dpOffset;              // data parallel: each layer's staging buffer inside ctx.dp_arena (floats)
     unsigned long long  launchesAtStepStart, launchesLastStep;
 };
 

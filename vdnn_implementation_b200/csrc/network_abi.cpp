@@ -95,6 +95,7 @@ int vdnn_network_timeline(vdnn_network* net, float* out) { NET(net); return net-
 
 int vdnn_dp_unique_id(char* out128) { return vdnn::dp_unique_id(out128); }
 int vdnn_network_enable_dp(vdnn_network* net, int rank, int world, const char* id) { NET(net); return net->impl->enableDataParallel(rank, world, id); }
+int vdnn_network_dp_mode(vdnn_network* net) { NET(net); return net->impl->dpMode(); }
 int vdnn_network_weight_checksum(vdnn_network* net, uint64_t* out) { NET(net); return net->impl->weightChecksum(out); }
 
 }  // extern "C"

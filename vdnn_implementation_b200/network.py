@@ -167,6 +167,10 @@ class Network:
     def enable_dp(self, rank, world_size, unique_id):
         check(lib().vdnn_network_enable_dp(self._h, rank, world_size, unique_id), "enable_dp")
 
+    def dp_mode(self):
+        """0 single device, 1 NCCL all-reduce + axpy, 2 fused peer all-reduce + SGD kernel."""
+        return lib().vdnn_network_dp_mode(self._h)
+
     def weight_checksum(self):
         out = C.c_uint64()
         check(lib().vdnn_network_weight_checksum(self._h, C.byref(out)), "weight_checksum")
@@ -195,7 +199,8 @@ def dp_consistency_check(model, policy, per_rank, steps, lr, dist, local_device,
     the same steps alone on the whole batches.  Gradients are batch sums (layer.cu:631-660, 736-760 of the reference
     fold alpha = -lr sums into the weights), so the sum over the shards' gradients is the whole batch's gradient and
     the two runs must agree to rounding.  Returns on rank 0 a dict with `checksums` (one per rank; equal = weights
-    bit-identical across ranks), `max_rel_err_vs_single_gpu`, `grad_buffer_bytes`, `engine_status`; None elsewhere."""
+    bit-identical across ranks), `max_rel_err_vs_single_gpu`, `grad_buffer_bytes`, `engine_status`, `dp_mode` (1 NCCL,
+    2 the fused peer kernel, chosen by VDNN_DP_FUSED in the environment); None elsewhere."""
     import torch
     from . import ops
     rank, world = dist.get_rank(), dist.get_world_size()
@@ -221,6 +226,7 @@ def dp_consistency_check(model, policy, per_rank, steps, lr, dist, local_device,
     sums = [None] * world
     dist.all_gather_object(sums, net.weight_checksum())
     stats = net.stats()
+    mode = net.dp_mode()
     with_weights = [l for l in range(net.num_layers) if net.tensor_size(l, abi.TENSOR_WEIGHT) > 0]
     probe = (with_weights[0], with_weights[len(with_weights) // 2], with_weights[-1])
     dp_weights = {l: net.weights(l) for l in probe}
@@ -241,6 +247,6 @@ def dp_consistency_check(model, policy, per_rank, steps, lr, dist, local_device,
                 errs.append(float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-30)))
         one.close()
         result = {"checksums": [str(s) for s in sums], "grad_buffer_bytes": stats["grad_buffer_bytes"], "engine_status": status,
-                  "max_rel_err_vs_single_gpu": max(errs)}
+                  "max_rel_err_vs_single_gpu": max(errs), "dp_mode": mode}
     dist.barrier()
     return result

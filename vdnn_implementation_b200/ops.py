@@ -57,6 +57,12 @@ def conv_bwd_filter(desc, x, dy, dw, alpha=1.0, beta=0.0, algo_mode=0, workspace
                                      workspace_bytes, _s(stream)), "conv_bwd_filter")
 
 
+def conv_bwd_filter_bias(desc, x, dy, dw, db, alpha=1.0, beta=0.0, alpha_b=1.0, beta_b=0.0, algo_mode=0, workspace=None,
+                         workspace_bytes=0, stream=0):
+    check(lib().vdnn_conv_bwd_filter_bias(C.byref(desc), algo_mode, alpha, _p(x), _p(dy), beta, _p(dw), alpha_b, beta_b, _p(db),
+                                          _p(workspace), workspace_bytes, _s(stream)), "conv_bwd_filter_bias")
+
+
 STATIC_SCRATCH_BYTES = 16 << 20
 
 
