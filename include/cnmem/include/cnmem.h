@@ -65,6 +65,14 @@ cnmemStatus_t vdnnPoolFreeAfter(void* ptr, const cudaStream_t* streams, int numS
  * covers part of the returned block.  Among the free blocks that fit, the one that becomes usable
  * soonest is chosen (no pending event, else the oldest pending events), then the tightest fit. */
 cnmemStatus_t vdnnPoolMallocFor(void** ptr, size_t size, const cudaStream_t* streams, int numStreams);
+/* The same with a hint: transient != 0 marks a block that is given back within the same layer call (workspace).  A pool
+ * that is not packed places those at the end of a free range, highest address first, so that they do not cut the
+ * ranges the long-lived tensors grow into.  Byte counts are the same. */
+/* Keeps the top `bytes` of a pool that is not packed for transient blocks: other blocks go there only when they fit
+ * nowhere else.  With the reserve at least as large as the largest workspace, that workspace always finds its bytes in
+ * one piece, however the tensors below are spread by placement by pending events. */
+cnmemStatus_t vdnnPoolSetTransientReserve(size_t bytes);
+cnmemStatus_t vdnnPoolMallocKindFor(void** ptr, size_t size, const cudaStream_t* streams, int numStreams, int transient);
 /* Same as vdnnPoolFreeAfter, for bytes whose last reader has not been enqueued yet (a copy that the
  * host will submit later, in an order of its own choosing).  The bytes count as free, but carry a "hold"
  * named by `token` (> 0).  vdnnPoolResolve(token, stream), called once that reader has been enqueued on

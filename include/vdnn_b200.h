@@ -342,6 +342,15 @@ int vdnn_network_layer_algos(vdnn_network* net, int layer, int* out3);
  * bytes moved, the host-side allocation order and the pool's byte counts are the same either way.
  * forward_order = 1 (or the environment variable VDNN_OFFLOAD_ORDER=forward) restores layer order. */
 int vdnn_network_set_offload_order(vdnn_network* net, int forward_order);
+/* Lean variant of VDNN_ALL.  Not in the reference and never the default, because it changes the bytes moved and the
+ * allocation trace: the srcData of a ReLU layer that follows a CONV / FC layer is released after that ReLU's forward
+ * instead of being offloaded, and the ReLU's backward takes its mask from dstData (y > 0 exactly where x > 0), which
+ * the prefetch for the next layer brings back anyway; CONV / FC backward never read their own output
+ * (layer.cu:616-660, 721-760).  Results are bit-identical to VDNN_ALL; VGG16 moves about half the bytes.
+ * on = 1 / 0: networks created from now on follow / do not follow it; on < 0: the environment variable
+ * VDNN_LEAN_OFFLOAD decides (the initial state).  vdnn_network_lean reports what a network was built with. */
+int vdnn_set_lean_offload(int on);
+int vdnn_network_lean(const vdnn_network* net);
 /* Per-layer timeline of the last profiled step, in milliseconds from the step's first event:
  * out[8*l + 0..7] = forward begin, forward end, offload begin, offload end, backward begin, backward end,
  * prefetch begin, prefetch end of layer l (negative where the layer has no such event).  `out` holds

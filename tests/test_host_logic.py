@@ -315,3 +315,30 @@ def test_padded_pooling_is_refused(vdnn):
     specs = [(7, 2, 3, 8, 8, 1, 1, 2, 2, 0, 2, 2), (6, 2, 3, 5, 5, 0, 0, 0, 0, 0, 0, 0)]
     with pytest.raises(vdnn.VdnnError):
         vdnn.Network("CUSTOM_CNN", "VDNN_NONE", "VDNN_MEMORY_OPT_ALGO", device=-1, custom_layers=specs)
+
+
+def test_lean_offload_schedule_on_the_bookkeeping_pool(vdnn):
+    """Lean VDNN_ALL (opt-in, not in the reference): ReLU inputs behind CONV / FC layers are released instead of
+    offloaded.  Replayed without a device: fewer offloaded bytes (VGG16: about half), prefetches match offloads, a lower
+    peak, the pool back at the same level after every step; the other policies do not change with the switch."""
+    def run(policy, lean):
+        net = vdnn.Network("VGG16_128", policy, "VDNN_PERF_OPT_ALGO", device=-1, pool_bytes=int(24e9), lean_offload=lean)
+        try:
+            used = []
+            for _ in range(3):
+                net.step()
+                used.append(net.stats()["pool_used_bytes"])
+            return net.stats(), used, net.lean_offload
+        finally:
+            net.close()
+    full, used_full, flag_full = run("VDNN_ALL", False)
+    lean, used_lean, flag_lean = run("VDNN_ALL", True)
+    assert (flag_full, flag_lean) == (False, True)
+    assert lean["offload_bytes"] == lean["prefetch_bytes"] == lean["pinned_bytes"]
+    assert 0.45 * full["offload_bytes"] < lean["offload_bytes"] < 0.6 * full["offload_bytes"]
+    assert lean["pool_peak_bytes"] < full["pool_peak_bytes"]
+    assert used_lean == used_full and len(set(used_lean)) == 1
+    for policy in ("VDNN_CONV", "VDNN_NONE"):
+        a, _, _ = run(policy, False)
+        b, _, _ = run(policy, True)
+        assert a["offload_bytes"] == b["offload_bytes"] and a["pool_peak_bytes"] == b["pool_peak_bytes"]

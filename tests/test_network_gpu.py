@@ -189,8 +189,9 @@ def test_offload_bytes_and_overlap_are_reported(vdnn, oracle):
         net.close()
 
 
-def _steps(vdnn, pool_bytes, forward_order, model="ALEXNET", batch=32, layers=(0, 6, 13, 17), steps=2):
-    net = vdnn.Network(model, "VDNN_ALL", "VDNN_PERF_OPT_ALGO", batch_size=batch, pool_bytes=pool_bytes, learning_rate=1e-4)
+def _steps(vdnn, pool_bytes, forward_order, model="ALEXNET", batch=32, layers=(0, 6, 13, 17), steps=2, lean=None,
+           algo="VDNN_PERF_OPT_ALGO"):
+    net = vdnn.Network(model, "VDNN_ALL", algo, batch_size=batch, pool_bytes=pool_bytes, learning_rate=1e-4, lean_offload=lean)
     try:
         net.set_offload_order(forward_order)
         forced = 0
@@ -201,7 +202,7 @@ def _steps(vdnn, pool_bytes, forward_order, model="ALEXNET", batch=32, layers=(0
             net.backwardPropagation()
         net.synchronize()
         return ([net.weights(l) for l in layers], [net.bias(l) for l in (layers[0], layers[-1])], net.loss(), net.trace(),
-                net.stats()["pool_peak_bytes"], forced)
+                net.stats()["pool_peak_bytes"], forced, net.stats())
     finally:
         net.close()
 
@@ -219,6 +220,44 @@ def test_offload_order_is_not_observable(vdnn):
         assert rel_err(a, b) < 5e-5
     for a, b in zip(by_need[1], in_order[1]):        # bias gradients are summed with atomics: run-to-run noise
         assert rel_err(a, b) < 1e-3
+    assert vdnn.ops.engine_status() == 0
+
+
+@pytest.mark.parametrize("model,batch,layers", [("ALEXNET_LRN", 32, (0, 8, 15, 19)), ("VGG16_64", 8, (0, 5, 31, 35))])
+def test_lean_offload_moves_fewer_bytes_and_trains_the_same(vdnn, model, batch, layers):
+    """The opt-in lean form of VDNN_ALL drops the input of every ReLU that follows a CONV / FC layer instead of offloading
+    it, and takes the ReLU's mask from its output in backward.  Same step as VDNN_ALL (the mask is the same bit for bit;
+    what differs run to run is the order of the atomic sums), fewer bytes over PCIe, a lower peak, nothing leaked."""
+    full = _steps(vdnn, 8e9, False, model=model, batch=batch, layers=layers, lean=False)
+    lean = _steps(vdnn, 8e9, False, model=model, batch=batch, layers=layers, lean=True)
+    assert lean[6]["offload_bytes"] == lean[6]["prefetch_bytes"] == lean[6]["pinned_bytes"]
+    assert lean[6]["offload_bytes"] < 0.75 * full[6]["offload_bytes"]
+    assert lean[4] <= full[4] and lean[6]["pool_used_bytes"] == full[6]["pool_used_bytes"]
+    assert abs(lean[2][0] - full[2][0]) < 1e-6 and abs(lean[2][1] - full[2][1]) < 1e-5 * abs(full[2][1])
+    for a, b in zip(lean[0], full[0]):
+        assert rel_err(a, b) < 5e-5
+    for a, b in zip(lean[1], full[1]):
+        assert rel_err(a, b) < 1e-3
+    assert vdnn.ops.engine_status() == 0
+
+
+def test_workspace_reserve_keeps_a_roomy_pool_trainable(vdnn):
+    """PERF_OPT at a pool of 1.45 x the peak, where the largest workspace (1 GB of operand images at this batch size) is a
+    quarter of the pool: placement by pending events spreads the tensors, and the workspace finds its bytes in one piece
+    only because the top of the pool is kept for it.  Same step as in a roomy pool."""
+    vgg = dict(model="VGG16_64", batch=32, layers=(0, 5, 31, 35))
+    dry = vdnn.Network("VGG16_64", "VDNN_ALL", "VDNN_PERF_OPT_ALGO", batch_size=32, device=-1, pool_bytes=20e9)
+    try:
+        dry.step()
+        dry.step()
+        peak = dry.stats()["pool_peak_bytes"]
+    finally:
+        dry.close()
+    tight = _steps(vdnn, int(peak * 1.45), False, steps=3, **vgg)
+    roomy = _steps(vdnn, 12e9, False, steps=3, **vgg)
+    assert tight[3] == roomy[3] and tight[4] == roomy[4] == peak
+    for a, b in zip(tight[0], roomy[0]):
+        assert rel_err(a, b) < 1e-5
     assert vdnn.ops.engine_status() == 0
 
 

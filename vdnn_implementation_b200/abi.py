@@ -133,6 +133,8 @@ SIGNATURES = {
     "vdnn_network_get_stats": (_I, [_P, C.POINTER(NetworkStats)]),
     "vdnn_network_set_profiling": (_I, [_P, _I]),
     "vdnn_network_set_offload_order": (_I, [_P, _I]),
+    "vdnn_set_lean_offload": (_I, [_I]),
+    "vdnn_network_lean": (_I, [_P]),
     "vdnn_network_selected": (_I, [_P, C.POINTER(_I), C.POINTER(_I)]),
     "vdnn_network_layer_algos": (_I, [_P, _I, C.POINTER(_I)]),
     "vdnn_network_timeline": (_I, [_P, _P]),

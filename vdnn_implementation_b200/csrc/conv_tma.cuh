@@ -753,50 +753,60 @@ wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ C
 
 // NCHW fp32 -> two channels-last images: hi = tf32(x) (round to nearest), lo = x - hi.  One block moves 32 channels x
 // 128 pixels of one image through shared memory: reads run along the pixels of a channel, writes along the channels
-// of a pixel, both in full 128-byte lines.
+// of a pixel, both in full 128-byte lines.  A block takes `tiles_per_block` consecutive 128-pixel tiles.
 // SUMS: the pass also adds scale * (sum over the block's pixels) of every channel into sums[channel] (fp32 atomics): the
-// bias gradient of a convolution is the per-channel sum of dy, and this pass reads all of dy anyway.
+// bias gradient of a convolution is the per-channel sum of dy, and this pass reads all of dy anyway.  One atomic per
+// channel and block: with several tiles per block the atomics on one address stay a small part of the pass.
 template <bool SUMS>
 __global__ void __launch_bounds__(256) nchw_to_split_nhwc_kernel(const float* __restrict__ x, float* __restrict__ hi,
-                                                                 float* __restrict__ lo, int C, int HW, float* __restrict__ sums,
-                                                                 float scale) {
+                                                                 float* __restrict__ lo, int C, int HW, int tiles_per_block,
+                                                                 float* __restrict__ sums, float scale) {
     __shared__ float tile[32][TR_PIX + 1];
-    const int n = blockIdx.z, c0 = blockIdx.y * 32, p0 = blockIdx.x * TR_PIX;
+    const int n = blockIdx.z, c0 = blockIdx.y * 32;
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-    const float* src = x + (static_cast<size_t>(n) * C + c0) * HW + p0;
-    const int npix = min(TR_PIX, HW - p0);
+    const int quad = t & 7;                     // channels 4 * quad .. + 3
+    float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int it = 0; it < tiles_per_block; ++it) {
+        const int p0 = (blockIdx.x * tiles_per_block + it) * TR_PIX;
+        if (p0 >= HW) break;
+        if (it) __syncthreads();                // the tile of the last round has been written out
+        const float* src = x + (static_cast<size_t>(n) * C + c0) * HW + p0;
+        const int npix = min(TR_PIX, HW - p0);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int c = warp * 4 + j;
-        float part = 0.0f;
+        for (int j = 0; j < 4; ++j) {
+            const int c = warp * 4 + j;
 #pragma unroll
-        for (int q = 0; q < TR_PIX / 32; ++q) {
-            const int pix = q * 32 + lane;
-            const float v = pix < npix ? __ldg(src + static_cast<size_t>(c) * HW + pix) : 0.0f;
-            tile[c][pix] = v;
-            if (SUMS) part += v;
+            for (int q = 0; q < TR_PIX / 32; ++q) {
+                const int pix = q * 32 + lane;
+                const float v = pix < npix ? __ldg(src + static_cast<size_t>(c) * HW + pix) : 0.0f;
+                tile[c][pix] = v;
+                if (SUMS) part[j] += v;
+            }
         }
-        if (SUMS) {
+        __syncthreads();
+        float* dh = hi + (static_cast<size_t>(n) * HW + p0) * C + c0 + quad * 4;
+        float* dl = lo + (static_cast<size_t>(n) * HW + p0) * C + c0 + quad * 4;
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
-            if (lane == 0) atomicAdd(sums + c0 + c, scale * part);
+        for (int pass = 0; pass < TR_PIX / 32; ++pass) {
+            const int pix = pass * 32 + (t >> 3);
+            if (pix < npix) {
+                float4 h, l;
+                tc::split_tf32_safe(tile[quad * 4 + 0][pix], h.x, l.x);
+                tc::split_tf32_safe(tile[quad * 4 + 1][pix], h.y, l.y);
+                tc::split_tf32_safe(tile[quad * 4 + 2][pix], h.z, l.z);
+                tc::split_tf32_safe(tile[quad * 4 + 3][pix], h.w, l.w);
+                *reinterpret_cast<float4*>(dh + static_cast<size_t>(pix) * C) = h;
+                *reinterpret_cast<float4*>(dl + static_cast<size_t>(pix) * C) = l;
+            }
         }
     }
-    __syncthreads();
-    const int quad = t & 7;                     // channels 4 * quad .. + 3
-    float* dh = hi + (static_cast<size_t>(n) * HW + p0) * C + c0 + quad * 4;
-    float* dl = lo + (static_cast<size_t>(n) * HW + p0) * C + c0 + quad * 4;
+    if (SUMS) {
 #pragma unroll
-    for (int pass = 0; pass < TR_PIX / 32; ++pass) {
-        const int pix = pass * 32 + (t >> 3);
-        if (pix < npix) {
-            float4 h, l;
-            tc::split_tf32_safe(tile[quad * 4 + 0][pix], h.x, l.x);
-            tc::split_tf32_safe(tile[quad * 4 + 1][pix], h.y, l.y);
-            tc::split_tf32_safe(tile[quad * 4 + 2][pix], h.z, l.z);
-            tc::split_tf32_safe(tile[quad * 4 + 3][pix], h.w, l.w);
-            *reinterpret_cast<float4*>(dh + static_cast<size_t>(pix) * C) = h;
-            *reinterpret_cast<float4*>(dl + static_cast<size_t>(pix) * C) = l;
+        for (int j = 0; j < 4; ++j) {
+            float v = part[j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) atomicAdd(sums + c0 + warp * 4 + j, scale * v);
         }
     }
 }
@@ -884,7 +894,7 @@ int launch_bn(const Problem& q, const float* src, char* images, const char* b_ti
     const int hw = q.in_h * q.in_w;
     dim3 tgrid(ceil_div(hw, TR_PIX), q.cin / 32, q.n);
     if (tgrid.y > 65535u || tgrid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
-    nchw_to_split_nhwc_kernel<false><<<tgrid, 256, 0, stream>>>(src, hi, lo, q.cin, hw, nullptr, 0.0f);
+    nchw_to_split_nhwc_kernel<false><<<tgrid, 256, 0, stream>>>(src, hi, lo, q.cin, hw, 1, nullptr, 0.0f);
     VDNN_LAUNCHED();
     dim3 grid(ceil_div(p.total_boxes, BOXES), ceil_div(q.n_cols, BN), splits);
     if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
@@ -1095,10 +1105,16 @@ int wgrad_launch_bn(const WgradProblem& q, const float* x, const float* dy, char
     if ((st = make_image_map(&myl, yl, q.n, q.p, q.q, q.k, bw, p.bh, sw)) != VDNN_OK) return st;
     dim3 tx(ceil_div(q.h * q.w, TR_PIX), q.c / 32, q.n), ty(ceil_div(q.p * q.q, TR_PIX), q.k / 32, q.n);
     if (tx.y > 65535u || tx.z > 65535u || ty.y > 65535u) return VDNN_ERR_UNSUPPORTED;
-    nchw_to_split_nhwc_kernel<false><<<tx, 256, 0, stream>>>(x, xh, xl, q.c, q.h * q.w, nullptr, 0.0f);
+    nchw_to_split_nhwc_kernel<false><<<tx, 256, 0, stream>>>(x, xh, xl, q.c, q.h * q.w, 1, nullptr, 0.0f);
     VDNN_LAUNCHED();
-    if (bias_sums) nchw_to_split_nhwc_kernel<true><<<ty, 256, 0, stream>>>(dy, yh, yl, q.k, q.p * q.q, bias_sums, bias_scale);
-    else nchw_to_split_nhwc_kernel<false><<<ty, 256, 0, stream>>>(dy, yh, yl, q.k, q.p * q.q, nullptr, 0.0f);
+    if (bias_sums) {
+        // several tiles per block: fewer atomics per channel; the grid stays above two waves for every layer of interest
+        const int tiles = static_cast<int>(ty.x), per_block = tiles < 8 ? tiles : 8;
+        const dim3 tys((tiles + per_block - 1) / per_block, ty.y, ty.z);
+        nchw_to_split_nhwc_kernel<true><<<tys, 256, 0, stream>>>(dy, yh, yl, q.k, q.p * q.q, per_block, bias_sums, bias_scale);
+    } else {
+        nchw_to_split_nhwc_kernel<false><<<ty, 256, 0, stream>>>(dy, yh, yl, q.k, q.p * q.q, 1, nullptr, 0.0f);
+    }
     VDNN_LAUNCHED();
     dim3 grid(ceil_div(p.row_groups, BOXES), ceil_div(q.k, BN), splits);
     if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;

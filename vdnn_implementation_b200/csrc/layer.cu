@@ -41,7 +41,7 @@ void vdnnContext::record(int kind, int layer, int tag, int64_t bytes) {
 int vdnnContext::alloc(void** ptr, size_t bytes, int layer, int tag, bool isDynamic,
                        std::initializer_list<cudaStream_t> streams) {
     std::vector<cudaStream_t> s(streams);
-    const cnmemStatus_t st = vdnnPoolMallocFor(ptr, bytes, s.data(), dry_run ? 0 : static_cast<int>(s.size()));
+    const cnmemStatus_t st = vdnnPoolMallocKindFor(ptr, bytes, s.data(), dry_run ? 0 : static_cast<int>(s.size()), tag == TAG_WS);
     if (st == CNMEM_STATUS_OUT_OF_MEMORY) {
         if (isDynamic) return -1;                       // soft failure (layer.h:119-125)
         if (!quiet) fprintf(stderr, "\n[pool exhausted: %zu bytes for layer %d, tag %d]\n", bytes, layer, tag);

@@ -33,6 +33,9 @@ static const char* env_or(const char* name, const char* fallback) {
     return (v && *v) ? v : fallback;
 }
 
+static int g_lean_offload_default = -1;      // -1: follow VDNN_LEAN_OFFLOAD in the environment
+void Network::setLeanOffloadDefault(int on) { g_lean_offload_default = on < 0 ? -1 : (on != 0); }
+
 /* ------------------------------------------------------------------ construction (network.cu:10-92) */
 
 Network::Network(CNN_t _cnnType, vdnn_t _vdnnType, vdnnAlgoMode_t _algoMode, int _batchSize) {
@@ -155,8 +158,9 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
     launchesAtStepStart = launchesLastStep = 0;
     n_in = c_in = h_in = w_in = n_out = c_out = h_out = w_out = 0;
     for (int i = 0; i < DEFAULT_NUM_LAYER; i++) {
-        layer[i] = NULL; isOffload[i] = false; isPrefetched[i] = false; offloadedSrcData_h[i] = NULL;
+        layer[i] = NULL; isOffload[i] = false; isPrefetched[i] = false; offloadedSrcData_h[i] = NULL; leanDrop[i] = false;
     }
+    lean = g_lean_offload_default >= 0 ? g_lean_offload_default != 0 : atoi(env_or("VDNN_LEAN_OFFLOAD", "0")) != 0;
     handle = &ctx;
     ctx.dry_run = dry_run;
     ctx.learning_rate = cfg.learning_rate > 0.0f ? cfg.learning_rate : static_cast<float>(LEARNING_RATE);
@@ -266,6 +270,8 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
         layer[l]->setOpAlgos(use);
     }
     setVdnnType(vdnnType);
+    // placement by pending events spreads the tensors over a roomy pool; the largest workspace keeps a range of its own
+    if (!dry_run && !packedPool && vdnnType != BASELINE) vdnnPoolSetTransientReserve(static_cast<size_t>(ctx.workspace_bytes_max));
     if (state != VDNN_OK) return;
 
     /* input and label (network.cu:87-90) */
@@ -467,6 +473,7 @@ void Network::setVdnnType(vdnn_t newVdnnType) {
     for (int i = 0; i < DEFAULT_NUM_LAYER; i++) {
         isOffload[i] = false;
         isPrefetched[i] = false;
+        leanDrop[i] = false;
         if (offloadedSrcData_h[i] != NULL) cudaFreeHost(offloadedSrcData_h[i]);
         offloadedSrcData_h[i] = NULL;
         if (layer[i] != NULL) layer[i]->setVdnnMode(newVdnnType);
@@ -492,7 +499,11 @@ void Network::setVdnnType(vdnn_t newVdnnType) {
     } break;
     case VDNN_NONE: break;
     case VDNN_ALL:
-        for (int l = 0; l < numLayers - 1 && state == VDNN_OK; l++) pin(l);
+        for (int l = 0; l < numLayers - 1 && state == VDNN_OK; l++) {
+            const Layer_t below = l > 0 ? layer[l - 1]->LayerType() : RELU;
+            if (lean && layer[l]->LayerType() == RELU && (below == CONV || below == FC_CONV || below == FC_GEMM)) leanDrop[l] = true;
+            else pin(l);
+        }
         break;
     case VDNN_CONV:
         for (int l = 0; l < numLayers - 1 && state == VDNN_OK; l++)
@@ -643,6 +654,8 @@ int Network::forwardPropagation(bool isDynamic) {
                 else
                     NET_TRY(ctx.release(layer[l]->SrcData(), sizeof(DATATYPE) * layer[l]->SrcDataSize(), l, TAG_SRC,
                                         {stream_memory, stream_compute}));
+            } else if (leanDrop[l]) {            // lean VDNN_ALL: nobody reads this tensor again
+                NET_TRY(ctx.release(layer[l]->SrcData(), sizeof(DATATYPE) * layer[l]->SrcDataSize(), l, TAG_SRC, {stream_compute}));
             }
         }
         if (ctx.capture) NET_TRY(captureTensor(capDst[l], layer[l]->DstData(), layer[l]->DstDataSize()));
@@ -715,6 +728,7 @@ int Network::backwardPropagation(bool isDynamic) {
                 layer[l]->copyDiffData(layer[l + 1]->GradData());
                 layer[l]->copyDstData(layer[l + 1]->SrcData());
             }
+            if (leanDrop[l]) layer[l]->copySrcData(layer[l]->DstData());       // ReLU mask from y: y > 0 exactly where x > 0
             // this layer reads its own srcData: if that came back from the host, wait for the copy
             if (isOffload[l] && isPrefetched[l] && !ctx.dry_run)
                 NET_CU(cudaStreamWaitEvent(stream_compute, ctx.ev_prefetch_done[l], 0));
@@ -739,7 +753,8 @@ int Network::backwardPropagation(bool isDynamic) {
             if (ctx.capture) NET_TRY(captureTensor(capGrad[l], layer[l]->GradData(), layer[l]->SrcDataSize()));
 
             /* Release dstData and diffData (network.cu:1172-1173) */
-            NET_TRY(ctx.release(layer[l]->DstData(), sizeof(DATATYPE) * layer[l]->DstDataSize(), l, TAG_DST, {stream_compute}));
+            if (l == last || !leanDrop[l + 1])      // a dropped tensor went back to the pool in forward
+                NET_TRY(ctx.release(layer[l]->DstData(), sizeof(DATATYPE) * layer[l]->DstDataSize(), l, TAG_DST, {stream_compute}));
             NET_TRY(ctx.release(layer[l]->DiffData(), sizeof(DATATYPE) * layer[l]->DstDataSize(), l, TAG_DIFF, {stream_compute}));
             ctx.record(5, l, TAG_NONE, 0);
             memoryLine("Bwd", l, layer[l]->BwdDataWorkSpaceSize() + layer[l]->BwdFilterWorkSpaceSize());

@@ -70,6 +70,13 @@ public:
     int             enableDataParallel(int rank, int world, const char* unique_id128);
     int             weightChecksum(uint64_t* out);
     int             dpMode() const;            // 0 single device, 1 NCCL all-reduce + axpy, 2 fused peer all-reduce + SGD
+    /* Lean variant of VDNN_ALL (not in the reference; it moves fewer bytes, so it is never the default): the srcData of
+       a ReLU layer that follows a CONV / FC layer is neither offloaded nor kept -- it is released after the ReLU's
+       forward, and the ReLU's backward takes its mask from dstData (y > 0 exactly where x > 0), which the next layer's
+       prefetch brings back anyway.  CONV / FC backward never read their own output.  Networks constructed while the
+       switch is on (or with VDNN_LEAN_OFFLOAD=1 in the environment) follow it. */
+    static void     setLeanOffloadDefault(int on);
+    bool            leanOffload() const { return lean; }
 
 private:
     void            init(const vdnn_network_config& cfg, bool dry_run);
@@ -114,6 +121,8 @@ private:
     Layer*              layer[DEFAULT_NUM_LAYER];
     bool                isOffload[DEFAULT_NUM_LAYER];
     bool                isPrefetched[DEFAULT_NUM_LAYER];
+    bool                lean;                              // lean VDNN_ALL (see setLeanOffloadDefault)
+    bool                leanDrop[DEFAULT_NUM_LAYER];       // this layer's srcData is released after its forward, not offloaded
     DATATYPE*           offloadedSrcData_h[DEFAULT_NUM_LAYER];
 
     const vdnn_layer_spec* customLayers;

@@ -91,6 +91,9 @@ int vdnn_network_layer_algos(vdnn_network* net, int layer, int* out3) { NET(net)
 
 int vdnn_network_set_offload_order(vdnn_network* net, int forward_order) { NET(net); return net->impl->setOffloadOrder(forward_order != 0); }
 
+int vdnn_set_lean_offload(int on) { Network::setLeanOffloadDefault(on); return VDNN_OK; }
+int vdnn_network_lean(const vdnn_network* net) { return (net && net->impl && net->impl->leanOffload()) ? 1 : 0; }
+
 int vdnn_network_timeline(vdnn_network* net, float* out) { NET(net); return net->impl->timeline(out); }
 
 int vdnn_dp_unique_id(char* out128) { return vdnn::dp_unique_id(out128); }

@@ -34,6 +34,7 @@ struct Pool {
     void* resolver_user = nullptr;
     int fail_countdown = 0;
     bool packed = false;                // tightest fit only (vdnnPoolSetPacked)
+    size_t reserve = 0;                 // top bytes kept for transient blocks while the pool is not packed
     unsigned long long next_seq = 1;
     std::vector<cudaEvent_t> spare_events;   // recycled fence events
 };
@@ -80,8 +81,12 @@ cnmemStatus_t resolve_holds_locked(size_t begin, size_t end) {
 // finished, instead of queueing behind the copy or kernel that just released the tightest-fitting block
 // (a prefetch target must not wait for compute, nor an activation for an offload).  The byte accounting
 // (used / peak) is the same either way; only the placement differs.
+//
+// transient: a block that is given back within the same layer call (workspace).  In a roomy pool those are placed at
+// the END of a free block, highest address first among the equally ready: long-lived tensors grow from the low end of
+// the free ranges, and a large workspace that is cut out of the middle of one would leave two short ranges behind.
 cnmemStatus_t alloc_locked(void** ptr, size_t size, size_t* off_out, size_t* len_out,
-                           const cudaStream_t* consumers = nullptr, int num_consumers = 0) {
+                           const cudaStream_t* consumers = nullptr, int num_consumers = 0, bool transient = false) {
     if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
     if (!ptr) return CNMEM_STATUS_INVALID_ARGUMENT;
     if (size == 0) { *ptr = nullptr; return CNMEM_STATUS_SUCCESS; }
@@ -104,18 +109,36 @@ cnmemStatus_t alloc_locked(void** ptr, size_t size, size_t* off_out, size_t* len
                                      ((at == it->first) == (best_at == best->first) && it->second.size < best->second.size)));
         if (better) { best = it; best_ready = ready; best_at = at; }
     };
-    for (auto it = g_pool.blocks.begin(); it != g_pool.blocks.end(); ++it) {
-        if (!it->second.free || it->second.size < need) continue;
-        const size_t lo = it->first, hi = it->first + it->second.size - need;   // admissible starts: [lo, hi]
-        consider(it, lo);
-        if (!rank || !roomy || (best == it && best_ready == 0)) continue;
-        for (const Fence& f : g_pool.fences) {
-            if (f.end > lo && f.end <= hi) consider(it, f.end);
-            if (f.begin > lo && f.begin <= hi) consider(it, f.begin);
-        }
-        for (const Hold& h : g_pool.holds) {
-            if (h.end > lo && h.end <= hi) consider(it, h.end);
-            if (h.begin > lo && h.begin <= hi) consider(it, h.begin);
+    const bool top_down = transient && roomy && !g_pool.is_virtual;
+    // Long-lived blocks keep out of the reserve at the top of a roomy pool as long as they fit below it (second pass:
+    // anywhere), so that the largest workspace always finds its bytes in one piece there.
+    const size_t fence_line = (roomy && !g_pool.is_virtual && !transient && g_pool.reserve < g_pool.capacity)
+                                  ? g_pool.capacity - g_pool.reserve : g_pool.capacity;
+    for (int pass = 0; pass < 2 && best == g_pool.blocks.end(); ++pass) {
+        const size_t limit = pass == 0 ? fence_line : g_pool.capacity;
+        if (pass == 1 && fence_line == g_pool.capacity) break;
+        for (auto it = g_pool.blocks.begin(); it != g_pool.blocks.end(); ++it) {
+            if (!it->second.free || it->second.size < need) continue;
+            const size_t block_end = it->first + it->second.size < limit ? it->first + it->second.size : limit;
+            if (block_end < it->first + need) continue;
+            const size_t lo = it->first, hi = block_end - need;   // admissible starts: [lo, hi]
+            if (top_down) {
+                const unsigned long long ready = rank ? range_readiness_locked(hi, hi + need, consumers, num_consumers, true) : 0;
+                if (best == g_pool.blocks.end() || ready < best_ready || (ready == best_ready && hi > best_at)) {
+                    best = it; best_ready = ready; best_at = hi;
+                }
+                continue;
+            }
+            consider(it, lo);
+            if (!rank || !roomy || (best == it && best_ready == 0)) continue;
+            for (const Fence& f : g_pool.fences) {
+                if (f.end > lo && f.end <= hi) consider(it, f.end);
+                if (f.begin > lo && f.begin <= hi) consider(it, f.begin);
+            }
+            for (const Hold& h : g_pool.holds) {
+                if (h.end > lo && h.end <= hi) consider(it, h.end);
+                if (h.begin > lo && h.begin <= hi) consider(it, h.begin);
+            }
         }
     }
     if (best == g_pool.blocks.end()) return CNMEM_STATUS_OUT_OF_MEMORY;
@@ -202,6 +225,7 @@ cnmemStatus_t cnmemInit(int numDevices, const cnmemDevice_t* devices, unsigned) 
     g_pool.device = devices[0].device;
     g_pool.capacity = size;
     g_pool.used = g_pool.peak = 0;
+    g_pool.reserve = 0;
     g_pool.blocks.clear();
     g_pool.blocks[0] = Block{size, true};
     g_pool.fences.clear();
@@ -293,10 +317,14 @@ cnmemStatus_t vdnnPoolFreeAfter(void* ptr, const cudaStream_t* streams, int numS
 }
 
 cnmemStatus_t vdnnPoolMallocFor(void** ptr, size_t size, const cudaStream_t* streams, int numStreams) {
+    return vdnnPoolMallocKindFor(ptr, size, streams, numStreams, 0);
+}
+
+cnmemStatus_t vdnnPoolMallocKindFor(void** ptr, size_t size, const cudaStream_t* streams, int numStreams, int transient) {
     std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     size_t off = 0, len = 0;
     if (!g_pool.is_virtual && g_pool.ready) drop_finished_fences_locked();
-    cnmemStatus_t st = alloc_locked(ptr, size, &off, &len, streams, g_pool.is_virtual ? 0 : numStreams);
+    cnmemStatus_t st = alloc_locked(ptr, size, &off, &len, streams, g_pool.is_virtual ? 0 : numStreams, transient != 0);
     if (st != CNMEM_STATUS_SUCCESS || size == 0) return st;
     if (!g_pool.holds.empty()) {
         st = resolve_holds_locked(off, off + len);
@@ -313,6 +341,13 @@ cnmemStatus_t vdnnPoolMallocFor(void** ptr, size_t size, const cudaStream_t* str
 cnmemStatus_t vdnnPoolSetPacked(int packed) {
     std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
     g_pool.packed = packed != 0;
+    return CNMEM_STATUS_SUCCESS;
+}
+
+cnmemStatus_t vdnnPoolSetTransientReserve(size_t bytes) {
+    std::lock_guard<std::recursive_mutex> lock(g_pool.mu);
+    if (!g_pool.ready) return CNMEM_STATUS_NOT_INITIALIZED;
+    g_pool.reserve = round_up(bytes);
     return CNMEM_STATUS_SUCCESS;
 }
 
@@ -378,6 +413,7 @@ cnmemStatus_t vdnnPoolInitVirtual(size_t size) {
     g_pool.device = -1;
     g_pool.capacity = size;
     g_pool.used = g_pool.peak = 0;
+    g_pool.reserve = 0;
     g_pool.blocks.clear();
     g_pool.blocks[0] = Block{size, true};
     g_pool.fences.clear();

@@ -17,7 +17,7 @@ class Network:
 
     def __init__(self, cnn_type, vdnn_type, algo_mode, batch_size=0, device=0, pool_bytes=0, learning_rate=0.0,
                  init_mode=0, weight_seed_base=3000, fix_input_leak=True, host_sync_per_layer=False,
-                 verbose=False, capture=False, custom_layers=None):
+                 verbose=False, capture=False, custom_layers=None, lean_offload=None):
         cnn_type = abi.CNN_NAMES.get(cnn_type, cnn_type)
         vdnn_type = abi.VDNN_NAMES.get(vdnn_type, vdnn_type)
         algo_mode = abi.ALGO_NAMES.get(algo_mode, algo_mode)
@@ -35,7 +35,15 @@ class Network:
             cfg.custom_layers = self._custom
             cfg.num_custom_layers = len(custom_layers)
         self._h = C.c_void_p()
-        check(lib().vdnn_network_create(C.byref(self._h), C.byref(cfg)), "vdnn_network_create")
+        # lean_offload: None = the environment decides (VDNN_LEAN_OFFLOAD), True / False = this network's own choice
+        if lean_offload is not None:
+            lib().vdnn_set_lean_offload(int(bool(lean_offload)))
+        try:
+            check(lib().vdnn_network_create(C.byref(self._h), C.byref(cfg)), "vdnn_network_create")
+        finally:
+            if lean_offload is not None:
+                lib().vdnn_set_lean_offload(-1)
+        self.lean_offload = bool(lib().vdnn_network_lean(self._h))
         self.num_layers = lib().vdnn_network_num_layers(self._h)
         self.input_size = lib().vdnn_network_input_size(self._h)
         self.output_size = lib().vdnn_network_output_size(self._h)
