@@ -427,6 +427,7 @@ def run_b200(args):
         raise SystemExit(f"non-finite loss in the timed region: {losses}")
     layer_specs = net.layer_specs()
     checksum = net.weight_checksum() if world > 1 else None
+    dp_mode = net.dp_mode()
     net.close()
 
     # the other policies, a few steps each, same process and same data (BASELINE config 5 names VDNN_CONV for the 1/2/4/8 runs;
@@ -519,6 +520,7 @@ def run_b200(args):
                  "prefetch_gbs_all_gpus": pre_gbs * world if pre_gbs else None,
                  "copy_overlap_frac": stats["copy_overlap_ms"] / copy_ms if copy_ms > 0 else None,
                  "forced_offloads": stats["forced_offloads"],
+                 "dp_mode": {0: "single", 1: "nccl all-reduce + axpy per layer", 2: "fused peer all-reduce + SGD kernel"}[dp_mode],
                  "by_policy": by_policy},
     }
     if measured:
