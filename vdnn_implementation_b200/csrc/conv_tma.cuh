@@ -1022,9 +1022,21 @@ inline int strip_tile_n(int n_cols) {
     return tc::tile_n(n_cols);
 }
 
+#include "conv_tma_pair.cuh"
+
+// VDNN_STRIP_PAIRS=0: 256-column tiles on single CTAs instead of CTA pairs (comparison runs).
+inline bool strip_pairs_enabled() {
+    static const bool v = []() { const char* e = getenv("VDNN_STRIP_PAIRS"); return !e || e[0] != '0'; }();
+    return v;
+}
+
 inline int strip_launch(const Problem& q, const float* src, char* images, const char* b_tiles, float* out, const float* bias,
                         float alpha, float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream) {
     const int bn = strip_tile_n(q.n_cols);
+    if (bn == 256 && strip_halves(q.n_cols) == 1 && strip_pairs_enabled()) {
+        const int st = pair::strip_pair_launch(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
+        if (st != VDNN_ERR_UNSUPPORTED) return st;
+    }
     if (strip_halves(q.n_cols) == 2) {
         if (bn == 64) return strip_launch_bn<64, 2>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
         return strip_launch_bn<128, 2>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
