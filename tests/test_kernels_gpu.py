@@ -48,6 +48,8 @@ CONV_CASES = [  # n, c, h, w, k, r, pad, stride
     (5, 32, 7, 7, 32, 3, 2, 1),        # padding beyond the filter radius: the output grid (9 x 9) is larger than the image
     (2, 512, 6, 6, 64, 3, 1, 1),       # one output tile, 4608-long reduction: split along k with partial sums
     (9, 64, 40, 24, 64, 3, 1, 1),      # many tiles of 64 columns, tiles that straddle images
+    (2, 32, 12, 12, 160, 3, 1, 1),     # 256-column tiles on CTA pairs with an odd number of row tiles: the last pair is half empty
+    (3, 288, 10, 10, 512, 3, 1, 1),    # two full 256-column tiles, 81 row groups (ragged last row tile), pairs in every kernel
 ]
 ENGINES = ["ffma", "tcgen05"]
 

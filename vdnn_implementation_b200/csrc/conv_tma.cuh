@@ -1052,11 +1052,21 @@ struct WgradProblem {
     int R, S, pad_h, pad_w;
 };
 
+// The filter gradient of layers with more than 128 filters runs on CTA pairs (conv_tma_pair.cuh); VDNN_WGRAD_PAIRS=0:
+// on single CTAs (comparison runs).  Pair tiles of 128 and 64 filters were measured too and are slower than single
+// CTAs (128 -> 128 @ 112 x 112, batch 32: 1.13 ms against 0.84; 64 -> 64 @ 224 x 224: 2.14 against 1.48).
+inline bool wgrad_pairs_enabled(int bn) {
+    static const bool on = []() { const char* e = getenv("VDNN_WGRAD_PAIRS"); return !e || e[0] != '0'; }();
+    return on && bn == 256;
+}
+
 // Reduction split for the filter gradient: the tiles (row-group quadruples x column tiles) are few, the reduction over
 // pixel boxes is long; as many splits as fill two waves of CTAs, at least two boxes each.
 inline void wgrad_plan(const WgradProblem& q, int total_boxes, int* splits, int* box_chunk) {
     const int bn = tc::tile_n(q.k);
-    const long tiles = static_cast<long>(ceil_div(q.R * q.S * (q.c / 32), BOXES)) * ceil_div(q.k, bn);
+    int row_tiles = ceil_div(q.R * q.S * (q.c / 32), BOXES);
+    if (wgrad_pairs_enabled(bn)) row_tiles = (row_tiles + 1) / 2 * 2;          // CTA pairs take two row tiles each
+    const long tiles = static_cast<long>(row_tiles) * ceil_div(q.k, bn);
     long s = (2L * sm_count()) / tiles;
     if (s > total_boxes / 2) s = total_boxes / 2;
     if (s > 1024) s = 1024;
@@ -1130,8 +1140,19 @@ int wgrad_launch_bn(const WgradProblem& q, const float* x, const float* dy, char
     VDNN_LAUNCHED();
     dim3 grid(ceil_div(p.row_groups, BOXES), ceil_div(q.k, BN), splits);
     if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
-    kern<<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(mxh, mxl, myh, myl, p);
-    VDNN_LAUNCHED();
+    if constexpr (BN == 256) {
+        if (wgrad_pairs_enabled(BN)) {
+            const int st = pair::wgrad_pair_launch<BN>(mxh, mxl, myh, myl, p, grid.x, grid.y, grid.z, stream);
+            if (st != VDNN_OK) return st;
+            *splits_out = splits;
+            *partial_out = partial;
+            return VDNN_OK;
+        }
+    }
+    {
+        kern<<<grid, THREADS, Cfg::SMEM_BYTES, stream>>>(mxh, mxl, myh, myl, p);
+        VDNN_LAUNCHED();
+    }
     *splits_out = splits;
     *partial_out = partial;
     return VDNN_OK;

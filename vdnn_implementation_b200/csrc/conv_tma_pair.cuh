@@ -60,17 +60,20 @@ __device__ __forceinline__ void mma_tf32_2cta(uint32_t tmem_d, uint64_t adesc, u
                  "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
-// One 32-wide k block of the 3xTF32 product on the pair (order and descriptors as tc::mma_block_3xtf32).
-__device__ __forceinline__ void mma_block_3xtf32_2cta(uint32_t d_tmem, uint64_t dah, uint64_t dal, uint64_t dbh, uint64_t dbl, bool fresh) {
-    mma_tf32_2cta(d_tmem, dal, dbh, Cfg::IDESC, fresh ? 0u : 1u);
-    mma_tf32_2cta(d_tmem, dah, dbl, Cfg::IDESC, 1u);
-    mma_tf32_2cta(d_tmem, dah, dbh, Cfg::IDESC, 1u);
+// One 32-wide k block of the 3xTF32 product on the pair (order and descriptors as tc::mma_block_3xtf32; STEP = what a
+// k slice adds to the descriptors' address field: 2 for K-major tiles, 64 for MN-major strips).
+template <int STEP = 2>
+__device__ __forceinline__ void mma_block_3xtf32_2cta(uint32_t d_tmem, uint64_t dah, uint64_t dal, uint64_t dbh, uint64_t dbl, bool fresh,
+                                                      uint32_t idesc = Cfg::IDESC) {
+    mma_tf32_2cta(d_tmem, dal, dbh, idesc, fresh ? 0u : 1u);
+    mma_tf32_2cta(d_tmem, dah, dbl, idesc, 1u);
+    mma_tf32_2cta(d_tmem, dah, dbh, idesc, 1u);
 #pragma unroll
     for (int ks = 1; ks < BK / 8; ++ks) {
-        dah += 2; dal += 2; dbh += 2; dbl += 2;
-        mma_tf32_2cta(d_tmem, dal, dbh, Cfg::IDESC, 1u);
-        mma_tf32_2cta(d_tmem, dah, dbl, Cfg::IDESC, 1u);
-        mma_tf32_2cta(d_tmem, dah, dbh, Cfg::IDESC, 1u);
+        dah += STEP; dal += STEP; dbh += STEP; dbl += STEP;
+        mma_tf32_2cta(d_tmem, dal, dbh, idesc, 1u);
+        mma_tf32_2cta(d_tmem, dah, dbl, idesc, 1u);
+        mma_tf32_2cta(d_tmem, dah, dbh, idesc, 1u);
     }
 }
 // Arrive on the barrier at this offset in both CTAs of the pair once the MMAs issued so far have completed.
@@ -333,6 +336,221 @@ inline int strip_pair_launch(const Problem& q, const float* src, char* images, c
     if (pairs > tiles) pairs = tiles;
     cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs), ny, splits);
     VDNN_CUDA(cudaLaunchKernelEx(&cfg, kern, map_hi, map_lo, map_b, p));
+    VDNN_LAUNCHED();
+    return VDNN_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Filter gradient on CTA pairs: the two CTAs of a pair take neighbouring row tiles (128 rows = four (tap, channel block)
+// groups each) of the same column tile and pixel range, so they need the same 256-filter slice of dy; each stages its
+// own rows of x and half of that slice (four of the eight 32-filter boxes).  64 KB per CTA and k block instead of 96.
+// BNP = filters per pair tile (256, 128 or 64); each CTA stages BNP / 2 of them (BNP / 64 boxes of 32).
+template <int BNP> struct WgradCfg {
+    static_assert(BNP == 256 || BNP == 128 || BNP == 64, "pair tiles of 256, 128 or 64 filters");
+    static constexpr int HALF = BNP / 2;
+    static constexpr int HALF_BOXES = HALF / 32;
+    static constexpr int B_TILE_BYTES = HALF * BK * 4;
+    static constexpr int STAGE_BYTES = 2 * A_TILE_BYTES + 2 * B_TILE_BYTES;                 // 64 / 48 / 40 KB
+    static constexpr int S = BNP == 256 ? 3 : (BNP == 128 ? 4 : 5);
+    static constexpr int TMEM_COLS = 2 * BNP;
+    static constexpr int SMEM_BYTES = S * STAGE_BYTES + 1024 + 256;
+    // D = F32, A = B = TF32, both MN-major, N = BNP, M = 256 (128 rows in each CTA)
+    static constexpr uint32_t IDESC_MN = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (1u << 16) |
+                                         (static_cast<uint32_t>(BNP >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+};
+
+__device__ __forceinline__ void tma_load_box_2cta(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster, int c0, int x, int y, int n) {
+    asm volatile("cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster), "r"(c0), "r"(x), "r"(y), "r"(n) : "memory");
+}
+
+template <int BNP>
+__global__ void __launch_bounds__(THREADS, 1)
+wgrad_pair_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ CUtensorMap x_lo,
+                  const __grid_constant__ CUtensorMap dy_hi, const __grid_constant__ CUtensorMap dy_lo, const WgradParams p) {
+    typedef WgradCfg<BNP> WCfg;
+    constexpr int S = WCfg::S;
+    extern __shared__ char smem_raw[];
+    char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + S * WCfg::STAGE_BYTES);
+    uint64_t* full = bars;                  // [S]  used in the leader: bytes of both CTAs
+    uint64_t* empty = full + S;             // [S]  in each CTA
+    uint64_t* acc_ready = empty + S;        // [2]  in each CTA
+    uint64_t* acc_free = acc_ready + 2;     // [2]  used in the leader: drain warps of both CTAs
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_free + 2);
+
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+    const uint32_t rank = cta_rank();
+    const bool leader = rank == 0;
+    const int n0 = blockIdx.y * BNP;
+    const int box_beg = blockIdx.z * p.box_chunk;
+    const int box_end = min(p.total_boxes, box_beg + p.box_chunk);
+    const int nkb = box_beg < box_end ? box_end - box_beg : 0;
+    const int npairs = (nkb + 1) / 2;
+
+    if (t == 0) {
+        for (int s = 0; s < S; ++s) { tc::mbar_init(tc::smem_u32(&full[s]), 1); tc::mbar_init(tc::smem_u32(&empty[s]), 1); }
+        for (int b = 0; b < 2; ++b) { tc::mbar_init(tc::smem_u32(&acc_ready[b]), 1); tc::mbar_init(tc::smem_u32(&acc_free[b]), 2 * DRAIN_WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == DRAIN_WARPS + 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(tmem_slot)), "r"(WCfg::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster_sync();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < DRAIN_WARPS) {
+        constexpr int NACC = BNP / (DRAIN_WARPS / 4);
+        const int col_beg = (warp >> 2) * NACC;
+        const uint32_t tmem_mine = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(col_beg);
+        const uint32_t free0 = map_to_cta(tc::smem_u32(&acc_free[0]), 0), free1 = map_to_cta(tc::smem_u32(&acc_free[1]), 0);
+        float acc[NACC];
+#pragma unroll
+        for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
+        bool alive = true;
+        for (int pair = 0; pair < npairs && alive; ++pair) {
+            const int b = pair & 1;
+            bool ok = tc::mbar_wait(tc::smem_u32(&acc_ready[b]), static_cast<uint32_t>(pair >> 1) & 1u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { atomicCAS(&tc::g_tc_error, 0, 103); alive = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < NACC; c += 16) {
+                float v[16];
+                tc::tmem_ld16(tmem_mine + static_cast<uint32_t>(b * BNP + c), v);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[c + j] += v[j];
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(b ? free1 : free0);
+        }
+        // this thread's row: row group (warp & 3) of this CTA's tile, channel `lane` of its block
+        const int group = blockIdx.x * BOXES + (warp & 3);
+        if (alive && group < p.row_groups) {
+            const int tap = group / p.cblocks, cb = group - tap * p.cblocks;
+            const size_t crs = static_cast<size_t>(p.C) * p.taps;
+            float* o = p.out + static_cast<size_t>(cb * 32 + lane) * p.taps + tap;
+            if (p.mode == EPI_PARTIAL) o += static_cast<size_t>(blockIdx.z) * p.partial_stride;
+#pragma unroll
+            for (int j = 0; j < NACC; ++j) {
+                const int col = n0 + col_beg + j;
+                if (col < p.n_cols) {
+                    float* q = o + static_cast<size_t>(col) * crs;
+                    if (p.mode == EPI_DIRECT) {
+                        float v = p.alpha * acc[j];
+                        if (p.beta != 0.0f) v = fmaf(p.beta, *q, v);
+                        *q = v;
+                    } else if (p.mode == EPI_ATOMIC) {
+                        atomicAdd(q, p.alpha * acc[j]);
+                    } else {
+                        *q = acc[j];
+                    }
+                }
+            }
+        }
+    } else if (warp == DRAIN_WARPS) {
+        if (lane == 0) {
+            int gc[BOXES], gdy[BOXES], gdx[BOXES];
+            int groups = 0;
+#pragma unroll
+            for (int j = 0; j < BOXES; ++j) {
+                const int group = blockIdx.x * BOXES + j;
+                if (group < p.row_groups) {
+                    const int tap = group / p.cblocks, cb = group - tap * p.cblocks;
+                    const int r = tap / p.taps_s, sx = tap - r * p.taps_s;
+                    gc[j] = cb * 32; gdy[j] = r + p.off_h; gdx[j] = sx + p.off_w;
+                    groups = j + 1;
+                } else {
+                    gc[j] = 0; gdy[j] = 0; gdx[j] = 0;
+                }
+            }
+            // the peer's tile is the next one along x (the leader has the even tile of the pair)
+            const int peer_first = (static_cast<int>(blockIdx.x) + 1) * BOXES;
+            const int groups_peer = leader ? max(0, min(BOXES, p.row_groups - peer_first)) : 0;
+            const int col_boxes = min(BNP, p.n_cols - n0) / 32;                         // of the pair
+            const int box_first = leader ? 0 : WCfg::HALF_BOXES;                        // this CTA's boxes of the dy slice
+            const int my_boxes = max(0, min(WCfg::HALF_BOXES, col_boxes - box_first));
+            const uint32_t stage_tx = static_cast<uint32_t>(2 * (groups + groups_peer + col_boxes) * BOX_BYTES);    // armed by the leader
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % S;
+                const uint32_t phase = static_cast<uint32_t>(i / S) & 1u;
+                if (!tc::mbar_wait(tc::smem_u32(&empty[s]), phase ^ 1u)) { atomicCAS(&tc::g_tc_error, 0, 101); break; }
+                uint32_t n, rem, by, bx;
+                p.div_boxes_img.divmod(static_cast<uint32_t>(box_beg + i), n, rem);
+                p.div_boxes_w.divmod(rem, by, bx);
+                const int y0 = static_cast<int>(by) * p.bh, x0 = static_cast<int>(bx) << p.bw_log2;
+                const uint32_t bar = map_to_cta(tc::smem_u32(&full[s]), 0);
+                const uint32_t st = tc::smem_u32(tiles + s * WCfg::STAGE_BYTES);
+                if (leader)
+                    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc::smem_u32(&full[s])), "r"(stage_tx) : "memory");
+#pragma unroll
+                for (int j = 0; j < BOXES; ++j) {
+                    if (j < groups) {
+                        tma_load_box_2cta(st + j * BOX_BYTES, &x_hi, bar, gc[j], x0 + gdx[j], y0 + gdy[j], static_cast<int>(n));
+                        tma_load_box_2cta(st + A_TILE_BYTES + j * BOX_BYTES, &x_lo, bar, gc[j], x0 + gdx[j], y0 + gdy[j], static_cast<int>(n));
+                    }
+                }
+                for (int j = 0; j < my_boxes; ++j) {
+                    const int c0 = n0 + (box_first + j) * 32;
+                    tma_load_box_2cta(st + 2 * A_TILE_BYTES + j * BOX_BYTES, &dy_hi, bar, c0, x0, y0, static_cast<int>(n));
+                    tma_load_box_2cta(st + 2 * A_TILE_BYTES + WCfg::B_TILE_BYTES + j * BOX_BYTES, &dy_lo, bar, c0, x0, y0, static_cast<int>(n));
+                }
+            }
+        }
+    } else if (lane == 0 && leader) {
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % S, pair = i >> 1, b = pair & 1;
+            const uint32_t phase = static_cast<uint32_t>(i / S) & 1u;
+            if (!(i & 1) && pair >= 2 && !tc::mbar_wait(tc::smem_u32(&acc_free[b]), static_cast<uint32_t>((pair >> 1) - 1) & 1u)) {
+                atomicCAS(&tc::g_tc_error, 0, 102);
+                break;
+            }
+            if (!tc::mbar_wait(tc::smem_u32(&full[s]), phase)) { atomicCAS(&tc::g_tc_error, 0, 102); break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t a_hi = tc::smem_u32(tiles + s * WCfg::STAGE_BYTES);
+            const uint32_t a_lo = a_hi + A_TILE_BYTES;
+            const uint32_t b_hi = a_hi + 2 * A_TILE_BYTES;
+            const uint32_t b_lo = b_hi + WCfg::B_TILE_BYTES;
+            // one k slice = 8 pixels = 1024 bytes further into every strip
+            mma_block_3xtf32_2cta<1024 / 16>(tmem_base + static_cast<uint32_t>(b * BNP), make_desc_mn(a_hi), make_desc_mn(a_lo),
+                                             make_desc_mn(b_hi), make_desc_mn(b_lo), !(i & 1), WCfg::IDESC_MN);
+            mma_commit_both(tc::smem_u32(&empty[s]));
+            if ((i & 1) || i == nkb - 1) mma_commit_both(tc::smem_u32(&acc_ready[b]));
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster_sync();
+    if (warp == DRAIN_WARPS + 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(WCfg::TMEM_COLS) : "memory");
+    }
+}
+
+// Launch of the pair kernel on the grid of the single-CTA kernel with x rounded up to whole pairs.
+template <int BNP>
+int wgrad_pair_launch(const CUtensorMap& mxh, const CUtensorMap& mxl, const CUtensorMap& myh, const CUtensorMap& myl,
+                      const WgradParams& p, unsigned row_tiles, unsigned col_tiles, unsigned splits, cudaStream_t stream) {
+    typedef WgradCfg<BNP> WCfg;
+    int dev = 0;
+    VDNN_CUDA(cudaGetDevice(&dev));
+    auto kern = wgrad_pair_kernel<BNP>;
+    if (VDNN_ONCE_PER_DEVICE(dev))
+        VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, WCfg::SMEM_BYTES));
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3((row_tiles + 1u) / 2u * 2u, col_tiles, splits);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = WCfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    VDNN_CUDA(cudaLaunchKernelEx(&cfg, kern, mxh, mxl, myh, myl, p));
     VDNN_LAUNCHED();
     return VDNN_OK;
 }

@@ -193,7 +193,11 @@ void Network::init(const vdnn_network_config& cfg, bool dry_run) {
     if (!dry_run && vdnnType != BASELINE) {
         size_t peak = 0;
         const std::vector<unsigned char>* ops = layerOps.empty() ? NULL : &layerOps;
-        packed = !trainable(cfg, vdnnType, algoMode, ops, &peak) || static_cast<double>(pool) < 1.4 * static_cast<double>(peak);
+        const bool fits = trainable(cfg, vdnnType, algoMode, ops, &peak);
+        packed = !fits || static_cast<double>(pool) < 1.4 * static_cast<double>(peak);
+        if (getenv("VDNN_DEBUG_POOL"))
+            fprintf(stderr, "[pool] capacity %zu, replayed peak %zu, replay fits %d -> %s placement\n", pool, peak, fits ? 1 : 0,
+                    packed ? "packed" : "event-ranked");
     }
     if (dry_run) {
         if (vdnnPoolInitVirtual(pool) != CNMEM_STATUS_SUCCESS) { state = VDNN_ERR_OUT_OF_MEMORY; return; }
