@@ -511,43 +511,56 @@ strip_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__
 }
 
 // NCHW fp32 -> the padded position list of the strip engine, as two images (tf32 hi, lo): position q of image n is
-// (row q / wp, column q % wp); rows >= h and columns >= w are the zero gaps.  One block: 32 channels x 128 positions.
+// (row q / wp, column q % wp); rows >= h and columns >= w are the zero gaps.  One block: 32 channels x 128 PIXELS of one
+// image (reads in full, aligned 128-byte lines along the pixels of a channel), written to the pixels' positions (one
+// 128-byte line per pixel and image half); the thread that writes the last pixel of an image row also zeroes the gap
+// columns behind it, and the first block of every (image, channel block) zeroes the gap rows.
 __global__ void __launch_bounds__(256) nchw_to_split_strip_kernel(const float* __restrict__ x, float* __restrict__ hi,
                                                                   float* __restrict__ lo, int C, int H, int W, int wp, int lp) {
     __shared__ float tile[32][TR_PIX + 1];
-    const int n = blockIdx.z, c0 = blockIdx.y * 32, q0 = blockIdx.x * TR_PIX;
+    const int n = blockIdx.z, c0 = blockIdx.y * 32, p0 = blockIdx.x * TR_PIX;
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
-    const int nq = min(TR_PIX, lp - q0);
-    const size_t hw = static_cast<size_t>(H) * W;
-    const float* src = x + (static_cast<size_t>(n) * C + c0) * hw;
+    const int HW = H * W;
+    const int npix = min(TR_PIX, HW - p0);
+    const float* src = x + (static_cast<size_t>(n) * C + c0) * HW + p0;
 #pragma unroll
-    for (int j = 0; j < TR_PIX / 32; ++j) {
-        const int q = q0 + j * 32 + lane;
-        const int row = q / wp, col = q - row * wp;
-        const bool live = j * 32 + lane < nq && row < H && col < W;
-        const size_t off = static_cast<size_t>(row) * W + col;
+    for (int j = 0; j < 4; ++j) {
+        const int c = warp * 4 + j;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int c = warp * 4 + k;
-            tile[c][j * 32 + lane] = live ? __ldg(src + static_cast<size_t>(c) * hw + off) : 0.0f;
+        for (int q = 0; q < TR_PIX / 32; ++q) {
+            const int pix = q * 32 + lane;
+            tile[c][pix] = pix < npix ? __ldg(src + static_cast<size_t>(c) * HW + pix) : 0.0f;
         }
     }
     __syncthreads();
-    const int quad = t & 7;
-    const size_t base = (static_cast<size_t>(n) * lp + q0) * C + c0 + quad * 4;
+    const int quad = t & 7;                     // channels 4 * quad .. + 3
+    const size_t base = static_cast<size_t>(n) * lp * C + c0 + quad * 4;
+    const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
     for (int pass = 0; pass < TR_PIX / 32; ++pass) {
         const int pix = pass * 32 + (t >> 3);
-        if (pix < nq) {
+        if (pix < npix) {
+            const int pidx = p0 + pix, row = pidx / W, col = pidx - row * W;
+            const size_t q = static_cast<size_t>(row) * wp + col;
             float4 h, l;
             tc::split_tf32_safe(tile[quad * 4 + 0][pix], h.x, l.x);
             tc::split_tf32_safe(tile[quad * 4 + 1][pix], h.y, l.y);
             tc::split_tf32_safe(tile[quad * 4 + 2][pix], h.z, l.z);
             tc::split_tf32_safe(tile[quad * 4 + 3][pix], h.w, l.w);
-            *reinterpret_cast<float4*>(hi + base + static_cast<size_t>(pix) * C) = h;
-            *reinterpret_cast<float4*>(lo + base + static_cast<size_t>(pix) * C) = l;
+            *reinterpret_cast<float4*>(hi + base + q * C) = h;
+            *reinterpret_cast<float4*>(lo + base + q * C) = l;
+            if (col == W - 1)
+                for (int g = 1; g <= wp - W; ++g) {
+                    *reinterpret_cast<float4*>(hi + base + (q + g) * C) = zero;
+                    *reinterpret_cast<float4*>(lo + base + (q + g) * C) = zero;
+                }
         }
     }
+    if (blockIdx.x == 0)
+        for (int q = H * wp + (t >> 3); q < lp; q += 32) {
+            *reinterpret_cast<float4*>(hi + base + static_cast<size_t>(q) * C) = zero;
+            *reinterpret_cast<float4*>(lo + base + static_cast<size_t>(q) * C) = zero;
+        }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -983,7 +996,7 @@ int strip_launch_bn(const Problem& q, const float* src, char* images, const char
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return VDNN_ERR_CUDA;
     }
-    dim3 tgrid(ceil_div(g.lp, TR_PIX), q.cin / 32, q.n);
+    dim3 tgrid(ceil_div(q.in_h * q.in_w, TR_PIX), q.cin / 32, q.n);
     if (tgrid.y > 65535u || tgrid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
     nchw_to_split_strip_kernel<<<tgrid, 256, 0, stream>>>(src, hi, lo, q.cin, q.in_h, q.in_w, g.wp, g.lp);
     VDNN_LAUNCHED();
@@ -1024,7 +1037,10 @@ inline int strip_tile_n(int n_cols) {
 
 #include "conv_tma_pair.cuh"
 
-// VDNN_STRIP_PAIRS=0: 256-column tiles on single CTAs instead of CTA pairs (comparison runs).
+// 256-column tiles of the strip engine run on CTA pairs (conv_tma_pair.cuh); VDNN_STRIP_PAIRS=0: on single CTAs
+// (comparison runs).  Pair tiles of 128 and 64 columns were measured too and are slower than what single CTAs do there
+// (128 -> 128 @ 112 x 112 forward, batch 32: 0.735 ms against 0.647 for 256 x 128 tiles on one CTA; 64 -> 64 @ 224 x 224:
+// 1.35 ms against 0.90 for two CTAs per SM).
 inline bool strip_pairs_enabled() {
     static const bool v = []() { const char* e = getenv("VDNN_STRIP_PAIRS"); return !e || e[0] != '0'; }();
     return v;
@@ -1034,7 +1050,7 @@ inline int strip_launch(const Problem& q, const float* src, char* images, const 
                         float alpha, float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream) {
     const int bn = strip_tile_n(q.n_cols);
     if (bn == 256 && strip_halves(q.n_cols) == 1 && strip_pairs_enabled()) {
-        const int st = pair::strip_pair_launch(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
+        const int st = pair::strip_pair_launch<256>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
         if (st != VDNN_ERR_UNSUPPORTED) return st;
     }
     if (strip_halves(q.n_cols) == 2) {

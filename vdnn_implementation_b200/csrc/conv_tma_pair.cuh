@@ -19,17 +19,19 @@
 
 namespace pair {
 
-constexpr int BN_PAIR = 256;                 // columns of a pair tile
-constexpr int BN_HALF = 128;                 // of which each CTA stages this many
-struct Cfg {
+// BNP = columns of a pair tile (256, 128 or 64); each CTA stages BNP / 2 of them.
+template <int BNP> struct PairCfg {
+    static_assert(BNP == 256 || BNP == 128 || BNP == 64, "pair tiles of 256, 128 or 64 columns");
+    static constexpr int HALF = BNP / 2;
     static constexpr int SA = 2, SB = 4;
-    static constexpr int B_TILE_BYTES = BN_HALF * BK * 4;                   // 16 KB: one half (hi or lo) of 128 columns
+    static constexpr int B_TILE_BYTES = HALF * BK * 4;                      // one half (hi or lo) of this CTA's columns
     static constexpr int A_STAGE_BYTES = 2 * STRIP_HALF_BYTES;
     static constexpr int B_STAGE_BYTES = 2 * B_TILE_BYTES;
-    static constexpr int TMEM_COLS = 2 * BN_PAIR;
+    static constexpr int TMEM_COLS = 2 * BNP;
+    static constexpr int CTAS_PER_SM = BNP == 64 ? 2 : 1;                   // as for single CTAs: two issuers per SM at 64 columns
     static constexpr int SMEM_BYTES = SA * A_STAGE_BYTES + SB * B_STAGE_BYTES + 1024 + 256;
-    // instruction descriptor: D = F32, A = B = TF32, both K-major, N = 256, M = 256 (128 rows in each CTA)
-    static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(BN_PAIR >> 3) << 17) |
+    // instruction descriptor: D = F32, A = B = TF32, both K-major, N = BNP, M = 256 (128 rows in each CTA)
+    static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (static_cast<uint32_t>(BNP >> 3) << 17) |
                                       (static_cast<uint32_t>(256 >> 4) << 24);
 };
 
@@ -62,9 +64,9 @@ __device__ __forceinline__ void mma_tf32_2cta(uint32_t tmem_d, uint64_t adesc, u
 }
 // One 32-wide k block of the 3xTF32 product on the pair (order and descriptors as tc::mma_block_3xtf32; STEP = what a
 // k slice adds to the descriptors' address field: 2 for K-major tiles, 64 for MN-major strips).
-template <int STEP = 2>
+template <int STEP>
 __device__ __forceinline__ void mma_block_3xtf32_2cta(uint32_t d_tmem, uint64_t dah, uint64_t dal, uint64_t dbh, uint64_t dbl, bool fresh,
-                                                      uint32_t idesc = Cfg::IDESC) {
+                                                      uint32_t idesc) {
     mma_tf32_2cta(d_tmem, dal, dbh, idesc, fresh ? 0u : 1u);
     mma_tf32_2cta(d_tmem, dah, dbl, idesc, 1u);
     mma_tf32_2cta(d_tmem, dah, dbh, idesc, 1u);
@@ -82,9 +84,11 @@ __device__ __forceinline__ void mma_commit_both(uint32_t bar) {
                  ::"r"(bar), "h"(static_cast<uint16_t>(3)) : "memory");
 }
 
-__global__ void __launch_bounds__(THREADS, 1)
+template <int BNP>
+__global__ void __launch_bounds__(THREADS, PairCfg<BNP>::CTAS_PER_SM)
 strip_pair_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo,
                   const __grid_constant__ CUtensorMap map_b, const StripParams p) {
+    typedef PairCfg<BNP> Cfg;
     constexpr int SA = Cfg::SA, SB = Cfg::SB;
     constexpr int TILE_ROWS = 2 * BM;               // positions per pair tile
     extern __shared__ char smem_raw[];
@@ -103,7 +107,7 @@ strip_pair_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
     const uint32_t rank = cta_rank();
     const bool leader = rank == 0;
     const unsigned pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const int n0 = blockIdx.y * BN_PAIR;
+    const int n0 = blockIdx.y * BNP;
     const long long num_tiles = (p.total_pos + TILE_ROWS - 1) / TILE_ROWS;
     const int g_beg = blockIdx.z * p.group_chunk;
     const int g_end = min(p.groups_total, g_beg + p.group_chunk);
@@ -129,7 +133,7 @@ strip_pair_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
 
     if (warp < DRAIN_WARPS) {
         // ------------------------------------------------------------------ accumulator drain + epilogue (own 128 rows)
-        constexpr int NACC = BN_PAIR / (DRAIN_WARPS / 4);
+        constexpr int NACC = BNP / (DRAIN_WARPS / 4);
         const int col_beg = (warp >> 2) * NACC;
         const uint32_t tmem_mine = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(col_beg);
         const size_t plane = static_cast<size_t>(p.out_h) * p.out_w;
@@ -149,7 +153,7 @@ strip_pair_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
 #pragma unroll
                 for (int c = 0; c < NACC; c += 16) {
                     float v[16];
-                    tc::tmem_ld16(tmem_mine + static_cast<uint32_t>(b * BN_PAIR + c), v);
+                    tc::tmem_ld16(tmem_mine + static_cast<uint32_t>(b * BNP + c), v);
 #pragma unroll
                     for (int j = 0; j < 16; ++j) acc[c + j] += v[j];
                 }
@@ -187,7 +191,7 @@ strip_pair_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
         // ------------------------------------------------------------------ TMA producer: own strip, own half of the weights
         if (lane == 0) {
             // rows of the weight tile images: per (column tile, k block) 256 rows of the hi half, then 256 of the lo half
-            const long long b_row0 = static_cast<long long>(blockIdx.y) * p.kblocks_total * (2 * BN_PAIR) + rank * BN_HALF;
+            const long long b_row0 = static_cast<long long>(blockIdx.y) * p.kblocks_total * (2 * BNP) + rank * Cfg::HALF;
             unsigned i = 0, gcount = 0;
             bool ok = true;
             for (long long tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
@@ -212,9 +216,9 @@ strip_pair_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
                         const uint32_t bst = tc::smem_u32(b_ring + sb * Cfg::B_STAGE_BYTES);
                         if (leader)
                             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc::smem_u32(&b_full[sb])), "r"(2u * Cfg::B_STAGE_BYTES) : "memory");
-                        const long long brow = b_row0 + static_cast<long long>(kb) * (2 * BN_PAIR);
+                        const long long brow = b_row0 + static_cast<long long>(kb) * (2 * BNP);
                         tma_load_rows_2cta(bst, &map_b, bbar, 0, static_cast<int>(brow));
-                        tma_load_rows_2cta(bst + Cfg::B_TILE_BYTES, &map_b, bbar, 0, static_cast<int>(brow + BN_PAIR));
+                        tma_load_rows_2cta(bst + Cfg::B_TILE_BYTES, &map_b, bbar, 0, static_cast<int>(brow + BNP));
                     }
                 }
             }
@@ -240,8 +244,8 @@ strip_pair_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
                     const uint32_t a_lo = a_hi + STRIP_HALF_BYTES;
                     const uint32_t b_hi = tc::smem_u32(b_ring + sb * Cfg::B_STAGE_BYTES);
                     const uint32_t b_lo = b_hi + Cfg::B_TILE_BYTES;
-                    mma_block_3xtf32_2cta(tmem_base + static_cast<uint32_t>(b * BN_PAIR), tc::make_desc(a_hi), tc::make_desc(a_lo),
-                                          tc::make_desc(b_hi), tc::make_desc(b_lo), first_of_pair);
+                    mma_block_3xtf32_2cta<2>(tmem_base + static_cast<uint32_t>(b * BNP), tc::make_desc(a_hi), tc::make_desc(a_lo),
+                                             tc::make_desc(b_hi), tc::make_desc(b_lo), first_of_pair, Cfg::IDESC);
                     mma_commit_both(tc::smem_u32(&b_empty[sb]));
                     if (sx == p.S - 1) mma_commit_both(tc::smem_u32(&a_empty[sa]));
                     if (!first_of_pair || kb_in_tile == nkb - 1) { mma_commit_both(tc::smem_u32(&acc_ready[b])); ++pair; }
@@ -260,12 +264,14 @@ strip_pair_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
     }
 }
 
-// Same arguments as strip_launch_bn; the tile is 256 positions x 256 columns per CTA pair.
-inline int strip_pair_launch(const Problem& q, const float* src, char* images, const char* b_tiles, float* out, const float* bias,
+// Same arguments as strip_launch_bn; the tile is 256 positions x BNP columns per CTA pair.
+template <int BNP>
+int strip_pair_launch(const Problem& q, const float* src, char* images, const char* b_tiles, float* out, const float* bias,
                              float alpha, float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream) {
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
-    auto kern = strip_pair_kernel;
+    typedef PairCfg<BNP> Cfg;
+    auto kern = strip_pair_kernel<BNP>;
     if (VDNN_ONCE_PER_DEVICE(dev))
         VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     const StripGeom g = strip_geometry(q);
@@ -301,19 +307,19 @@ inline int strip_pair_launch(const Problem& q, const float* src, char* images, c
             if (r != CUDA_SUCCESS) return VDNN_ERR_CUDA;
         }
     }
-    const int ny = ceil_div(q.n_cols, BN_PAIR);
+    const int ny = ceil_div(q.n_cols, BNP);
     {
         // the packed weight tiles as rows of 128 bytes (they are stored swizzled already: the copy must not swizzle again)
-        const cuuint64_t rows = static_cast<cuuint64_t>(ny) * p.kblocks_total * (2 * BN_PAIR);
+        const cuuint64_t rows = static_cast<cuuint64_t>(ny) * p.kblocks_total * (2 * BNP);
         const cuuint64_t dims[2] = {static_cast<cuuint64_t>(BK), rows};
         const cuuint64_t strides[1] = {static_cast<cuuint64_t>(BK) * 4};
-        const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(BN_HALF)};
+        const cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(Cfg::HALF)};
         const CUresult r = enc(&map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<char*>(b_tiles), dims, strides, box, elem,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return VDNN_ERR_CUDA;
     }
-    dim3 tgrid(ceil_div(g.lp, TR_PIX), q.cin / 32, q.n);
+    dim3 tgrid(ceil_div(q.in_h * q.in_w, TR_PIX), q.cin / 32, q.n);
     if (tgrid.y > 65535u || tgrid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
     nchw_to_split_strip_kernel<<<tgrid, 256, 0, stream>>>(src, hi, lo, q.cin, q.in_h, q.in_w, g.wp, g.lp);
     VDNN_LAUNCHED();
@@ -327,7 +333,7 @@ inline int strip_pair_launch(const Problem& q, const float* src, char* images, c
     cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
     cfg.stream = stream;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    cfg.gridDim = dim3(2 * (sm_count() / 2), 1, 1);
+    cfg.gridDim = dim3(2 * (sm_count() / 2) * Cfg::CTAS_PER_SM, 1, 1);
     int resident = 0;
     if (cudaOccupancyMaxActiveClusters(&resident, kern, &cfg) != cudaSuccess || resident < 1) { (void)cudaGetLastError(); return VDNN_ERR_UNSUPPORTED; }
     const long long tiles = ceil_div<long long>(p.total_pos, 2 * BM);
