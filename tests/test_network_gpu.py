@@ -139,7 +139,7 @@ def test_policies_agree_at_full_width(vdnn):
     assert vdnn.ops.engine_status() == 0
     ref = seen["VDNN_NONE"]
     for policy, (loss, ws, bs) in seen.items():
-        assert abs(loss[0] - ref[0][0]) < 1e-6 and abs(loss[1] - ref[0][1]) < 1e-5 * abs(ref[0][1]), policy
+        assert abs(loss[0] - ref[0][0]) < 1e-5 * abs(ref[0][0]) and abs(loss[1] - ref[0][1]) < 1e-5 * abs(ref[0][1]), policy
         for a, b in zip(ws + bs, ref[1] + ref[2]):
             assert rel_err(a, b) < 1e-5, policy
 
@@ -215,7 +215,9 @@ def test_offload_order_is_not_observable(vdnn):
     in_order = _steps(vdnn, 6e9, True)
     assert by_need[3] == in_order[3] and by_need[4] == in_order[4]
     assert by_need[5] == 0 and in_order[5] == 0
-    assert abs(by_need[2][0] - in_order[2][0]) < 1e-6 and abs(by_need[2][1] - in_order[2][1]) < 1e-5 * abs(in_order[2][1])
+    # losses of the second step: they carry the first step's atomically summed bias gradients (run-to-run noise); 1e-5 is
+    # the bar the specification sets for the loss
+    assert abs(by_need[2][0] - in_order[2][0]) < 1e-5 * abs(in_order[2][0]) and abs(by_need[2][1] - in_order[2][1]) < 1e-5 * abs(in_order[2][1])
     for a, b in zip(by_need[0], in_order[0]):
         assert rel_err(a, b) < 5e-5
     for a, b in zip(by_need[1], in_order[1]):        # bias gradients are summed with atomics: run-to-run noise
@@ -233,7 +235,7 @@ def test_lean_offload_moves_fewer_bytes_and_trains_the_same(vdnn, model, batch, 
     assert lean[6]["offload_bytes"] == lean[6]["prefetch_bytes"] == lean[6]["pinned_bytes"]
     assert lean[6]["offload_bytes"] < 0.75 * full[6]["offload_bytes"]
     assert lean[4] <= full[4] and lean[6]["pool_used_bytes"] == full[6]["pool_used_bytes"]
-    assert abs(lean[2][0] - full[2][0]) < 1e-6 and abs(lean[2][1] - full[2][1]) < 1e-5 * abs(full[2][1])
+    assert abs(lean[2][0] - full[2][0]) < 1e-5 * abs(full[2][0]) and abs(lean[2][1] - full[2][1]) < 1e-5 * abs(full[2][1])
     for a, b in zip(lean[0], full[0]):
         assert rel_err(a, b) < 5e-5
     for a, b in zip(lean[1], full[1]):
