@@ -49,7 +49,8 @@ const char* vdnn_build_info(void);
 /* vdnnAlgoMode_t of the reference (vdnn.h:31-36).  MEMORY_OPT = zero-workspace kernels,
  * PERF_OPT = kernels that may use workspace (deterministic split-K partial sums). */
 typedef enum { VDNN_ALGO_MEMORY_OPT = 0, VDNN_ALGO_PERF_OPT = 1, VDNN_ALGO_DYNAMIC = 2 } vdnn_algo_mode;
-typedef enum { VDNN_CONV_FWD = 0, VDNN_CONV_BWD_DATA = 1, VDNN_CONV_BWD_FILTER = 2 } vdnn_conv_op;
+typedef enum { VDNN_CONV_FWD = 0, VDNN_CONV_BWD_DATA = 1, VDNN_CONV_BWD_FILTER = 2,
+               VDNN_CONV_BWD_ALL = 3 /* the three gradients in one workspace: vdnn_conv_bwd_data_filter_bias */ } vdnn_conv_op;
 /* Which contraction engine runs CONV/FC.  AUTO picks TCGEN05 (3xTF32 on the 5th-generation
  * tensor cores, fp32-accurate) when the shape is supported by it and FFMA otherwise.  In PERF_OPT the tensor-core
  * engine has a gather-fed and a TMA-fed kernel family; AUTO uses the TMA-fed one for stride-1 convolutions with
@@ -125,6 +126,18 @@ int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, co
 int vdnn_conv_bwd_filter_bias(const vdnn_conv_desc* d, int algo_mode, float alpha, const float* x, const float* dy,
                               float beta, float* dw, float alpha_b, float beta_b, float* db,
                               void* workspace, size_t workspace_bytes, void* stream);
+
+/* cudnnConvolutionBackwardData + BackwardBias + BackwardFilter of one layer (layer.cu:616-660) in one call:
+ *   dx = alpha_dx * (dy corr^T w) + beta_dx * dx   with the weights as they are on entry (dw may be w),
+ *   db = alpha_b * sum dy + beta_b * db,   dw = alpha_w * (x corr dy) + beta_w * dw.
+ * Workspace: vdnn_conv_workspace_bytes(VDNN_CONV_BWD_ALL, mode, d); the figure for VDNN_CONV_BWD_FILTER is at least as large.
+ * In PERF_OPT, where both gradients run on the TMA-fed kernels (vdnn_conv_bwd_shares_dy), dy is rewritten into operand
+ * images once for both and the bias sums come from the same pass; elsewhere the separate entry points run in the
+ * reference's order. */
+int vdnn_conv_bwd_data_filter_bias(const vdnn_conv_desc* d, int algo_mode, float alpha_dx, const float* w, const float* x,
+                                   const float* dy, float beta_dx, float* dx, float alpha_w, float beta_w, float* dw,
+                                   float alpha_b, float beta_b, float* db, void* workspace, size_t workspace_bytes, void* stream);
+int vdnn_conv_bwd_shares_dy(const vdnn_conv_desc* d, int algo_mode);
 
 /* Filter gradient for callers that cannot provide workspace.  No counterpart in the reference.
  *

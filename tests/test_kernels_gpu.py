@@ -116,6 +116,18 @@ def test_convolution_trio(vdnn, oracle, case, algo, engine):
         ops.conv_bwd_filter_bias(d, xd, dyd, gd, gb, algo_mode=algo, workspace=ws, workspace_bytes=ws_bytes)
         assert rel_err(host(gd), oracle.conv_bwd_filter(x, dy, wt.shape, (pad, pad), (st, st))) < TOL
         assert rel_err(host(gb), oracle.conv_bwd_bias(dy)) < TOL
+        # the three gradients in one call and one workspace (one pass over dy where both gradients are TMA-fed); dw aliases
+        # w as in training: the data gradient must see the weights as they were
+        need = ops.conv_workspace_bytes(3, algo, d)
+        assert need <= max(ws_bytes, ops.conv_workspace_bytes(2, algo, d))
+        ws3 = torch.empty(max(need, 4) // 4, dtype=torch.float32, device="cuda")
+        wupd, bupd = dev(wt), dev(bias)
+        dxd = torch.full((n, c, h, w), -3.0, device="cuda")
+        ops.conv_bwd_data_filter_bias(d, wupd, xd, dyd, dxd, wupd, bupd, alpha_w=-lr, beta_w=1.0, alpha_b=-lr, beta_b=1.0, algo_mode=algo,
+                                      workspace=ws3, workspace_bytes=need)
+        assert rel_err(host(dxd), oracle.conv_bwd_data(wt, dy, x.shape, (pad, pad), (st, st))) < TOL
+        assert rel_err(host(wupd), oracle.conv_bwd_filter(x, dy, wt.shape, (pad, pad), (st, st), alpha=-lr, beta=1.0, dw=wt)) < TOL
+        assert rel_err(host(bupd), oracle.conv_bwd_bias(dy, alpha=-lr, beta=1.0, db=bias)) < TOL
         assert ops.engine_status() == 0
     finally:
         _engine(vdnn, "auto")

@@ -285,8 +285,8 @@ def test_held_blocks_are_given_back_under_pool_pressure(vdnn):
     assert pressed[5] > 0 and roomy[5] == 0 and packed[5] == 0
     for other in (pressed, packed):
         assert other[3] == roomy[3] and other[4] == roomy[4] == peak
-        for a, b in zip(other[0], roomy[0]):
-            assert rel_err(a, b) < 1e-5
+        for a, b in zip(other[0], roomy[0]):       # the zero-workspace kernels sum their reduction splits with atomics
+            assert rel_err(a, b) < 5e-5
         for a, b in zip(other[1], roomy[1]):       # layer 0's bias gradient: 1.6 M terms per channel, summed with atomics
             assert rel_err(a, b) < 2e-3
     assert vdnn.ops.engine_status() == 0

@@ -91,6 +91,8 @@ SIGNATURES = {
     "vdnn_conv_bwd_bias": (_I, [_I, _I, _I, _F, _P, _F, _P, _P]),
     "vdnn_conv_bwd_filter": (_I, [_D, _I, _F, _P, _P, _F, _P, _P, _Z, _P]),
     "vdnn_conv_bwd_filter_bias": (_I, [_D, _I, _F, _P, _P, _F, _P, _F, _F, _P, _P, _Z, _P]),
+    "vdnn_conv_bwd_data_filter_bias": (_I, [_D, _I, _F, _P, _P, _P, _F, _P, _F, _F, _P, _F, _F, _P, _P, _Z, _P]),
+    "vdnn_conv_bwd_shares_dy": (_I, [_D, _I]),
     "vdnn_conv_bwd_filter_static": (_I, [_D, _F, _P, _P, _F, _P, _P]),
     "vdnn_sgemm_workspace_bytes": (_Z, [_I, _I, _I, _I]),
     "vdnn_sgemm": (_I, [_I, _I, _I, _I, _I, _F, _P, _I, _P, _I, _F, _P, _I, _I, _P, _Z, _P]),

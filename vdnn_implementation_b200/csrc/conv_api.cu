@@ -450,6 +450,85 @@ int wgrad_tma(const tma::WgradProblem& q, const float* x, const float* dy, char*
     return VDNN_OK;
 }
 
+// ---- one image pass over dy for both gradients --------------------------------------------------------------------
+// The data gradient's strip engine and the filter gradient both read dy as channels-last tf32 hi / lo images; the strip
+// layout (a padded position list) contains the plain image as a strided view, so where both gradients of a layer run on
+// the TMA-fed kernels one pass writes dy once (and forms the bias sums), and the two kernels run slab by slab from it.
+bool bwd_shared_shape(const vdnn_conv_desc* d, int P, int Q) {
+    if (g_no_tma || !tma_shape(d, VDNN_CONV_BWD_DATA) || !tma_wgrad_shape(d)) return false;
+    return tma_use_strips(tma_problem(d, VDNN_CONV_BWD_DATA, P, Q));
+}
+
+struct BwdSharedPlan { int slab; size_t pack, strips, ximg, partial, total; };
+
+BwdSharedPlan bwd_shared_plan(const vdnn_conv_desc* d, int P, int Q) {
+    BwdSharedPlan plan;
+    tma::Problem q = tma_problem(d, VDNN_CONV_BWD_DATA, P, Q);
+    q.n = 1;
+    plan.slab = tma_slab_images(d->n, tma::strip_image_bytes(q) + tma::image_bytes(1, d->c, d->h, d->w));
+    q.n = plan.slab;
+    plan.pack = packed_weight_bytes(d, VDNN_CONV_BWD_DATA);
+    plan.strips = tma::strip_image_bytes(q);
+    plan.ximg = tma::image_bytes(plan.slab, d->c, d->h, d->w);
+    tma::WgradProblem wq = wgrad_problem(d, P, Q);
+    wq.n = plan.slab;
+    plan.partial = tma::wgrad_partial_bytes(wq);
+    plan.total = plan.pack + plan.strips + plan.ximg + plan.partial;
+    return plan;
+}
+
+// KCRS weights viewed as [c][(tap, ko)]: offset c*RS + tap + ko*C*RS (the B operand of the data gradient).
+SplitDense dgrad_weight_view(const vdnn_conv_desc* d, const float* w) {
+    const int rs = d->r * d->s;
+    SplitDense B;
+    B.p = w; B.rows = d->c; B.cols = d->k * rs;
+    B.row_div = FastDiv(1u << 30); B.row_hi = 0;
+    B.col_div = FastDiv(d->k);
+    B.row_lo = rs; B.col_hi = 1; B.col_lo = d->c * rs;
+    return B;
+}
+
+int bwd_shared_tma(const vdnn_conv_desc* d, int P, int Q, float alpha_dx, const float* w, const float* x, const float* dy, float beta_dx,
+                   float* dx, float alpha_w, float beta_w, float* dw, float alpha_b, float beta_b, float* db, char* ws, size_t ws_bytes,
+                   cudaStream_t s) {
+    const BwdSharedPlan plan = bwd_shared_plan(d, P, Q);
+    if (ws_bytes < plan.total) return VDNN_ERR_WORKSPACE;
+    char* tiles = ws;
+    char* strips = tiles + plan.pack;
+    char* ximg = strips + plan.strips;
+    const tma::Problem q = tma_problem(d, VDNN_CONV_BWD_DATA, P, Q);
+    const tma::StripGeom g = tma::strip_geometry(q);
+    // the weights as they are now: the filter gradient below may update them in place (dw == w)
+    int st = tc::pack_b<SplitDense, false>(dgrad_weight_view(d, w), d->c, d->k * d->r * d->s, s, tiles, tma::strip_tile_n(d->c));
+    if (st != VDNN_OK) return st;
+    if (beta_b == 0.0f) VDNN_CUDA(cudaMemsetAsync(db, 0, sizeof(float) * d->k, s));
+    const size_t dy_img = static_cast<size_t>(d->k) * P * Q, x_img = static_cast<size_t>(d->c) * d->h * d->w;
+    const size_t dx_elems = static_cast<size_t>(d->n) * x_img, dw_elems = static_cast<size_t>(d->k) * d->c * d->r * d->s;
+    const int groups = q.R * (q.cin / 32);
+    tma::WgradProblem wq = wgrad_problem(d, P, Q);
+    for (int n0 = 0; n0 < d->n; n0 += plan.slab) {
+        tma::Problem part = q;
+        part.n = min(plan.slab, d->n - n0);
+        if ((st = tma::strip_prepare(part, dy + n0 * dy_img, strips, s, db, alpha_b)) != VDNN_OK) return st;
+        if ((st = tma::strip_launch(part, nullptr, strips, tiles, dx + n0 * x_img, nullptr, alpha_dx, beta_dx, EPI_DIRECT, dx_elems, 1, groups, s,
+                                    false)) != VDNN_OK)
+            return st;
+        wq.n = part.n;
+        const float* hi = reinterpret_cast<const float*>(strips);
+        const tma::SharedDy shared{hi, hi + static_cast<size_t>(part.n) * g.lp * q.cin, g.wp, g.lp};
+        int splits = 1;
+        float* partial = nullptr;
+        const float b = n0 == 0 ? beta_w : 1.0f;
+        if ((st = tma::wgrad_launch(wq, x + n0 * x_img, nullptr, ximg, dw, alpha_w, b, s, &splits, &partial, nullptr, 0.0f, &shared)) != VDNN_OK)
+            return st;
+        if (splits > 1) {
+            reduce_partials_kernel<<<stream_blocks(dw_elems), 256, 0, s>>>(dw_elems, splits, alpha_w, b, partial, dw);
+            VDNN_LAUNCHED();
+        }
+    }
+    return VDNN_OK;
+}
+
 bool valid_desc(const vdnn_conv_desc* d, int* P, int* Q) {
     if (!d || d->n <= 0 || d->c <= 0 || d->h <= 0 || d->w <= 0 || d->k <= 0 || d->r <= 0 || d->s <= 0 ||
         d->pad_h < 0 || d->pad_w < 0 || d->stride_h <= 0 || d->stride_w <= 0)
@@ -541,11 +620,20 @@ size_t vdnn_conv_workspace_bytes(int op, int algo_mode, const vdnn_conv_desc* d)
     int M, N, K;
     size_t out;
     const int crs = d->c * d->r * d->s;
+    if (op == VDNN_CONV_BWD_ALL) {
+        if (bwd_shared_shape(d, P, Q)) return bwd_shared_plan(d, P, Q).total;
+        const size_t a = vdnn_conv_workspace_bytes(VDNN_CONV_BWD_DATA, algo_mode, d), b = vdnn_conv_workspace_bytes(VDNN_CONV_BWD_FILTER, algo_mode, d);
+        return a > b ? a : b;
+    }
     if (op == VDNN_CONV_BWD_FILTER && tma_wgrad_shape(d)) {
         tma::WgradProblem q = wgrad_problem(d, P, Q);
         q.n = 1;
         q.n = tma_slab_images(d->n, tma::wgrad_image_bytes(q));
-        return tma::wgrad_image_bytes(q) + tma::wgrad_partial_bytes(q);
+        size_t own = tma::wgrad_image_bytes(q) + tma::wgrad_partial_bytes(q);
+        // a caller that sizes the filter gradient's workspace by this figure can also run all three gradients in it
+        // (vdnn_conv_bwd_data_filter_bias)
+        if (bwd_shared_shape(d, P, Q)) { const size_t all = bwd_shared_plan(d, P, Q).total; if (all > own) own = all; }
+        return own;
     }
     if (is_full_extent(d)) {        // runs as the corresponding FC product
         switch (op) {
@@ -739,6 +827,35 @@ int vdnn_conv_bwd_filter_bias(const vdnn_conv_desc* d, int algo_mode, float alph
     if (beta_b == 0.0f) VDNN_CUDA(cudaMemsetAsync(db, 0, sizeof(float) * d->k, as_stream(stream)));
     return wgrad_tma(wgrad_problem(d, P, Q), x, dy, static_cast<char*>(workspace), workspace_bytes, dw, alpha, beta, as_stream(stream),
                      db, alpha_b);
+}
+
+
+// cudnnConvolutionBackwardData, BackwardBias and BackwardFilter of one layer (layer.cu:616-660) in one call and one
+// workspace (vdnn_conv_workspace_bytes(VDNN_CONV_BWD_ALL, ...), which the figure for VDNN_CONV_BWD_FILTER covers).  The data
+// gradient uses the weights as they are on entry, also when dw == w.  Where both gradients run on the TMA-fed engine, dy
+// is rewritten into operand images once for both; otherwise the three separate entry points run in the reference's order.
+int vdnn_conv_bwd_data_filter_bias(const vdnn_conv_desc* d, int algo_mode, float alpha_dx, const float* w, const float* x, const float* dy,
+                                   float beta_dx, float* dx, float alpha_w, float beta_w, float* dw, float alpha_b, float beta_b, float* db,
+                                   void* workspace, size_t workspace_bytes, void* stream) {
+    int P, Q;
+    if (!w || !x || !dy || !dx || !dw || !db || !valid_desc(d, &P, &Q)) return VDNN_ERR_BAD_ARG;
+    const bool shared = algo_mode == VDNN_ALGO_PERF_OPT && g_engine != VDNN_ENGINE_FFMA && workspace &&
+                        (reinterpret_cast<uintptr_t>(workspace) & 127u) == 0 && (beta_b == 0.0f || beta_b == 1.0f) &&
+                        !is_full_extent(d) && fits_int32(d, P, Q) && bwd_shared_shape(d, P, Q);
+    if (shared)
+        return bwd_shared_tma(d, P, Q, alpha_dx, w, x, dy, beta_dx, dx, alpha_w, beta_w, dw, alpha_b, beta_b, db, static_cast<char*>(workspace),
+                              workspace_bytes, as_stream(stream));
+    const int st = vdnn_conv_bwd_data(d, algo_mode, alpha_dx, w, dy, beta_dx, dx, workspace, workspace_bytes, stream);
+    return st != VDNN_OK ? st
+                         : vdnn_conv_bwd_filter_bias(d, algo_mode, alpha_w, x, dy, beta_w, dw, alpha_b, beta_b, db, workspace, workspace_bytes, stream);
+}
+
+// 1 where vdnn_conv_bwd_data_filter_bias shares one pass over dy between the gradients (a host that keeps the three calls
+// apart loses nothing elsewhere).
+int vdnn_conv_bwd_shares_dy(const vdnn_conv_desc* d, int algo_mode) {
+    int P, Q;
+    return (algo_mode == VDNN_ALGO_PERF_OPT && g_engine != VDNN_ENGINE_FFMA && valid_desc(d, &P, &Q) && !is_full_extent(d) &&
+            fits_int32(d, P, Q) && bwd_shared_shape(d, P, Q)) ? 1 : 0;
 }
 
 }  // extern "C"

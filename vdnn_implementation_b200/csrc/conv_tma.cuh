@@ -511,49 +511,61 @@ strip_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__
 }
 
 // NCHW fp32 -> the padded position list of the strip engine, as two images (tf32 hi, lo): position q of image n is
-// (row q / wp, column q % wp); rows >= h and columns >= w are the zero gaps.  One block: 32 channels x 128 PIXELS of one
-// image (reads in full, aligned 128-byte lines along the pixels of a channel), written to the pixels' positions (one
-// 128-byte line per pixel and image half); the thread that writes the last pixel of an image row also zeroes the gap
-// columns behind it, and the first block of every (image, channel block) zeroes the gap rows.
+// (row q / wp, column q % wp); rows >= h and columns >= w are the zero gaps.  A block takes `tiles_per_block` consecutive
+// tiles of 32 channels x 128 PIXELS of one image (reads in full, aligned 128-byte lines along the pixels of a channel),
+// written to the pixels' positions (one 128-byte line per pixel and image half); the thread that writes the last pixel
+// of an image row also zeroes the gap columns behind it, and the first block of every (image, channel block) zeroes the
+// gap rows.  SUMS: also adds scale * (per-channel sums of the block's pixels) into sums[channel] (see
+// nchw_to_split_nhwc_kernel).
+template <bool SUMS>
 __global__ void __launch_bounds__(256) nchw_to_split_strip_kernel(const float* __restrict__ x, float* __restrict__ hi,
-                                                                  float* __restrict__ lo, int C, int H, int W, int wp, int lp) {
+                                                                  float* __restrict__ lo, int C, int H, int W, int wp, int lp,
+                                                                  int tiles_per_block, float* __restrict__ sums, float scale) {
     __shared__ float tile[32][TR_PIX + 1];
-    const int n = blockIdx.z, c0 = blockIdx.y * 32, p0 = blockIdx.x * TR_PIX;
+    const int n = blockIdx.z, c0 = blockIdx.y * 32;
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int HW = H * W;
-    const int npix = min(TR_PIX, HW - p0);
-    const float* src = x + (static_cast<size_t>(n) * C + c0) * HW + p0;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int c = warp * 4 + j;
-#pragma unroll
-        for (int q = 0; q < TR_PIX / 32; ++q) {
-            const int pix = q * 32 + lane;
-            tile[c][pix] = pix < npix ? __ldg(src + static_cast<size_t>(c) * HW + pix) : 0.0f;
-        }
-    }
-    __syncthreads();
     const int quad = t & 7;                     // channels 4 * quad .. + 3
     const size_t base = static_cast<size_t>(n) * lp * C + c0 + quad * 4;
     const float4 zero = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int it = 0; it < tiles_per_block; ++it) {
+        const int p0 = (blockIdx.x * tiles_per_block + it) * TR_PIX;
+        if (p0 >= HW) break;
+        if (it) __syncthreads();                // the tile of the last round has been written out
+        const int npix = min(TR_PIX, HW - p0);
+        const float* src = x + (static_cast<size_t>(n) * C + c0) * HW + p0;
 #pragma unroll
-    for (int pass = 0; pass < TR_PIX / 32; ++pass) {
-        const int pix = pass * 32 + (t >> 3);
-        if (pix < npix) {
-            const int pidx = p0 + pix, row = pidx / W, col = pidx - row * W;
-            const size_t q = static_cast<size_t>(row) * wp + col;
-            float4 h, l;
-            tc::split_tf32_safe(tile[quad * 4 + 0][pix], h.x, l.x);
-            tc::split_tf32_safe(tile[quad * 4 + 1][pix], h.y, l.y);
-            tc::split_tf32_safe(tile[quad * 4 + 2][pix], h.z, l.z);
-            tc::split_tf32_safe(tile[quad * 4 + 3][pix], h.w, l.w);
-            *reinterpret_cast<float4*>(hi + base + q * C) = h;
-            *reinterpret_cast<float4*>(lo + base + q * C) = l;
-            if (col == W - 1)
-                for (int g = 1; g <= wp - W; ++g) {
-                    *reinterpret_cast<float4*>(hi + base + (q + g) * C) = zero;
-                    *reinterpret_cast<float4*>(lo + base + (q + g) * C) = zero;
-                }
+        for (int j = 0; j < 4; ++j) {
+            const int c = warp * 4 + j;
+#pragma unroll
+            for (int q = 0; q < TR_PIX / 32; ++q) {
+                const int pix = q * 32 + lane;
+                const float v = pix < npix ? __ldg(src + static_cast<size_t>(c) * HW + pix) : 0.0f;
+                tile[c][pix] = v;
+                if (SUMS) part[j] += v;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int pass = 0; pass < TR_PIX / 32; ++pass) {
+            const int pix = pass * 32 + (t >> 3);
+            if (pix < npix) {
+                const int pidx = p0 + pix, row = pidx / W, col = pidx - row * W;
+                const size_t q = static_cast<size_t>(row) * wp + col;
+                float4 h, l;
+                tc::split_tf32_safe(tile[quad * 4 + 0][pix], h.x, l.x);
+                tc::split_tf32_safe(tile[quad * 4 + 1][pix], h.y, l.y);
+                tc::split_tf32_safe(tile[quad * 4 + 2][pix], h.z, l.z);
+                tc::split_tf32_safe(tile[quad * 4 + 3][pix], h.w, l.w);
+                *reinterpret_cast<float4*>(hi + base + q * C) = h;
+                *reinterpret_cast<float4*>(lo + base + q * C) = l;
+                if (col == W - 1)
+                    for (int g = 1; g <= wp - W; ++g) {
+                        *reinterpret_cast<float4*>(hi + base + (q + g) * C) = zero;
+                        *reinterpret_cast<float4*>(lo + base + (q + g) * C) = zero;
+                    }
+            }
         }
     }
     if (blockIdx.x == 0)
@@ -561,6 +573,15 @@ __global__ void __launch_bounds__(256) nchw_to_split_strip_kernel(const float* _
             *reinterpret_cast<float4*>(hi + base + static_cast<size_t>(q) * C) = zero;
             *reinterpret_cast<float4*>(lo + base + static_cast<size_t>(q) * C) = zero;
         }
+    if (SUMS) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v = part[j];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) atomicAdd(sums + c0 + warp * 4 + j, scale * v);
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -842,12 +863,15 @@ inline EncodeTiledFn encode_tiled() {
 
 // Tensor map over a channels-last image [n][h][w][c] (fp32, dense) with boxes of 32 channels x bw x bh pixels of one
 // image, 128-byte swizzle, zeros outside the image.
+// row_pitch / image_pitch (pixels; 0 = dense): the image may be a view of a larger one, e.g. the h x w pixels of a padded
+// position list whose rows are row_pitch positions apart and whose images are image_pitch positions apart.
 inline int make_image_map(CUtensorMap* map, const float* image, int n, int h, int w, int c, int bw, int bh,
-                          CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+                          CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B, int row_pitch = 0, long long image_pitch = 0) {
     EncodeTiledFn enc = encode_tiled();
     if (!enc) return VDNN_ERR_UNSUPPORTED;
+    const cuuint64_t rp = row_pitch ? row_pitch : w, ip = image_pitch ? static_cast<cuuint64_t>(image_pitch) : static_cast<cuuint64_t>(h) * w;
     const cuuint64_t dims[4] = {static_cast<cuuint64_t>(c), static_cast<cuuint64_t>(w), static_cast<cuuint64_t>(h), static_cast<cuuint64_t>(n)};
-    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(c) * 4, static_cast<cuuint64_t>(w) * c * 4, static_cast<cuuint64_t>(h) * w * c * 4};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(c) * 4, rp * c * 4, ip * c * 4};
     const cuuint32_t box[4] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(bw), static_cast<cuuint32_t>(bh), 1u};
     const cuuint32_t elem[4] = {1u, 1u, 1u, 1u};
     const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(image), dims, strides, box, elem,
@@ -950,10 +974,32 @@ inline size_t strip_image_bytes(const Problem& q) {
     return 2 * sizeof(float) * static_cast<size_t>(q.n) * g.lp * q.cin;
 }
 
+// Writes the operand images of the strip engine for problem q (strip_image_bytes(q) bytes at `images`).  sums (may be
+// null): cin floats that receive += scale * (per-channel sums of src).
+inline int strip_prepare(const Problem& q, const float* src, char* images, cudaStream_t stream, float* sums = nullptr, float scale = 0.0f) {
+    const StripGeom g = strip_geometry(q);
+    if (!g.ok) return VDNN_ERR_UNSUPPORTED;
+    const size_t elems = static_cast<size_t>(q.n) * g.lp * q.cin;
+    float* hi = reinterpret_cast<float*>(images);
+    float* lo = hi + elems;
+    const int tiles = ceil_div(q.in_h * q.in_w, TR_PIX);
+    if (q.cin / 32 > 65535 || q.n > 65535) return VDNN_ERR_UNSUPPORTED;
+    if (sums) {
+        const int per_block = tiles < 8 ? tiles : 8;        // fewer atomics per channel
+        nchw_to_split_strip_kernel<true><<<dim3(ceil_div(tiles, per_block), q.cin / 32, q.n), 256, 0, stream>>>(
+            src, hi, lo, q.cin, q.in_h, q.in_w, g.wp, g.lp, per_block, sums, scale);
+    } else {
+        nchw_to_split_strip_kernel<false><<<dim3(tiles, q.cin / 32, q.n), 256, 0, stream>>>(src, hi, lo, q.cin, q.in_h, q.in_w, g.wp, g.lp, 1,
+                                                                                           nullptr, 0.0f);
+    }
+    VDNN_LAUNCHED();
+    return VDNN_OK;
+}
+
 // group_chunk: (filter row, channel block) groups per split; splits = ceil(R * cin / 32 / group_chunk).
 template <int BN, int MH>
 int strip_launch_bn(const Problem& q, const float* src, char* images, const char* b_tiles, float* out, const float* bias, float alpha,
-                    float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream) {
+                    float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream, bool prepare) {
     typedef StripConfig<BN, MH> Cfg;
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
@@ -996,10 +1042,10 @@ int strip_launch_bn(const Problem& q, const float* src, char* images, const char
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return VDNN_ERR_CUDA;
     }
-    dim3 tgrid(ceil_div(q.in_h * q.in_w, TR_PIX), q.cin / 32, q.n);
-    if (tgrid.y > 65535u || tgrid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
-    nchw_to_split_strip_kernel<<<tgrid, 256, 0, stream>>>(src, hi, lo, q.cin, q.in_h, q.in_w, g.wp, g.lp);
-    VDNN_LAUNCHED();
+    if (prepare) {
+        const int st = strip_prepare(q, src, images, stream);
+        if (st != VDNN_OK) return st;
+    }
     // persistent along x: as many CTAs as the GPU holds at once (all column tiles and splits of an output tile run side
     // by side, so that they share its strips through L2), each walking every gridDim.x-th output tile
     const long long tiles = ceil_div<long long>(p.total_pos, BM * MH);
@@ -1046,20 +1092,22 @@ inline bool strip_pairs_enabled() {
     return v;
 }
 
+// prepare = false: the images at `images` have been written already (strip_prepare) and src is not read.
 inline int strip_launch(const Problem& q, const float* src, char* images, const char* b_tiles, float* out, const float* bias,
-                        float alpha, float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream) {
+                        float alpha, float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream,
+                        bool prepare = true) {
     const int bn = strip_tile_n(q.n_cols);
     if (bn == 256 && strip_halves(q.n_cols) == 1 && strip_pairs_enabled()) {
-        const int st = pair::strip_pair_launch<256>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
+        const int st = pair::strip_pair_launch<256>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream, prepare);
         if (st != VDNN_ERR_UNSUPPORTED) return st;
     }
     if (strip_halves(q.n_cols) == 2) {
-        if (bn == 64) return strip_launch_bn<64, 2>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
-        return strip_launch_bn<128, 2>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
+        if (bn == 64) return strip_launch_bn<64, 2>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream, prepare);
+        return strip_launch_bn<128, 2>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream, prepare);
     }
-    if (bn == 64) return strip_launch_bn<64, 1>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
-    if (bn == 128) return strip_launch_bn<128, 1>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
-    return strip_launch_bn<256, 1>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream);
+    if (bn == 64) return strip_launch_bn<64, 1>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream, prepare);
+    if (bn == 128) return strip_launch_bn<128, 1>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream, prepare);
+    return strip_launch_bn<256, 1>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream, prepare);
 }
 
 struct WgradProblem {
@@ -1104,10 +1152,17 @@ inline size_t wgrad_partial_bytes(const WgradProblem& q) {
     return splits > 1 ? static_cast<size_t>(splits) * q.k * q.c * q.R * q.S * sizeof(float) : 0;
 }
 
+// The images of dy as the data gradient's strip engine has written them (padded position list: rows wp positions apart,
+// images lp positions apart): the filter gradient reads the h x w pixels of every image through a strided tensor map, so
+// one pass over dy serves both gradients.
+struct SharedDy { const float* hi; const float* lo; int wp; long long lp; };
+
 // bias_sums (may be null): K floats that receive += bias_scale * (per-channel sums of dy) from the dy transform pass.
+// shared (may be null): dy has been written as images already (then dy, bias_sums are not used, and ws holds the x images
+// and the partial sums only).
 template <int BN>
 int wgrad_launch_bn(const WgradProblem& q, const float* x, const float* dy, char* ws, float* dw, float alpha, float beta,
-                    cudaStream_t stream, int* splits_out, float** partial_out, float* bias_sums, float bias_scale) {
+                    cudaStream_t stream, int* splits_out, float** partial_out, float* bias_sums, float bias_scale, const SharedDy* shared) {
     typedef Config<BN> Cfg;
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
@@ -1117,9 +1172,9 @@ int wgrad_launch_bn(const WgradProblem& q, const float* x, const float* dy, char
     const size_t xe = static_cast<size_t>(q.n) * q.c * q.h * q.w, ye = static_cast<size_t>(q.n) * q.k * q.p * q.q;
     float* xh = reinterpret_cast<float*>(ws);
     float* xl = xh + xe;
-    float* yh = xl + xe;
-    float* yl = yh + ye;
-    float* partial = yl + ye;
+    float* yh = shared ? const_cast<float*>(shared->hi) : xl + xe;
+    float* yl = shared ? const_cast<float*>(shared->lo) : yh + ye;
+    float* partial = shared ? xl + xe : yl + ye;
     WgradParams p;
     p.n_img = q.n;
     p.total_boxes = wgrad_boxes(q, &p.bw_log2, &p.bh);
@@ -1139,13 +1194,15 @@ int wgrad_launch_bn(const WgradProblem& q, const float* x, const float* dy, char
     const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B;
     if ((st = make_image_map(&mxh, xh, q.n, q.h, q.w, q.c, bw, p.bh, sw)) != VDNN_OK) return st;
     if ((st = make_image_map(&mxl, xl, q.n, q.h, q.w, q.c, bw, p.bh, sw)) != VDNN_OK) return st;
-    if ((st = make_image_map(&myh, yh, q.n, q.p, q.q, q.k, bw, p.bh, sw)) != VDNN_OK) return st;
-    if ((st = make_image_map(&myl, yl, q.n, q.p, q.q, q.k, bw, p.bh, sw)) != VDNN_OK) return st;
+    if ((st = make_image_map(&myh, yh, q.n, q.p, q.q, q.k, bw, p.bh, sw, shared ? shared->wp : 0, shared ? shared->lp : 0)) != VDNN_OK) return st;
+    if ((st = make_image_map(&myl, yl, q.n, q.p, q.q, q.k, bw, p.bh, sw, shared ? shared->wp : 0, shared ? shared->lp : 0)) != VDNN_OK) return st;
     dim3 tx(ceil_div(q.h * q.w, TR_PIX), q.c / 32, q.n), ty(ceil_div(q.p * q.q, TR_PIX), q.k / 32, q.n);
     if (tx.y > 65535u || tx.z > 65535u || ty.y > 65535u) return VDNN_ERR_UNSUPPORTED;
     nchw_to_split_nhwc_kernel<false><<<tx, 256, 0, stream>>>(x, xh, xl, q.c, q.h * q.w, 1, nullptr, 0.0f);
     VDNN_LAUNCHED();
-    if (bias_sums) {
+    if (shared) {
+        // dy is there already
+    } else if (bias_sums) {
         // several tiles per block: fewer atomics per channel; the grid stays above two waves for every layer of interest
         const int tiles = static_cast<int>(ty.x), per_block = tiles < 8 ? tiles : 8;
         const dim3 tys((tiles + per_block - 1) / per_block, ty.y, ty.z);
@@ -1180,11 +1237,12 @@ inline size_t wgrad_image_bytes(const WgradProblem& q) {
 }
 
 inline int wgrad_launch(const WgradProblem& q, const float* x, const float* dy, char* ws, float* dw, float alpha, float beta,
-                        cudaStream_t stream, int* splits, float** partial, float* bias_sums = nullptr, float bias_scale = 0.0f) {
+                        cudaStream_t stream, int* splits, float** partial, float* bias_sums = nullptr, float bias_scale = 0.0f,
+                        const SharedDy* shared = nullptr) {
     const int bn = tc::tile_n(q.k);
-    if (bn == 64) return wgrad_launch_bn<64>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale);
-    if (bn == 128) return wgrad_launch_bn<128>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale);
-    return wgrad_launch_bn<256>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale);
+    if (bn == 64) return wgrad_launch_bn<64>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale, shared);
+    if (bn == 128) return wgrad_launch_bn<128>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale, shared);
+    return wgrad_launch_bn<256>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale, shared);
 }
 
 }  // namespace tma

@@ -267,7 +267,7 @@ strip_pair_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
 // Same arguments as strip_launch_bn; the tile is 256 positions x BNP columns per CTA pair.
 template <int BNP>
 int strip_pair_launch(const Problem& q, const float* src, char* images, const char* b_tiles, float* out, const float* bias,
-                             float alpha, float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream) {
+                      float alpha, float beta, int mode, size_t partial_stride, int splits, int group_chunk, cudaStream_t stream, bool prepare) {
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
     typedef PairCfg<BNP> Cfg;
@@ -319,10 +319,10 @@ int strip_pair_launch(const Problem& q, const float* src, char* images, const ch
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) return VDNN_ERR_CUDA;
     }
-    dim3 tgrid(ceil_div(q.in_h * q.in_w, TR_PIX), q.cin / 32, q.n);
-    if (tgrid.y > 65535u || tgrid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
-    nchw_to_split_strip_kernel<<<tgrid, 256, 0, stream>>>(src, hi, lo, q.cin, q.in_h, q.in_w, g.wp, g.lp);
-    VDNN_LAUNCHED();
+    if (prepare) {
+        const int st = strip_prepare(q, src, images, stream);
+        if (st != VDNN_OK) return st;
+    }
     if (ny > 65535 || splits > 65535) return VDNN_ERR_UNSUPPORTED;
     // persistent along x: as many CTA pairs as the GPU holds at once
     cudaLaunchConfig_t cfg = {};

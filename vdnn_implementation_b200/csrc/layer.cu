@@ -361,10 +361,16 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
         const int a = handle->alloc(&curWorkSpace, bwdDataWorkSpaceSize, layerId, TAG_WS, isDynamic, {*stream_compute});
         if (a != 0) return a;
     }
+    // Where both gradients run on the TMA-fed kernels, one pass over dy serves them: the three gradients are then computed
+    // by ONE call inside the filter gradient's workspace window below, and the data gradient's window (allocated and
+    // released here as the reference's schedule has it) stays unused.
+    const bool sharedDy = opMode[1] == VDNN_ALGO_PERF_OPT && opMode[2] == VDNN_ALGO_PERF_OPT &&
+                          vdnn_conv_bwd_shares_dy(&d, VDNN_ALGO_PERF_OPT) != 0;
     // data gradient with the weights as they were in forward
-    DEV(vdnn_conv_bwd_data(&d, opMode[1], 1.0f, (const float*)filterData, (const float*)diffData, 0.0f, (float*)gradData,
-                           curWorkSpace, workSpace != NULL ? caller_workspace_bytes(handle, workSpace) : bwdDataWorkSpaceSize,
-                           *stream_compute));
+    if (!sharedDy)
+        DEV(vdnn_conv_bwd_data(&d, opMode[1], 1.0f, (const float*)filterData, (const float*)diffData, 0.0f, (float*)gradData,
+                               curWorkSpace, workSpace != NULL ? caller_workspace_bytes(handle, workSpace) : bwdDataWorkSpaceSize,
+                               *stream_compute));
     if (workSpace == NULL && bwdDataWorkSpaceSize > 0) {
         MARK(ev_bwd_done);
         const int f = handle->release(curWorkSpace, bwdDataWorkSpaceSize, layerId, TAG_WS, {*stream_compute});
@@ -378,10 +384,17 @@ int Layer::convolutionBackward(int _layer_id_to_prefetch, DATATYPE* _prefetchedS
         const int a = handle->alloc(&curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, isDynamic, {*stream_compute});
         if (a != 0) return a;
     }
-    DEV(vdnn_conv_bwd_filter_bias(&d, opMode[2], staged ? 1.0f : lr, (const float*)srcData, (const float*)diffData,
-                                  staged ? 0.0f : 1.0f, staged ? gradFilter : (float*)filterData,
-                                  staged ? 1.0f : lr, staged ? 0.0f : 1.0f, staged ? gradBias : (float*)biasData, curWorkSpace,
-                                  workSpace != NULL ? caller_workspace_bytes(handle, workSpace) : bwdFilterWorkSpaceSize, *stream_compute));
+    const size_t filterWsBytes = workSpace != NULL ? caller_workspace_bytes(handle, workSpace) : bwdFilterWorkSpaceSize;
+    if (sharedDy)
+        DEV(vdnn_conv_bwd_data_filter_bias(&d, VDNN_ALGO_PERF_OPT, 1.0f, (const float*)filterData, (const float*)srcData,
+                                           (const float*)diffData, 0.0f, (float*)gradData, staged ? 1.0f : lr, staged ? 0.0f : 1.0f,
+                                           staged ? gradFilter : (float*)filterData, staged ? 1.0f : lr, staged ? 0.0f : 1.0f,
+                                           staged ? gradBias : (float*)biasData, curWorkSpace, filterWsBytes, *stream_compute));
+    else
+        DEV(vdnn_conv_bwd_filter_bias(&d, opMode[2], staged ? 1.0f : lr, (const float*)srcData, (const float*)diffData,
+                                      staged ? 0.0f : 1.0f, staged ? gradFilter : (float*)filterData,
+                                      staged ? 1.0f : lr, staged ? 0.0f : 1.0f, staged ? gradBias : (float*)biasData, curWorkSpace,
+                                      filterWsBytes, *stream_compute));
     MARK(ev_bwd_done);
     if (workSpace == NULL && bwdFilterWorkSpaceSize > 0)
         return handle->release(curWorkSpace, bwdFilterWorkSpaceSize, layerId, TAG_WS, {*stream_compute});

@@ -63,6 +63,17 @@ def conv_bwd_filter_bias(desc, x, dy, dw, db, alpha=1.0, beta=0.0, alpha_b=1.0, 
                                           _p(workspace), workspace_bytes, _s(stream)), "conv_bwd_filter_bias")
 
 
+def conv_bwd_data_filter_bias(desc, w, x, dy, dx, dw, db, alpha_dx=1.0, beta_dx=0.0, alpha_w=1.0, beta_w=0.0, alpha_b=1.0, beta_b=0.0,
+                              algo_mode=0, workspace=None, workspace_bytes=0, stream=0):
+    check(lib().vdnn_conv_bwd_data_filter_bias(C.byref(desc), algo_mode, alpha_dx, _p(w), _p(x), _p(dy), beta_dx, _p(dx), alpha_w, beta_w,
+                                               _p(dw), alpha_b, beta_b, _p(db), _p(workspace), workspace_bytes, _s(stream)),
+          "conv_bwd_data_filter_bias")
+
+
+def conv_bwd_shares_dy(desc, algo_mode):
+    return bool(lib().vdnn_conv_bwd_shares_dy(C.byref(desc), algo_mode))
+
+
 STATIC_SCRATCH_BYTES = 16 << 20
 
 
