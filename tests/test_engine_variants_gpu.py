@@ -1,6 +1,7 @@
 """The kernel variants that the defaults do not reach, each checked against the oracle by running the convolution parity
 cases in a child process with the switch that selects it: the 256-column strip kernel and the 256-filter filter
-gradient on single CTAs (the defaults run them on CTA pairs), the first TMA engine (boxes of 32 pixels per tap, the
+gradient on single CTAs (the defaults run them on CTA pairs), the filter gradient's tile shapes forced either way, the
+first TMA engine (boxes of 32 pixels per tap, the
 fallback for filters wider than nine taps), and PERF_OPT on the gather-fed kernels alone."""
 import os
 import subprocess
@@ -14,6 +15,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 @pytest.mark.parametrize("switches", [
     {"VDNN_STRIP_PAIRS": "0", "VDNN_WGRAD_PAIRS": "0"},
+    {"VDNN_WGRAD_SHAPE": "tall"},
+    {"VDNN_WGRAD_SHAPE": "flat"},
     {"VDNN_TMA_BOXES": "1"},
     {"VDNN_TMA_WGRAD": "0"},
     {"VDNN_NO_TMA": "1"},

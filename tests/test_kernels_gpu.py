@@ -50,6 +50,7 @@ CONV_CASES = [  # n, c, h, w, k, r, pad, stride
     (9, 64, 40, 24, 64, 3, 1, 1),      # many tiles of 64 columns, tiles that straddle images
     (2, 32, 12, 12, 160, 3, 1, 1),     # 256-column tiles on CTA pairs with an odd number of row tiles: the last pair is half empty
     (3, 288, 10, 10, 512, 3, 1, 1),    # two full 256-column tiles, 81 row groups (ragged last row tile), pairs in every kernel
+    (2, 128, 16, 16, 128, 3, 1, 1),    # 128 filters, 36 row groups: the filter gradient's two-half tiles (the fifth is half empty)
 ]
 ENGINES = ["ffma", "tcgen05"]
 

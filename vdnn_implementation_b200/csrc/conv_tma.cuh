@@ -623,12 +623,27 @@ __device__ __forceinline__ uint64_t make_desc_mn(uint32_t saddr) {
     return d;
 }
 
-template <int BN>
+// MH = 128-row halves of a tile (MH * four row groups).  A tile's dy slice (BN * 256 bytes per k block) is fetched once
+// for all its rows, and the SM's ingest rate is what bounds the narrow tiles: with 128 or 64 filters a CTA takes two
+// halves (a quarter / a sixth fewer bytes per flop); with 256 filters the tensor memory holds one (2 * MH * BN <= 512).
+template <int BN, int MH> struct WgradConfig {
+    static_assert(MH == 1 || (MH == 2 && BN <= 128), "two row halves need 4 * BN <= 512 columns of tensor memory");
+    static constexpr int B_TILE_BYTES = BN * BK * 4;
+    static constexpr int A_BYTES = MH * 2 * A_TILE_BYTES;                 // hi and lo of every half
+    static constexpr int STAGE_BYTES = A_BYTES + 2 * B_TILE_BYTES;
+    static constexpr int STAGES = MH == 2 ? 2 : (BN == 256 ? 2 : (BN == 128 ? 3 : 4));
+    static constexpr int TMEM_COLS = 2 * MH * BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+    static constexpr uint32_t IDESC = tc::Config<BN>::IDESC;
+};
+
+template <int BN, int MH>
 __global__ void __launch_bounds__(THREADS, 1)
 wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ CUtensorMap x_lo,
              const __grid_constant__ CUtensorMap dy_hi, const __grid_constant__ CUtensorMap dy_lo, const WgradParams p) {
-    typedef Config<BN> Cfg;
+    typedef WgradConfig<BN, MH> Cfg;
     constexpr int S = Cfg::STAGES;
+    constexpr int GROUPS = MH * BOXES;                                       // row groups of a tile
     constexpr uint32_t IDESC_MN = Cfg::IDESC | (1u << 15) | (1u << 16);      // both operands MN-major
     extern __shared__ char smem_raw[];
     char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -654,7 +669,7 @@ wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ C
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == DRAIN_WARPS + 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(tmem_slot)), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(tmem_slot)), "r"(Cfg::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -666,9 +681,11 @@ wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ C
         constexpr int NACC = BN / (DRAIN_WARPS / 4);
         const int col_beg = (warp >> 2) * NACC;
         const uint32_t tmem_mine = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(col_beg);
-        float acc[NACC];
+        float acc[MH][NACC];
 #pragma unroll
-        for (int j = 0; j < NACC; ++j) acc[j] = 0.0f;
+        for (int h = 0; h < MH; ++h)
+#pragma unroll
+            for (int j = 0; j < NACC; ++j) acc[h][j] = 0.0f;
         bool alive = true;
         for (int pair = 0; pair < npairs && alive; ++pair) {
             const int b = pair & 1;
@@ -677,19 +694,23 @@ wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ C
             if (!ok) { atomicCAS(&tc::g_tc_error, 0, 103); alive = false; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int c = 0; c < NACC; c += 16) {
-                float v[16];
-                tc::tmem_ld16(tmem_mine + static_cast<uint32_t>(b * BN + c), v);
+            for (int h = 0; h < MH; ++h)
 #pragma unroll
-                for (int j = 0; j < 16; ++j) acc[c + j] += v[j];
-            }
+                for (int c = 0; c < NACC; c += 16) {
+                    float v[16];
+                    tc::tmem_ld16(tmem_mine + static_cast<uint32_t>((b * MH + h) * BN + c), v);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) acc[h][c + j] += v[j];
+                }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) tc::mbar_arrive(tc::smem_u32(&bars[2 * S + 2 + b]));
         }
-        // this thread's row: row group (warp & 3) of the tile, channel `lane` of its block
-        const int group = blockIdx.x * BOXES + (warp & 3);
-        if (alive && group < p.row_groups) {
+        // this thread's rows: row group (warp & 3) of every half of the tile, channel `lane` of its block
+#pragma unroll
+        for (int h = 0; h < MH; ++h) {
+            const int group = (blockIdx.x * MH + h) * BOXES + (warp & 3);
+            if (!alive || group >= p.row_groups) continue;
             const int tap = group / p.cblocks, cb = group - tap * p.cblocks;
             const size_t crs = static_cast<size_t>(p.C) * p.taps;
             float* o = p.out + static_cast<size_t>(cb * 32 + lane) * p.taps + tap;
@@ -700,24 +721,24 @@ wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ C
                 if (col < p.n_cols) {
                     float* q = o + static_cast<size_t>(col) * crs;
                     if (p.mode == EPI_DIRECT) {
-                        float v = p.alpha * acc[j];
+                        float v = p.alpha * acc[h][j];
                         if (p.beta != 0.0f) v = fmaf(p.beta, *q, v);
                         *q = v;
                     } else if (p.mode == EPI_ATOMIC) {
-                        atomicAdd(q, p.alpha * acc[j]);
+                        atomicAdd(q, p.alpha * acc[h][j]);
                     } else {
-                        *q = acc[j];
+                        *q = acc[h][j];
                     }
                 }
             }
         }
     } else if (warp == DRAIN_WARPS) {
         if (lane == 0) {
-            int gc[BOXES], gdy[BOXES], gdx[BOXES];
+            int gc[GROUPS], gdy[GROUPS], gdx[GROUPS];
             int groups = 0;
 #pragma unroll
-            for (int j = 0; j < BOXES; ++j) {
-                const int group = blockIdx.x * BOXES + j;
+            for (int j = 0; j < GROUPS; ++j) {
+                const int group = blockIdx.x * GROUPS + j;
                 if (group < p.row_groups) {
                     const int tap = group / p.cblocks, cb = group - tap * p.cblocks;
                     const int r = tap / p.taps_s, sx = tap - r * p.taps_s;
@@ -741,15 +762,17 @@ wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ C
                 const uint32_t st = tc::smem_u32(tiles + s * Cfg::STAGE_BYTES);
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(stage_tx) : "memory");
 #pragma unroll
-                for (int j = 0; j < BOXES; ++j) {
+                for (int j = 0; j < GROUPS; ++j) {
                     if (j < groups) {
-                        tma_load_box(st + j * BOX_BYTES, &x_hi, bar, gc[j], x0 + gdx[j], y0 + gdy[j], static_cast<int>(n));
-                        tma_load_box(st + A_TILE_BYTES + j * BOX_BYTES, &x_lo, bar, gc[j], x0 + gdx[j], y0 + gdy[j], static_cast<int>(n));
+                        // half j / BOXES: [hi tile][lo tile], group j % BOXES inside each
+                        const uint32_t a = st + (j / BOXES) * 2 * A_TILE_BYTES + (j % BOXES) * BOX_BYTES;
+                        tma_load_box(a, &x_hi, bar, gc[j], x0 + gdx[j], y0 + gdy[j], static_cast<int>(n));
+                        tma_load_box(a + A_TILE_BYTES, &x_lo, bar, gc[j], x0 + gdx[j], y0 + gdy[j], static_cast<int>(n));
                     }
                 }
                 for (int j = 0; j < col_boxes; ++j) {
-                    tma_load_box(st + 2 * A_TILE_BYTES + j * BOX_BYTES, &dy_hi, bar, n0 + j * 32, x0, y0, static_cast<int>(n));
-                    tma_load_box(st + 2 * A_TILE_BYTES + Cfg::B_TILE_BYTES + j * BOX_BYTES, &dy_lo, bar, n0 + j * 32, x0, y0, static_cast<int>(n));
+                    tma_load_box(st + Cfg::A_BYTES + j * BOX_BYTES, &dy_hi, bar, n0 + j * 32, x0, y0, static_cast<int>(n));
+                    tma_load_box(st + Cfg::A_BYTES + Cfg::B_TILE_BYTES + j * BOX_BYTES, &dy_lo, bar, n0 + j * 32, x0, y0, static_cast<int>(n));
                 }
             }
         }
@@ -764,14 +787,17 @@ wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ C
             }
             if (!tc::mbar_wait(tc::smem_u32(&bars[s]), phase)) { atomicCAS(&tc::g_tc_error, 0, 102); break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_hi = tc::smem_u32(tiles + s * Cfg::STAGE_BYTES);
-            const uint32_t a_lo = a_hi + A_TILE_BYTES;
-            const uint32_t b_hi = a_hi + 2 * A_TILE_BYTES;
+            const uint32_t a0 = tc::smem_u32(tiles + s * Cfg::STAGE_BYTES);
+            const uint32_t b_hi = a0 + Cfg::A_BYTES;
             const uint32_t b_lo = b_hi + Cfg::B_TILE_BYTES;
-            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(b * BN);
-            // one k slice = 8 pixels = 1024 bytes further into every strip
-            tc::mma_block_3xtf32<1024 / 16>(d_tmem, make_desc_mn(a_hi), make_desc_mn(a_lo), make_desc_mn(b_hi), make_desc_mn(b_lo),
-                                            IDESC_MN, !(i & 1));
+            const uint64_t dbh = make_desc_mn(b_hi), dbl = make_desc_mn(b_lo);
+#pragma unroll
+            for (int h = 0; h < MH; ++h) {      // the row halves share the dy slice
+                const uint32_t a_hi = a0 + h * 2 * A_TILE_BYTES, a_lo = a_hi + A_TILE_BYTES;
+                // one k slice = 8 pixels = 1024 bytes further into every strip
+                tc::mma_block_3xtf32<1024 / 16>(tmem_base + static_cast<uint32_t>((b * MH + h) * BN), make_desc_mn(a_hi), make_desc_mn(a_lo),
+                                                dbh, dbl, IDESC_MN, !(i & 1));
+            }
             tc::mma_commit(tc::smem_u32(&bars[S + s]));
             if ((i & 1) || i == nkb - 1) tc::mma_commit(tc::smem_u32(&bars[2 * S + b]));
         }
@@ -781,7 +807,7 @@ wgrad_kernel(const __grid_constant__ CUtensorMap x_hi, const __grid_constant__ C
     __syncthreads();
     if (warp == DRAIN_WARPS + 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(2 * BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::TMEM_COLS) : "memory");
     }
 }
 
@@ -1126,9 +1152,21 @@ inline bool wgrad_pairs_enabled(int bn) {
 
 // Reduction split for the filter gradient: the tiles (row-group quadruples x column tiles) are few, the reduction over
 // pixel boxes is long; as many splits as fill two waves of CTAs, at least two boxes each.
+// Row halves of a filter-gradient tile.  Measured (B200, batch 128): 128 -> 128 @ 112 x 112 (36 row groups) 3.39 ms with
+// one half, 3.20 with two; 64 -> 128 @ 112 x 112 (18 groups: the third two-half tile is mostly padding) 2.03 / 2.05;
+// 64 -> 64 @ 224 x 224 5.86 / 6.02.  So: two halves for 128-filter tiles with at least 32 row groups.
+// VDNN_WGRAD_SHAPE=flat / tall: one half everywhere / two wherever the tensor memory holds them (comparison runs).
+inline int wgrad_halves(int bn, int row_groups) {
+    static const int force = []() { const char* e = getenv("VDNN_WGRAD_SHAPE"); return !e ? 0 : (e[0] == 'f' ? 1 : (e[0] == 't' ? 2 : 0)); }();
+    if (force == 1 || bn > 128) return 1;
+    if (force == 2) return 2;
+    return (bn == 128 && row_groups >= 32) ? 2 : 1;
+}
+
 inline void wgrad_plan(const WgradProblem& q, int total_boxes, int* splits, int* box_chunk) {
     const int bn = tc::tile_n(q.k);
-    int row_tiles = ceil_div(q.R * q.S * (q.c / 32), BOXES);
+    const int row_groups = q.R * q.S * (q.c / 32);
+    int row_tiles = ceil_div(row_groups, BOXES * wgrad_halves(bn, row_groups));
     if (wgrad_pairs_enabled(bn)) row_tiles = (row_tiles + 1) / 2 * 2;          // CTA pairs take two row tiles each
     const long tiles = static_cast<long>(row_tiles) * ceil_div(q.k, bn);
     long s = (2L * sm_count()) / tiles;
@@ -1160,13 +1198,13 @@ struct SharedDy { const float* hi; const float* lo; int wp; long long lp; };
 // bias_sums (may be null): K floats that receive += bias_scale * (per-channel sums of dy) from the dy transform pass.
 // shared (may be null): dy has been written as images already (then dy, bias_sums are not used, and ws holds the x images
 // and the partial sums only).
-template <int BN>
+template <int BN, int MH>
 int wgrad_launch_bn(const WgradProblem& q, const float* x, const float* dy, char* ws, float* dw, float alpha, float beta,
                     cudaStream_t stream, int* splits_out, float** partial_out, float* bias_sums, float bias_scale, const SharedDy* shared) {
-    typedef Config<BN> Cfg;
+    typedef WgradConfig<BN, MH> Cfg;
     int dev = 0;
     VDNN_CUDA(cudaGetDevice(&dev));
-    auto kern = wgrad_kernel<BN>;
+    auto kern = wgrad_kernel<BN, MH>;
     if (VDNN_ONCE_PER_DEVICE(dev))
         VDNN_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
     const size_t xe = static_cast<size_t>(q.n) * q.c * q.h * q.w, ye = static_cast<size_t>(q.n) * q.k * q.p * q.q;
@@ -1211,7 +1249,7 @@ int wgrad_launch_bn(const WgradProblem& q, const float* x, const float* dy, char
         nchw_to_split_nhwc_kernel<false><<<ty, 256, 0, stream>>>(dy, yh, yl, q.k, q.p * q.q, 1, nullptr, 0.0f);
     }
     VDNN_LAUNCHED();
-    dim3 grid(ceil_div(p.row_groups, BOXES), ceil_div(q.k, BN), splits);
+    dim3 grid(ceil_div(p.row_groups, BOXES * MH), ceil_div(q.k, BN), splits);
     if (grid.y > 65535u || grid.z > 65535u) return VDNN_ERR_UNSUPPORTED;
     if constexpr (BN == 256) {
         if (wgrad_pairs_enabled(BN)) {
@@ -1240,9 +1278,13 @@ inline int wgrad_launch(const WgradProblem& q, const float* x, const float* dy, 
                         cudaStream_t stream, int* splits, float** partial, float* bias_sums = nullptr, float bias_scale = 0.0f,
                         const SharedDy* shared = nullptr) {
     const int bn = tc::tile_n(q.k);
-    if (bn == 64) return wgrad_launch_bn<64>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale, shared);
-    if (bn == 128) return wgrad_launch_bn<128>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale, shared);
-    return wgrad_launch_bn<256>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale, shared);
+    if (wgrad_halves(bn, q.R * q.S * (q.c / 32)) == 2) {
+        if (bn == 64) return wgrad_launch_bn<64, 2>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale, shared);
+        return wgrad_launch_bn<128, 2>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale, shared);
+    }
+    if (bn == 64) return wgrad_launch_bn<64, 1>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale, shared);
+    if (bn == 128) return wgrad_launch_bn<128, 1>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale, shared);
+    return wgrad_launch_bn<256, 1>(q, x, dy, ws, dw, alpha, beta, stream, splits, partial, bias_sums, bias_scale, shared);
 }
 
 }  // namespace tma
