@@ -3,8 +3,9 @@
     python opbench.py --engine tcgen05 --batch 32
     python opbench.py --engine tcgen05 --batch 32 --layer 5 --op fwd --reps 3   (one kernel, for ncu)
 
-Times vdnn_conv_fwd / vdnn_conv_bwd_data / vdnn_conv_bwd_filter through the C ABI with CUDA events on
-the launching stream; PyTorch only owns the buffers.  Prints algorithmic TFLOP/s (2*M*N*K per call).
+Times vdnn_conv_fwd / vdnn_conv_bwd_data / vdnn_conv_bwd_filter (and, with --op bwd, the three gradients in one call:
+vdnn_conv_bwd_data_filter_bias) through the C ABI with CUDA events on the launching stream; PyTorch only owns the
+buffers.  Prints algorithmic TFLOP/s (2*M*N*K per call; twice that for bwd).
 """
 import argparse
 
@@ -55,7 +56,7 @@ def main():
     ap.add_argument("--engine", default="tcgen05", choices=["ffma", "tcgen05"])
     ap.add_argument("--batch", type=int, default=32)
     ap.add_argument("--layer", type=int, default=-1, help="index into the VGG16 shape list; -1 = all")
-    ap.add_argument("--op", default="all", choices=["all", "fwd", "dgrad", "wgrad", "elementwise"])
+    ap.add_argument("--op", default="all", choices=["all", "fwd", "dgrad", "wgrad", "bwd", "elementwise"])
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--algo", type=int, default=1, help="0 MEMORY_OPT, 1 PERF_OPT")
     args = ap.parse_args()
@@ -64,7 +65,7 @@ def main():
     n = args.batch
     if args.op == "elementwise":
         return elementwise(ops, n, args)
-    total = {"fwd": 0.0, "dgrad": 0.0, "wgrad": 0.0}
+    total = {"fwd": 0.0, "dgrad": 0.0, "wgrad": 0.0, "bwd": 0.0}
     flops = 0.0
     for idx, (c, k, h) in enumerate(SHAPES):
         if args.layer >= 0 and idx != args.layer:
@@ -77,27 +78,29 @@ def main():
         dx = torch.empty_like(x)
         dw = torch.empty_like(w)
         bias = torch.zeros(k, device="cuda")
-        need = max(ops.conv_workspace_bytes(op, args.algo, d) for op in range(3))
+        need = max(ops.conv_workspace_bytes(op, args.algo, d) for op in range(4))
         ws = torch.empty(max(need, 4) // 4, device="cuda")
         calls = {
             "fwd": lambda: ops.conv_fwd(d, x, w, y, bias=bias, algo_mode=args.algo, workspace=ws, workspace_bytes=need),
             "dgrad": lambda: ops.conv_bwd_data(d, w, dy, dx, algo_mode=args.algo, workspace=ws, workspace_bytes=need),
             "wgrad": lambda: ops.conv_bwd_filter(d, x, dy, dw, alpha=-0.01, beta=1.0, algo_mode=args.algo, workspace=ws,
                                                  workspace_bytes=need),
+            "bwd": lambda: ops.conv_bwd_data_filter_bias(d, w, x, dy, dx, dw, bias, alpha_w=-0.01, beta_w=1.0, alpha_b=-0.01, beta_b=1.0,
+                                                         algo_mode=args.algo, workspace=ws, workspace_bytes=need),
         }
         fl = 2.0 * n * h * h * k * c * 9
         flops += fl
         line = f"conv {c:4d}->{k:4d} @{h:3d}x{h:<3d} batch {n}:"
         for name, fn in calls.items():
-            if args.op not in ("all", name):
+            if args.op != name and not (args.op == "all" and name != "bwd"):
                 continue
             ms = timeit(fn, args.reps)
             total[name] += ms
-            line += f"  {name} {ms:8.3f} ms {fl / ms / 1e9:7.1f} TFLOP/s"
+            line += f"  {name} {ms:8.3f} ms {(2 if name == 'bwd' else 1) * fl / ms / 1e9:7.1f} TFLOP/s"
         print(line, flush=True)
     for name, ms in total.items():
         if ms > 0:
-            print(f"{name}: {ms:.2f} ms, {flops / ms / 1e9:.1f} TFLOP/s")
+            print(f"{name}: {ms:.2f} ms, {(2 if name == 'bwd' else 1) * flops / ms / 1e9:.1f} TFLOP/s")
     print("engine status", ops.engine_status())
 
 

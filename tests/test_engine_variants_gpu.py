@@ -15,6 +15,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 @pytest.mark.parametrize("switches", [
     {"VDNN_STRIP_PAIRS": "0", "VDNN_WGRAD_PAIRS": "0"},
+    {"VDNN_WGRAD_STRIPS": "0"},
     {"VDNN_WGRAD_SHAPE": "tall"},
     {"VDNN_WGRAD_SHAPE": "flat"},
     {"VDNN_TMA_BOXES": "1"},

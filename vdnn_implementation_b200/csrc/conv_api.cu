@@ -459,20 +459,31 @@ bool bwd_shared_shape(const vdnn_conv_desc* d, int P, int Q) {
     return tma_use_strips(tma_problem(d, VDNN_CONV_BWD_DATA, P, Q));
 }
 
-struct BwdSharedPlan { int slab; size_t pack, strips, ximg, partial, total; };
+// The filter gradient of layers with at most 128 filters can run on the two position lists themselves
+// (conv_tma_wstrip.cuh: one strip of x per filter row instead of one box per tap).  VDNN_WGRAD_STRIPS=0 switches it off.
+bool g_wgrad_strips = []() { const char* e = getenv("VDNN_WGRAD_STRIPS"); return !e || e[0] != '0'; }();
+
+bool bwd_wstrip_shape(const vdnn_conv_desc* d, int P, int Q) {
+    return g_wgrad_strips && tma::wstrip_filters_ok(d->k, d->c) &&
+           tma::wstrip_ok(tma_problem(d, VDNN_CONV_FWD, P, Q), tma_problem(d, VDNN_CONV_BWD_DATA, P, Q));
+}
+
+struct BwdSharedPlan { int slab; bool wstrip; size_t pack, strips, ximg, partial, total; };
 
 BwdSharedPlan bwd_shared_plan(const vdnn_conv_desc* d, int P, int Q) {
     BwdSharedPlan plan;
-    tma::Problem q = tma_problem(d, VDNN_CONV_BWD_DATA, P, Q);
-    q.n = 1;
-    plan.slab = tma_slab_images(d->n, tma::strip_image_bytes(q) + tma::image_bytes(1, d->c, d->h, d->w));
-    q.n = plan.slab;
+    plan.wstrip = bwd_wstrip_shape(d, P, Q);
+    tma::Problem q = tma_problem(d, VDNN_CONV_BWD_DATA, P, Q), fq = tma_problem(d, VDNN_CONV_FWD, P, Q);
+    q.n = 1; fq.n = 1;
+    const size_t x_one = plan.wstrip ? tma::strip_image_bytes(fq) : tma::image_bytes(1, d->c, d->h, d->w);
+    plan.slab = tma_slab_images(d->n, tma::strip_image_bytes(q) + x_one);
+    q.n = plan.slab; fq.n = plan.slab;
     plan.pack = packed_weight_bytes(d, VDNN_CONV_BWD_DATA);
     plan.strips = tma::strip_image_bytes(q);
-    plan.ximg = tma::image_bytes(plan.slab, d->c, d->h, d->w);
+    plan.ximg = plan.wstrip ? tma::strip_image_bytes(fq) : tma::image_bytes(plan.slab, d->c, d->h, d->w);
     tma::WgradProblem wq = wgrad_problem(d, P, Q);
     wq.n = plan.slab;
-    plan.partial = tma::wgrad_partial_bytes(wq);
+    plan.partial = plan.wstrip ? tma::wstrip_partial_bytes(fq, d->k) : tma::wgrad_partial_bytes(wq);
     plan.total = plan.pack + plan.strips + plan.ximg + plan.partial;
     return plan;
 }
@@ -519,8 +530,16 @@ int bwd_shared_tma(const vdnn_conv_desc* d, int P, int Q, float alpha_dx, const 
         int splits = 1;
         float* partial = nullptr;
         const float b = n0 == 0 ? beta_w : 1.0f;
-        if ((st = tma::wgrad_launch(wq, x + n0 * x_img, nullptr, ximg, dw, alpha_w, b, s, &splits, &partial, nullptr, 0.0f, &shared)) != VDNN_OK)
+        if (plan.wstrip) {
+            // x as a position list of the same pitch; the filter gradient runs on the two lists
+            tma::Problem fpart = tma_problem(d, VDNN_CONV_FWD, P, Q);
+            fpart.n = part.n;
+            if ((st = tma::strip_prepare(fpart, x + n0 * x_img, ximg, s)) != VDNN_OK) return st;
+            partial = reinterpret_cast<float*>(ximg + tma::strip_image_bytes(fpart));
+            if ((st = tma::wstrip_launch(fpart, d->k, ximg, strips, partial, dw, alpha_w, b, s, &splits)) != VDNN_OK) return st;
+        } else if ((st = tma::wgrad_launch(wq, x + n0 * x_img, nullptr, ximg, dw, alpha_w, b, s, &splits, &partial, nullptr, 0.0f, &shared)) != VDNN_OK) {
             return st;
+        }
         if (splits > 1) {
             reduce_partials_kernel<<<stream_blocks(dw_elems), 256, 0, s>>>(dw_elems, splits, alpha_w, b, partial, dw);
             VDNN_LAUNCHED();

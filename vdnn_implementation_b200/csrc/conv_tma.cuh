@@ -1136,6 +1136,8 @@ inline int strip_launch(const Problem& q, const float* src, char* images, const 
     return strip_launch_bn<256, 1>(q, src, images, b_tiles, out, bias, alpha, beta, mode, partial_stride, splits, group_chunk, stream, prepare);
 }
 
+#include "conv_tma_wstrip.cuh"
+
 struct WgradProblem {
     int n, c, h, w;          // x
     int k, p, q;             // dy: n x k x p x q
