@@ -141,7 +141,7 @@ def test_policies_agree_at_full_width(vdnn):
     for policy, (loss, ws, bs) in seen.items():
         assert abs(loss[0] - ref[0][0]) < 1e-5 * abs(ref[0][0]) and abs(loss[1] - ref[0][1]) < 1e-5 * abs(ref[0][1]), policy
         for a, b in zip(ws + bs, ref[1] + ref[2]):
-            assert rel_err(a, b) < 1e-5, policy
+            assert rel_err(a, b) < 5e-5, policy
 
 
 def test_resident_batch_is_reused_correctly_across_steps(vdnn):
