@@ -450,6 +450,135 @@ int wgrad_tma(const tma::WgradProblem& q, const float* x, const float* dy, char*
     return VDNN_OK;
 }
 
+// Filter gradient (and bias gradient) for layers with very few input channels and a 3 x 3 / stride-1 filter (VGG16's
+// first layer: C = 3).  As a contraction it has 27 rows: a 128-row tensor-core tile is four fifths empty and the gather
+// that feeds it costs more than the arithmetic.  Here a block walks tiles of 8 x 32 output pixels of one image; dy of
+// 64 filters and the x halo lie in shared memory; thread (filter kk, row set g) keeps the sums of its filter for up to
+// three (channel, filter row) pairs x three taps in registers, reading four dy values (one LDS.128) and, per pair, six x
+// values (warp-uniform, broadcast) for 12 multiply-adds.  Every block leaves its sums as one partial result
+// (partial_w[block][K][C][3][3], partial_b[block][K]); reduce_partials_kernel adds the blocks up in index order.
+constexpr int WSC_TR = 8, WSC_TC = 32, WSC_KT = 64;
+constexpr int WSC_DY_PITCH = WSC_TR * WSC_TC + 4;        // floats per filter in shared memory (+4: conflict-free LDS.128)
+constexpr int WSC_X_PITCH = WSC_TC + 4;                  // 34 columns of halo, padded to a multiple of four floats
+
+template <int C>
+__global__ void __launch_bounds__(256, 3) wgrad_small_c_kernel(const float* __restrict__ x, const float* __restrict__ dy,
+                                                               float* __restrict__ partial_w, float* __restrict__ partial_b, int N, int H,
+                                                               int W, int K, int P, int Q, int pad_h, int pad_w, int tiles_y,
+                                                               int tiles_x) {
+    extern __shared__ float wsc_smem[];
+    float* dyS = wsc_smem;                                               // [WSC_KT][WSC_DY_PITCH]
+    float* xS = wsc_smem + WSC_KT * WSC_DY_PITCH;                        // [C][WSC_TR + 2][WSC_X_PITCH]
+    constexpr int PAIRS = C * 3;                                         // (channel, filter row)
+    constexpr int MINE = (PAIRS + 3) / 4;                                // per row set
+    const int t = threadIdx.x, kk = t & 63, g = t >> 6;
+    const int k0 = blockIdx.y * WSC_KT;
+    float acc[MINE][3];
+#pragma unroll
+    for (int j = 0; j < MINE; ++j) acc[j][0] = acc[j][1] = acc[j][2] = 0.0f;
+    float bsum = 0.0f;
+    const long long tiles = static_cast<long long>(N) * tiles_y * tiles_x;
+    const size_t pq = static_cast<size_t>(P) * Q, hw = static_cast<size_t>(H) * W;
+    for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int n = static_cast<int>(tile / (tiles_y * tiles_x)), rem = static_cast<int>(tile - static_cast<long long>(n) * tiles_y * tiles_x);
+        const int p0 = (rem / tiles_x) * WSC_TR, q0 = (rem % tiles_x) * WSC_TC;
+        __syncthreads();                                                 // the last tile has been consumed
+        // dy: 64 filters x 8 rows x 32 columns, float4 along a row (Q is a multiple of 4: checked by the host)
+        for (int i = t; i < WSC_KT * WSC_TR * (WSC_TC / 4); i += 256) {
+            const int c4 = i % (WSC_TC / 4), row = (i / (WSC_TC / 4)) % WSC_TR, k = i / (WSC_TC / 4 * WSC_TR);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k0 + k < K && p0 + row < P && q0 + c4 * 4 < Q)
+                v = __ldg(reinterpret_cast<const float4*>(dy + (static_cast<size_t>(n) * K + k0 + k) * pq + static_cast<size_t>(p0 + row) * Q + q0) + c4);
+            *reinterpret_cast<float4*>(dyS + k * WSC_DY_PITCH + row * WSC_TC + c4 * 4) = v;
+        }
+        // x halo: rows p0 - pad_h .. + 9, columns q0 - pad_w .. + 33
+        for (int i = t; i < C * (WSC_TR + 2) * (WSC_TC + 2); i += 256) {
+            const int col = i % (WSC_TC + 2), row = (i / (WSC_TC + 2)) % (WSC_TR + 2), c = i / ((WSC_TC + 2) * (WSC_TR + 2));
+            const int ih = p0 - pad_h + row, iw = q0 - pad_w + col;
+            float v = 0.0f;
+            if (static_cast<unsigned>(ih) < static_cast<unsigned>(H) && static_cast<unsigned>(iw) < static_cast<unsigned>(W))
+                v = __ldg(x + (static_cast<size_t>(n) * C + c) * hw + static_cast<size_t>(ih) * W + iw);
+            xS[(c * (WSC_TR + 2) + row) * WSC_X_PITCH + col] = v;
+        }
+        __syncthreads();
+        const float* dk = dyS + kk * WSC_DY_PITCH;
+#pragma unroll 2
+        for (int pr = 0; pr < WSC_TR; ++pr) {
+#pragma unroll
+            for (int q4 = 0; q4 < WSC_TC / 4; ++q4) {
+                const float4 d = *reinterpret_cast<const float4*>(dk + pr * WSC_TC + q4 * 4);
+                if (g == 0) bsum += (d.x + d.y) + (d.z + d.w);
+#pragma unroll
+                for (int j = 0; j < MINE; ++j) {
+                    const int pair = g + 4 * j;                          // warp-uniform
+                    if (pair < PAIRS) {
+                        const int c = pair / 3, r = pair - c * 3;
+                        const float* xr = xS + (c * (WSC_TR + 2) + pr + r) * WSC_X_PITCH + q4 * 4;
+                        const float4 a = *reinterpret_cast<const float4*>(xr);
+                        const float2 b = *reinterpret_cast<const float2*>(xr + 4);
+                        acc[j][0] = fmaf(d.x, a.x, fmaf(d.y, a.y, fmaf(d.z, a.z, fmaf(d.w, a.w, acc[j][0]))));
+                        acc[j][1] = fmaf(d.x, a.y, fmaf(d.y, a.z, fmaf(d.z, a.w, fmaf(d.w, b.x, acc[j][1]))));
+                        acc[j][2] = fmaf(d.x, a.z, fmaf(d.y, a.w, fmaf(d.z, b.x, fmaf(d.w, b.y, acc[j][2]))));
+                    }
+                }
+            }
+        }
+    }
+    if (k0 + kk < K) {
+        float* o = partial_w + (static_cast<size_t>(blockIdx.x) * K + k0 + kk) * (C * 9);
+#pragma unroll
+        for (int j = 0; j < MINE; ++j) {
+            const int pair = g + 4 * j;
+            if (pair < PAIRS) { o[pair * 3 + 0] = acc[j][0]; o[pair * 3 + 1] = acc[j][1]; o[pair * 3 + 2] = acc[j][2]; }
+        }
+        if (g == 0) partial_b[static_cast<size_t>(blockIdx.x) * K + k0 + kk] = bsum;
+    }
+}
+
+bool wgrad_small_c_shape(const vdnn_conv_desc* d, int Q) {
+    return d->c <= SMALL_C_MAX && d->c >= 1 && d->r == 3 && d->s == 3 && d->stride_h == 1 && d->stride_w == 1 && Q % 4 == 0 && d->k % 4 == 0 &&
+           !is_full_extent(d);
+}
+int wgrad_small_c_blocks() { return sm_count() * 3; }
+size_t wgrad_small_c_bytes(const vdnn_conv_desc* d) {
+    return static_cast<size_t>(wgrad_small_c_blocks()) * d->k * (d->c * 9 + 1) * sizeof(float);
+}
+
+// dw = alpha * (x corr dy) + beta * dw and, when db is given, db = alpha_b * sum dy + beta_b * db.
+int wgrad_small_c(const vdnn_conv_desc* d, int P, int Q, const float* x, const float* dy, float alpha, float beta, float* dw, float alpha_b,
+                  float beta_b, float* db, char* ws, size_t ws_bytes, cudaStream_t s) {
+    if (ws_bytes < wgrad_small_c_bytes(d)) return VDNN_ERR_WORKSPACE;
+    const int blocks = wgrad_small_c_blocks();
+    float* partial_w = reinterpret_cast<float*>(ws);
+    float* partial_b = partial_w + static_cast<size_t>(blocks) * d->k * d->c * 9;
+    const int tiles_y = ceil_div(P, WSC_TR), tiles_x = ceil_div(Q, WSC_TC);
+    const size_t smem = (static_cast<size_t>(WSC_KT) * WSC_DY_PITCH + static_cast<size_t>(d->c) * (WSC_TR + 2) * WSC_X_PITCH) * sizeof(float);
+    dim3 grid(blocks, ceil_div(d->k, WSC_KT));
+    int dev = 0;
+    VDNN_CUDA(cudaGetDevice(&dev));
+#define WSC_LAUNCH(CC)                                                                                                                   \
+    {                                                                                                                                   \
+        if (VDNN_ONCE_PER_DEVICE(dev)) VDNN_CUDA(cudaFuncSetAttribute(wgrad_small_c_kernel<CC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 80 * 1024)); \
+        wgrad_small_c_kernel<CC><<<grid, 256, smem, s>>>(x, dy, partial_w, partial_b, d->n, d->h, d->w, d->k, P, Q, d->pad_h, d->pad_w, tiles_y, tiles_x); \
+    }
+    switch (d->c) {
+    case 1: WSC_LAUNCH(1) break;
+    case 2: WSC_LAUNCH(2) break;
+    case 3: WSC_LAUNCH(3) break;
+    default: WSC_LAUNCH(4) break;
+    }
+#undef WSC_LAUNCH
+    VDNN_LAUNCHED();
+    const size_t we = static_cast<size_t>(d->k) * d->c * 9;
+    reduce_partials_kernel<<<stream_blocks(we), 256, 0, s>>>(we, blocks, alpha, beta, partial_w, dw);
+    VDNN_LAUNCHED();
+    if (db) {
+        reduce_partials_kernel<<<stream_blocks(d->k), 256, 0, s>>>(static_cast<size_t>(d->k), blocks, alpha_b, beta_b, partial_b, db);
+        VDNN_LAUNCHED();
+    }
+    return VDNN_OK;
+}
+
 // ---- one image pass over dy for both gradients --------------------------------------------------------------------
 // The data gradient's strip engine and the filter gradient both read dy as channels-last tf32 hi / lo images; the strip
 // layout (a padded position list) contains the plain image as a strided view, so where both gradients of a layer run on
@@ -668,6 +797,7 @@ size_t vdnn_conv_workspace_bytes(int op, int algo_mode, const vdnn_conv_desc* d)
     case VDNN_CONV_BWD_FILTER: M = crs; N = d->k; K = d->n * P * Q; out = static_cast<size_t>(M) * N; break;
     default: return 0;
     }
+    if (op == VDNN_CONV_BWD_FILTER && wgrad_small_c_shape(d, Q)) return wgrad_small_c_bytes(d);
     const SplitPlan plan = plan_split(M, N, K);
     size_t bytes = plan.splits > 1 ? static_cast<size_t>(plan.splits) * out * sizeof(float) : 0;
     if (op == VDNN_CONV_FWD || op == VDNN_CONV_BWD_DATA) bytes += packed_weight_bytes(d, op);
@@ -795,6 +925,9 @@ int vdnn_conv_bwd_filter(const vdnn_conv_desc* d, int algo_mode, float alpha, co
     const int crs = d->c * d->r * d->s, pq = P * Q;
     if (is_full_extent(d))      // W[k][j] = alpha * sum_n X[n][j] dY[n][k] + beta * W[k][j]   (layer.cu:736-744)
         return vdnn_sgemm(0, 1, crs, d->k, d->n, alpha, x, crs, dy, d->k, beta, dw, crs, algo_mode, workspace, workspace_bytes, stream);
+    if (algo_mode == VDNN_ALGO_PERF_OPT && g_engine != VDNN_ENGINE_FFMA && wgrad_small_c_shape(d, Q) && workspace &&
+        (reinterpret_cast<uintptr_t>(dy) & 15u) == 0 && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0)
+        return wgrad_small_c(d, P, Q, x, dy, alpha, beta, dw, 0.0f, 0.0f, nullptr, static_cast<char*>(workspace), workspace_bytes, as_stream(stream));
     // D[j][k] = sum over pixels of x(j; pixel) * dy(k; pixel), written to dw[k*CRS + j]: the expensive operand, the
     // gathered input, supplies the 128 tile rows; dy supplies up to 256 columns, so every gathered element feeds up to
     // 256 multiply-adds and layers with few filters (K = 64) still fill the tile's rows.
@@ -839,6 +972,9 @@ int vdnn_conv_bwd_filter_bias(const vdnn_conv_desc* d, int algo_mode, float alph
     const bool combined = algo_mode == VDNN_ALGO_PERF_OPT && !is_full_extent(d) && tma_wgrad_shape(d) && g_engine != VDNN_ENGINE_FFMA && workspace &&
                           (reinterpret_cast<uintptr_t>(workspace) & 127u) == 0 && (beta_b == 0.0f || beta_b == 1.0f) &&
                           fits_int32(d, P, Q);
+    if (!combined && algo_mode == VDNN_ALGO_PERF_OPT && g_engine != VDNN_ENGINE_FFMA && wgrad_small_c_shape(d, Q) && workspace && fits_int32(d, P, Q) &&
+        (reinterpret_cast<uintptr_t>(dy) & 15u) == 0 && (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0)
+        return wgrad_small_c(d, P, Q, x, dy, alpha, beta, dw, alpha_b, beta_b, db, static_cast<char*>(workspace), workspace_bytes, as_stream(stream));
     if (!combined) {
         const int st = vdnn_conv_bwd_bias(d->n, d->k, P * Q, alpha_b, dy, beta_b, db, stream);
         return st != VDNN_OK ? st : vdnn_conv_bwd_filter(d, algo_mode, alpha, x, dy, beta, dw, workspace, workspace_bytes, stream);
