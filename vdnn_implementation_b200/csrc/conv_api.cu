@@ -579,6 +579,100 @@ int wgrad_small_c(const vdnn_conv_desc* d, int P, int Q, const float* x, const f
     return VDNN_OK;
 }
 
+// Forward for the same few-channel 3 x 3 / stride-1 layers: y[n][k][p][q] = alpha * sum x * w + bias[k] + beta * y.  A block
+// computes a tile of 8 x 32 output pixels of one image for 64 filters; the x halo and the 64 x (C * 9) weights (stored
+// tap-major, filter innermost) lie in shared memory; a thread owns four neighbouring pixels of one row and 16 filters:
+// 64 accumulators, per (channel, filter row) six x values and per tap 16 weights (warp-uniform LDS.128, broadcast) for 64
+// multiply-adds.  The reduction has 27 terms: as a tensor-core tile it would be one k block per CTA.
+template <int C>
+__global__ void __launch_bounds__(256, 2) fwd_small_c_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                             const float* __restrict__ bias, float* __restrict__ y, int N, int H, int W,
+                                                             int K, int P, int Q, int pad_h, int pad_w, int tiles_y, int tiles_x, float alpha,
+                                                             float beta) {
+    extern __shared__ float fsc_smem[];
+    float* wS = fsc_smem;                                                // [C * 9][WSC_KT]
+    float* xS = fsc_smem + C * 9 * WSC_KT;                               // [C][WSC_TR + 2][WSC_X_PITCH]
+    const int t = threadIdx.x, quad = t & 63, kg = t >> 6;               // pixel quad of the tile, group of 16 filters
+    const int pr = quad >> 3, q4 = quad & 7;
+    const int k0 = blockIdx.y * WSC_KT;
+    for (int i = t; i < C * 9 * WSC_KT; i += 256) {
+        const int k = i % WSC_KT, tap = i / WSC_KT;                     // tap = c * 9 + r * 3 + s
+        wS[i] = k0 + k < K ? __ldg(w + static_cast<size_t>(k0 + k) * (C * 9) + tap) : 0.0f;
+    }
+    const long long tiles = static_cast<long long>(N) * tiles_y * tiles_x;
+    const size_t pq = static_cast<size_t>(P) * Q, hw = static_cast<size_t>(H) * W;
+    for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        const int n = static_cast<int>(tile / (tiles_y * tiles_x)), rem = static_cast<int>(tile - static_cast<long long>(n) * tiles_y * tiles_x);
+        const int p0 = (rem / tiles_x) * WSC_TR, q0 = (rem % tiles_x) * WSC_TC;
+        __syncthreads();                                                 // the last tile's halo has been consumed (and wS is written)
+        for (int i = t; i < C * (WSC_TR + 2) * (WSC_TC + 2); i += 256) {
+            const int col = i % (WSC_TC + 2), row = (i / (WSC_TC + 2)) % (WSC_TR + 2), c = i / ((WSC_TC + 2) * (WSC_TR + 2));
+            const int ih = p0 - pad_h + row, iw = q0 - pad_w + col;
+            float v = 0.0f;
+            if (static_cast<unsigned>(ih) < static_cast<unsigned>(H) && static_cast<unsigned>(iw) < static_cast<unsigned>(W))
+                v = __ldg(x + (static_cast<size_t>(n) * C + c) * hw + static_cast<size_t>(ih) * W + iw);
+            xS[(c * (WSC_TR + 2) + row) * WSC_X_PITCH + col] = v;
+        }
+        __syncthreads();
+        float acc[16][4];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+#pragma unroll
+            for (int r = 0; r < 3; ++r) {
+                const float* xr = xS + (c * (WSC_TR + 2) + pr + r) * WSC_X_PITCH + q4 * 4;
+                const float4 a = *reinterpret_cast<const float4*>(xr);
+                const float2 b = *reinterpret_cast<const float2*>(xr + 4);
+                const float xv[6] = {a.x, a.y, a.z, a.w, b.x, b.y};
+#pragma unroll
+                for (int sx = 0; sx < 3; ++sx) {
+                    const float* wk = wS + ((c * 3 + r) * 3 + sx) * WSC_KT + kg * 16;
+#pragma unroll
+                    for (int j4 = 0; j4 < 4; ++j4) {
+                        const float4 wv = *reinterpret_cast<const float4*>(wk + j4 * 4);
+                        const float ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) acc[j4 * 4 + j][i] = fmaf(ww[j], xv[sx + i], acc[j4 * 4 + j][i]);
+                    }
+                }
+            }
+        const int p = p0 + pr, q = q0 + q4 * 4;
+        if (p < P && q < Q) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int k = k0 + kg * 16 + j;
+                if (k >= K) break;
+                float4* o = reinterpret_cast<float4*>(y + (static_cast<size_t>(n) * K + k) * pq + static_cast<size_t>(p) * Q + q);
+                const float bk = bias ? __ldg(bias + k) : 0.0f;
+                float4 v = make_float4(fmaf(alpha, acc[j][0], bk), fmaf(alpha, acc[j][1], bk), fmaf(alpha, acc[j][2], bk), fmaf(alpha, acc[j][3], bk));
+                if (beta != 0.0f) { const float4 old = *o; v.x = fmaf(beta, old.x, v.x); v.y = fmaf(beta, old.y, v.y); v.z = fmaf(beta, old.z, v.z); v.w = fmaf(beta, old.w, v.w); }
+                *o = v;
+            }
+        }
+    }
+}
+
+int fwd_small_c(const vdnn_conv_desc* d, int P, int Q, float alpha, const float* x, const float* w, const float* bias, float beta, float* y,
+                cudaStream_t s) {
+    const int tiles_y = ceil_div(P, WSC_TR), tiles_x = ceil_div(Q, WSC_TC);
+    const size_t smem = (static_cast<size_t>(d->c) * 9 * WSC_KT + static_cast<size_t>(d->c) * (WSC_TR + 2) * WSC_X_PITCH) * sizeof(float);
+    const long long tiles = static_cast<long long>(d->n) * tiles_y * tiles_x;
+    long long blocks = static_cast<long long>(sm_count()) * 2;
+    if (blocks > tiles) blocks = tiles;
+    dim3 grid(static_cast<unsigned>(blocks), ceil_div(d->k, WSC_KT));
+    switch (d->c) {
+    case 1: fwd_small_c_kernel<1><<<grid, 256, smem, s>>>(x, w, bias, y, d->n, d->h, d->w, d->k, P, Q, d->pad_h, d->pad_w, tiles_y, tiles_x, alpha, beta); break;
+    case 2: fwd_small_c_kernel<2><<<grid, 256, smem, s>>>(x, w, bias, y, d->n, d->h, d->w, d->k, P, Q, d->pad_h, d->pad_w, tiles_y, tiles_x, alpha, beta); break;
+    case 3: fwd_small_c_kernel<3><<<grid, 256, smem, s>>>(x, w, bias, y, d->n, d->h, d->w, d->k, P, Q, d->pad_h, d->pad_w, tiles_y, tiles_x, alpha, beta); break;
+    default: fwd_small_c_kernel<4><<<grid, 256, smem, s>>>(x, w, bias, y, d->n, d->h, d->w, d->k, P, Q, d->pad_h, d->pad_w, tiles_y, tiles_x, alpha, beta); break;
+    }
+    VDNN_LAUNCHED();
+    return VDNN_OK;
+}
+
 // ---- one image pass over dy for both gradients --------------------------------------------------------------------
 // The data gradient's strip engine and the filter gradient both read dy as channels-last tf32 hi / lo images; the strip
 // layout (a padded position list) contains the plain image as a strided view, so where both gradients of a layer run on
@@ -817,6 +911,9 @@ int vdnn_conv_fwd(const vdnn_conv_desc* d, int algo_mode, float alpha, const flo
         if (st != VDNN_OK || !bias) return st;
         return vdnn_add_bias(d->n, d->k, 1, 1.0f, bias, y, stream);
     }
+    // few input channels, 3 x 3, stride 1 (the first layer of VGG16): 27 terms per output, an FFMA kernel of its own
+    if (g_engine != VDNN_ENGINE_FFMA && wgrad_small_c_shape(d, Q) && (reinterpret_cast<uintptr_t>(y) & 15u) == 0)
+        return fwd_small_c(d, P, Q, alpha, x, w, bias, beta, y, as_stream(stream));
     Epilogue e{};
     e.out = y; e.bias = bias; e.alpha = alpha; e.beta = beta;
     e.row_div = FastDiv(pq); e.row_hi = d->k * pq; e.row_lo = 1; e.col_stride = pq;
