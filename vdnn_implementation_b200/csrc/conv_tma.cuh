@@ -1,16 +1,27 @@
-// TMA-fed convolution engine for sm_100a (PERF_OPT forward and data gradient of stride-1 convolutions whose
-// reduction channel count is a multiple of 32).
+// TMA-fed convolution engines for sm_100a (PERF_OPT, stride-1 convolutions whose channel counts are multiples of 32).
 //
-// The gathered operand is first rewritten once, by a bandwidth-bound pass, into two channels-last images in
-// workspace: hi = tf32(x) and lo = x - hi, both [n][row][col][channel] fp32.  The contraction kernel then spends no
-// instruction on operand elements at all:
+// The gathered operands are first rewritten once, by bandwidth-bound passes, into channels-last images in workspace:
+// hi = tf32(x) and lo = x - hi, fp32 containers, 32-channel blocks of 128 bytes.  The contraction kernels then spend no
+// instruction on operand elements: a warp of its own issues cp.async.bulk.tensor loads that complete the stage's
+// "full" barrier by byte count, one thread issues the 3xTF32 tcgen05.mma sequence of gemm_tc.cuh, and 16 warps add each
+// finished accumulator buffer (two k blocks = 24 chained MMAs) into fp32 registers and run the epilogue.  In this file:
+//   conv_kernel          forward / data gradient, one set of four 32-pixel boxes per filter tap (the first design; the
+//                        fallback for filters wider than nine taps);
+//   strip_kernel         forward / data gradient on a padded position list: one strip per filter row serves its taps
+//                        through shifted descriptors; persistent CTAs; tiles of 128 x 64, 256 x 128 or 128 x 256;
+//   wgrad_kernel         filter gradient, both operands MN-major, one box per (tap, channel block) row group;
+//   conv_tma_pair.cuh    (included below) the 256-column cases of the last two on CTA pairs (tcgen05 cta_group::2);
+//   conv_tma_wstrip.cuh  (included below) the filter gradient on two position lists, taps as 128-byte shifts of a
+//                        tile's row groups;
+//   the image passes (nchw_to_split_*), tensor-map construction and the launch plans.
+// The box kernel in detail:
 //   warp 16    one thread issues, per 32-wide k block (one filter tap, 32 channels), eight tiled
 //              cp.async.bulk.tensor loads -- four 32-pixel boxes of the hi image and of the lo image, shifted by the
 //              tap, zero-filled by the TMA unit outside the image (that is the padding) -- plus one cp.async.bulk for
 //              the packed weight tile; all nine complete the stage's "full" barrier by byte count;
 //   warp 17    allocates TMEM and issues the 3xTF32 tcgen05.mma sequence of gemm_tc.cuh on the stage;
-//   warps 0-15 add each finished accumulator buffer (two k blocks = 24 chained MMAs) into fp32 registers and run the
-//              epilogue (alpha / beta / bias / split-K partials), as in gemm_tc.cuh.
+//   warps 0-15 add each finished accumulator buffer into fp32 registers and run the epilogue (alpha / beta / bias /
+//              split-K partials), as in gemm_tc.cuh.
 // An output tile is 128 pixels = four boxes of bw x bh = 32 pixels of one image; the box shape is chosen per layer
 // so that the boxes cover the output grid with the least overhang.  Every barrier wait is bounded.
 //
