@@ -130,7 +130,8 @@ int vdnn_conv_bwd_filter_bias(const vdnn_conv_desc* d, int algo_mode, float alph
 /* cudnnConvolutionBackwardData + BackwardBias + BackwardFilter of one layer (layer.cu:616-660) in one call:
  *   dx = alpha_dx * (dy corr^T w) + beta_dx * dx   with the weights as they are on entry (dw may be w),
  *   db = alpha_b * sum dy + beta_b * db,   dw = alpha_w * (x corr dy) + beta_w * dw.
- * Workspace: vdnn_conv_workspace_bytes(VDNN_CONV_BWD_ALL, mode, d); the figure for VDNN_CONV_BWD_FILTER is at least as large.
+ * Workspace: vdnn_conv_workspace_bytes(VDNN_CONV_BWD_ALL, mode, d); where vdnn_conv_bwd_shares_dy is 1 the figure for
+ * VDNN_CONV_BWD_FILTER is at least as large, elsewhere it is the larger of the two separate figures.
  * In PERF_OPT, where both gradients run on the TMA-fed kernels (vdnn_conv_bwd_shares_dy), dy is rewritten into operand
  * images once for both and the bias sums come from the same pass; elsewhere the separate entry points run in the
  * reference's order. */

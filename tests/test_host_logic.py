@@ -342,3 +342,33 @@ def test_lean_offload_schedule_on_the_bookkeeping_pool(vdnn):
         a, _, _ = run(policy, False)
         b, _, _ = run(policy, True)
         assert a["offload_bytes"] == b["offload_bytes"] and a["pool_peak_bytes"] == b["pool_peak_bytes"]
+
+
+def test_backward_in_one_workspace_is_covered_by_the_filter_gradient_figure(vdnn):
+    """Where the two gradients share an image pass over dy, vdnn_conv_bwd_data_filter_bias runs inside the filter gradient's
+    workspace window of the reference's schedule, so the figure reported for VDNN_CONV_BWD_FILTER must cover what the
+    combined call needs (VDNN_CONV_BWD_ALL) there; elsewhere VDNN_CONV_BWD_ALL is the larger of the two separate figures.
+    VGG16's first layer (3 channels) is the one layer of that network that does not share, and the workspace stays at
+    about 1 GiB whatever the batch size."""
+    L = vdnn.lib()
+    for model, batch in (("VGG16_128", 128), ("VGG16_256", 256), ("ALEXNET", 128), ("OVERFEAT", 128)):
+        net = vdnn.Network(model, "VDNN_NONE", "VDNN_PERF_OPT_ALGO", device=-1, pool_bytes=int(60e9))
+        try:
+            specs = net.layer_specs()
+        finally:
+            net.close()
+        shares = []
+        for sp in specs:
+            if sp.type not in (vdnn.CONV, vdnn.FC_CONV):
+                continue
+            d = vdnn.ConvDesc(sp.n, sp.c, sp.h, sp.w, sp.k, sp.r, sp.s, sp.pad_h, sp.pad_w, sp.stride_h, sp.stride_w)
+            everything, filt = L.vdnn_conv_workspace_bytes(3, 1, C.byref(d)), L.vdnn_conv_workspace_bytes(2, 1, C.byref(d))
+            data = L.vdnn_conv_workspace_bytes(1, 1, C.byref(d))
+            shares.append(L.vdnn_conv_bwd_shares_dy(C.byref(d), 1))
+            if shares[-1]:
+                assert everything <= filt <= int(1.25 * 2 ** 30), (model, sp.astuple())
+            else:
+                assert everything == max(data, filt), (model, sp.astuple())
+            assert L.vdnn_conv_workspace_bytes(3, 0, C.byref(d)) == 0 and L.vdnn_conv_bwd_shares_dy(C.byref(d), 0) == 0
+        if model.startswith("VGG16"):
+            assert shares == [0] + [1] * 12

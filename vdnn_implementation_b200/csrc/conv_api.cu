@@ -1083,7 +1083,8 @@ int vdnn_conv_bwd_filter_bias(const vdnn_conv_desc* d, int algo_mode, float alph
 
 
 // cudnnConvolutionBackwardData, BackwardBias and BackwardFilter of one layer (layer.cu:616-660) in one call and one
-// workspace (vdnn_conv_workspace_bytes(VDNN_CONV_BWD_ALL, ...), which the figure for VDNN_CONV_BWD_FILTER covers).  The data
+// workspace (vdnn_conv_workspace_bytes(VDNN_CONV_BWD_ALL, ...), which the figure for VDNN_CONV_BWD_FILTER covers where the
+// gradients share an image pass).  The data
 // gradient uses the weights as they are on entry, also when dw == w.  Where both gradients run on the TMA-fed engine, dy
 // is rewritten into operand images once for both; otherwise the three separate entry points run in the reference's order.
 int vdnn_conv_bwd_data_filter_bias(const vdnn_conv_desc* d, int algo_mode, float alpha_dx, const float* w, const float* x, const float* dy,
