@@ -244,7 +244,7 @@ def pcie_probe(torch, device, mib=1024, reps=3):
     d2h, h2d = run(True, False)[0], run(False, True)[1]
     both = run(True, True)
     return {"d2h_alone_gbs": d2h, "h2d_alone_gbs": h2d, "d2h_with_h2d_gbs": both[0], "h2d_with_d2h_gbs": both[1],
-            "how": f"{mib} MiB pinned <-> device copies on two streams, best of {reps}, CUDA events"}
+            "pcie_how": f"{mib} MiB pinned <-> device copies on two streams, best of {reps}, CUDA events"}
 
 
 def tf32_probe(torch, vdnn, stream):
@@ -267,7 +267,7 @@ def tf32_probe(torch, vdnn, stream):
     sustained = once(20000, 80)                                      # ~2 s back to back
     assert ops.engine_status() == 0
     return {"tf32_dense_tflops_burst": burst, "tf32_dense_tflops_sustained": sustained,
-            "how": "vdnn_engine_mma_rate_probe: one CTA per SM issuing tcgen05.mma kind::tf32 128x256x8 on resident operands"}
+            "tf32_how": "vdnn_engine_mma_rate_probe: one CTA per SM issuing tcgen05.mma kind::tf32 128x256x8 on resident operands"}
 
 
 def reference_warm(args, policies):
