@@ -297,7 +297,14 @@ template <int BN, int MH> struct StripConfig {
     static constexpr int B_TILE_BYTES = BN * BK * 4;
     static constexpr int A_STAGE_BYTES = MH * 2 * STRIP_HALF_BYTES;
     static constexpr int B_STAGE_BYTES = 2 * B_TILE_BYTES;
-    static constexpr int TMEM_COLS = 2 * MH * BN;
+    // MERGED (64-column tiles): the hi and the lo weight tile lie back to back, so ONE MMA of 2 * BN columns forms
+    // a_hi * b_hi and a_hi * b_lo side by side, and a second one of BN columns adds a_lo * b_hi to the first half: two
+    // instructions per k slice instead of three, and the A operand is read from shared memory twice instead of three
+    // times -- what bounds the 64-column kernels is the tensor core's operand reads and the one issuing thread.  The
+    // accumulator is 2 * BN columns wide; the drain adds the halves.
+    static constexpr bool MERGED = (BN == 64 && MH == 1);
+    static constexpr int ACC_COLS = MERGED ? 2 * BN : BN;
+    static constexpr int TMEM_COLS = 2 * MH * ACC_COLS;
     // Ring depths.  A strip is in use for S k blocks, i.e. S * 6 * BN clocks of MMA work, and its refill (a TMA box of
     // ~130 rows gathered from rows C * 4 bytes apart) takes a few thousand clocks to land: narrow tiles need more strips
     // in flight than wide ones.  Measured with two strips: 256 columns 77 % tensor-pipe activity (bound by the SM's ingest
@@ -310,7 +317,23 @@ template <int BN, int MH> struct StripConfig {
     static constexpr int CTAS_PER_SM = (MH == 1 && BN == 64) ? 2 : 1;
     static constexpr int SMEM_BYTES = SA * A_STAGE_BYTES + SB * B_STAGE_BYTES + 1024 + 256;
     static constexpr uint32_t IDESC = tc::Config<BN>::IDESC;
+    static constexpr uint32_t IDESC_WIDE = tc::Config<2 * BN <= 256 ? 2 * BN : 256>::IDESC;
 };
+
+// One 32-wide k block with the hi and lo tiles of B taken as one operand of twice the columns (StripConfig::MERGED):
+// d[:, 0:BN] = a_hi * b_hi + a_lo * b_hi, d[:, BN:2BN] = a_hi * b_lo.  dbh is the descriptor of the hi tile; the lo tile
+// follows it in shared memory.
+__device__ __forceinline__ void mma_block_merged(uint32_t d_tmem, uint64_t dah, uint64_t dal, uint64_t dbh, uint32_t idesc, uint32_t idesc_wide,
+                                                 bool fresh) {
+    tc::mma_tf32(d_tmem, dah, dbh, idesc_wide, fresh ? 0u : 1u);
+    tc::mma_tf32_acc(d_tmem, dal, dbh, idesc);
+#pragma unroll
+    for (int ks = 1; ks < BK / 8; ++ks) {
+        dah += 2; dal += 2; dbh += 2;
+        tc::mma_tf32_acc(d_tmem, dah, dbh, idesc_wide);
+        tc::mma_tf32_acc(d_tmem, dal, dbh, idesc);
+    }
+}
 
 // The same descriptor with the row's position inside the 1024-byte swizzle period, (address >> 7) & 7, in the
 // base-offset field (bits 49-51).  Kept for the diagnostic mode only: see the note on the strip engine above.
@@ -396,9 +419,14 @@ strip_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__
 #pragma unroll
                     for (int c = 0; c < NACC; c += 16) {
                         float v[16];
-                        tc::tmem_ld16(tmem_mine + static_cast<uint32_t>((b * MH + h) * BN + c), v);
+                        tc::tmem_ld16(tmem_mine + static_cast<uint32_t>((b * MH + h) * Cfg::ACC_COLS + c), v);
 #pragma unroll
                         for (int j = 0; j < 16; ++j) acc[h][c + j] += v[j];
+                        if (Cfg::MERGED) {      // the a_hi * b_lo half of the accumulator
+                            tc::tmem_ld16(tmem_mine + static_cast<uint32_t>((b * MH + h) * Cfg::ACC_COLS + BN + c), v);
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) acc[h][c + j] += v[j];
+                        }
                     }
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
@@ -497,9 +525,11 @@ strip_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__
                     const uint64_t dbh = tc::make_desc(b_hi), dbl = tc::make_desc(b_lo);
 #pragma unroll
                     for (int h = 0; h < MH; ++h) {      // the row halves share the weight operand
-                        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((b * MH + h) * BN);
+                        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((b * MH + h) * Cfg::ACC_COLS);
                         const uint32_t ah = a_hi + h * 2 * STRIP_HALF_BYTES, al = a_lo + h * 2 * STRIP_HALF_BYTES;
-                        if (p.use_base_offset)      // diagnostic mode only
+                        if (Cfg::MERGED)
+                            mma_block_merged(d_tmem, tc::make_desc(ah), tc::make_desc(al), dbh, Cfg::IDESC, Cfg::IDESC_WIDE, first_of_pair);
+                        else if (p.use_base_offset)      // diagnostic mode only
                             tc::mma_block_3xtf32(d_tmem, make_desc_at(ah), make_desc_at(al), dbh, dbl, Cfg::IDESC, first_of_pair);
                         else
                             tc::mma_block_3xtf32(d_tmem, tc::make_desc(ah), tc::make_desc(al), dbh, dbl, Cfg::IDESC, first_of_pair);
