@@ -258,8 +258,8 @@ def test_workspace_reserve_keeps_a_roomy_pool_trainable(vdnn):
     tight = _steps(vdnn, int(peak * 1.45), False, steps=3, **vgg)
     roomy = _steps(vdnn, 12e9, False, steps=3, **vgg)
     assert tight[3] == roomy[3] and tight[4] == roomy[4] == peak
-    for a, b in zip(tight[0], roomy[0]):
-        assert rel_err(a, b) < 1e-5
+    for a, b in zip(tight[0], roomy[0]):           # three steps of atomically summed bias / FC gradients apart
+        assert rel_err(a, b) < 5e-5
     assert vdnn.ops.engine_status() == 0
 
 
