@@ -413,8 +413,12 @@ def run_b200(args):
     barrier(net)
 
     net.set_profiling(True)
+    # the clock sampler is started one (untimed) step early: nvidia-smi's own start-up takes driver locks for a few hundred
+    # milliseconds, which must not fall into the timed region; it then samples every 200 ms through that region
     sampler = ClockSampler(local)
     sampler.start()
+    net.step()
+    barrier(net)
     ms, launches, _ = timed(net, stream, hosts, args.steps, upload=False)
     clocks = sampler.stop()
     stats = net.stats()
