@@ -9,6 +9,11 @@ from helpers import rel_err, relu_knife_edges, tiny_net
 pytestmark = pytest.mark.gpu
 TOL = 1e-4
 POLICIES = ["BASELINE", "VDNN_NONE", "VDNN_ALL", "VDNN_CONV"]
+# Two runs of the same network differ by the order of their atomic sums (bias gradients of the TMA-fed layers, reduction
+# splits of the zero-workspace kernels).  The first layer's bias gradient is a sum of up to 1.6 M terms of either sign
+# per channel, so the second step's value carries that noise amplified by the cancellation: 1.2e-3 of the largest bias
+# was measured between runs; the bound leaves room for the tail.
+BIAS_NOISE = 5e-3
 
 
 def _run(vdnn, oracle, specs, cnn, policy, algo, batch, lr, steps=2, host_sync=False, init_mode=0, seed0=1000, pool_bytes=4e9,
@@ -221,7 +226,7 @@ def test_offload_order_is_not_observable(vdnn):
     for a, b in zip(by_need[0], in_order[0]):
         assert rel_err(a, b) < 5e-5
     for a, b in zip(by_need[1], in_order[1]):        # bias gradients are summed with atomics: run-to-run noise
-        assert rel_err(a, b) < 2e-3
+        assert rel_err(a, b) < BIAS_NOISE
     assert vdnn.ops.engine_status() == 0
 
 
@@ -239,7 +244,7 @@ def test_lean_offload_moves_fewer_bytes_and_trains_the_same(vdnn, model, batch, 
     for a, b in zip(lean[0], full[0]):
         assert rel_err(a, b) < 5e-5
     for a, b in zip(lean[1], full[1]):          # layer 0's bias gradient: up to 1.6 M terms per channel, summed with atomics
-        assert rel_err(a, b) < 2e-3
+        assert rel_err(a, b) < BIAS_NOISE
     assert vdnn.ops.engine_status() == 0
 
 
@@ -288,7 +293,7 @@ def test_held_blocks_are_given_back_under_pool_pressure(vdnn):
         for a, b in zip(other[0], roomy[0]):       # the zero-workspace kernels sum their reduction splits with atomics
             assert rel_err(a, b) < 5e-5
         for a, b in zip(other[1], roomy[1]):       # layer 0's bias gradient: 1.6 M terms per channel, summed with atomics
-            assert rel_err(a, b) < 2e-3
+            assert rel_err(a, b) < BIAS_NOISE
     assert vdnn.ops.engine_status() == 0
 
 
